@@ -1,0 +1,73 @@
+// Shared helpers of the sm_100a kernels: storage types, conversions, reductions,
+// and the device-side error word.
+//
+// Storage type T is float or __nv_bfloat16.  Arithmetic that the model's
+// numerics depend on (sums, softmax, norms, angles, residual adds) is done in
+// float; `store<T>` rounds to nearest even at the operator's edge, as the
+// reference rounds to its storage type at every operator boundary
+// (rust/engine/README.md:430-447).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LAB_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum LabDtype : int { LAB_F32 = 0, LAB_BF16 = 1 };
+
+// Error codes a kernel may leave in the error word (first one wins).
+enum LabDeviceError : int {
+  LAB_OK = 0,
+  LAB_ERR_PAGE_RANGE = 1,      // a page or slot index outside the pool
+  LAB_ERR_WAIT_TIMEOUT = 2,    // a bounded wait on an mbarrier ran out
+  LAB_ERR_ROW_RANGE = 3,       // a gathered row index outside the batch
+};
+
+// One copy per shared library (each library is built from one .cu file).
+static __device__ int g_lab_error_word;
+
+__device__ __forceinline__ void lab_set_error(int code) { atomicCAS(&g_lab_error_word, 0, code); }
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Round a float to the storage type and back: the value an operator boundary leaves.
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads, same order for every call; `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+#define LAB_LAUNCH_CHECK() return (int)cudaGetLastError()
+
+// Reads the error word of this library and clears it.  Synchronises the device.
+LAB_EXPORT int lab_take_error_word(int* out) {
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_lab_error_word, sizeof(int));
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemcpyToSymbol(g_lab_error_word, &zero, sizeof(int));
+}

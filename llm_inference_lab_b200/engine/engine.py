@@ -1,0 +1,271 @@
+"""The step function: one packed batch in, logits at the wanted places out.
+
+`Engine.step` takes entries ``(request id, next tokens, wanted places)``:
+portions of prompts beside single decoded tokens, cut anywhere.  It runs only
+the tokens it is given, as one batch, on top of the cache that earlier steps
+left, and returns 32-bit logits at the wanted places.  It is the counterpart of
+the reference's `CausalModel::next_tokens` / `step_with_logits`
+(rust/engine/src/runner/model/api.rs:203-243;
+rust/engine/src/runner/model/qwen2/engine.rs:781-789, 916-1130), with the
+difference that logits are produced only where asked (the reference computes a
+prediction at the end of every portion and the runner drops it,
+rust/engine/README.md:549-551).
+
+Order inside a step, as in the reference's `execute_append_batch`
+(rust/engine/src/runner/model/api.rs:80-106): validate, reserve pages, upload
+the step's metadata, run the kernels, then commit the cache.  A step that fails
+gives its reserved pages back.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import manager as cache_mod
+from ..kernels import ops
+from ..models.builder import CausalLM, load_model
+from ..parts.base import CacheView, GroupView, StepContext
+from ..parts.spec import FixedState, PagedKV
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
+          "fp32": torch.float32}
+
+
+class InvalidInput(ValueError):
+    """An entry the step refuses before anything runs (rust/engine/src/runner/model/error.rs:7-12)."""
+
+
+@dataclasses.dataclass
+class Entry:
+    """One request's share of a step."""
+    request: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()     # places among `tokens` whose logits are asked for
+
+
+@dataclasses.dataclass
+class EngineStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name in (torch.bfloat16, torch.float32):
+            return name
+        raise ValueError(f"unsupported dtype {name}")
+    try:
+        return DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"unknown dtype {name!r}: use bfloat16 or float32") from None
+
+
+class Engine:
+    """A model, its cache and the step function, on one GPU."""
+
+    def __init__(self, model: CausalLM | str, dtype="bfloat16", *, max_tokens: Optional[int] = None,
+                 page_size: int = 16, max_requests: int = 64, max_batch_tokens: int = 8192,
+                 max_seq_len: Optional[int] = None, device="cuda:0"):
+        ops.require_gpu()
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = parse_dtype(dtype)
+        if isinstance(model, str):
+            model, self.config = load_model(model, self.dtype, self.device)
+        else:
+            self.config = None
+        if model.dtype != self.dtype:
+            raise ValueError("the model was built for another dtype than the engine")
+        self.model = model
+        bp = model.blueprint
+        self.vocab = bp.vocab
+        self.page_size = int(page_size)
+        self.max_requests = int(max_requests)
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.max_seq_len = int(min(max_seq_len or bp.max_positions, bp.max_positions))
+        if max_tokens is None:
+            max_tokens = self.max_seq_len * min(self.max_requests, 8)
+        # Every request's count is rounded up to whole pages, so the pool is counted in pages.
+        self.num_pages = -(-int(max_tokens) // self.page_size)
+        plan = model.cache_plan
+        rt = cache_mod.runtime()
+        groups = [rt.GroupConfig(self.page_size, w, self.num_pages) for w in plan.group_windows]
+        self.cache = rt.CacheManager(groups, self.max_requests)
+        self.group_windows = list(plan.group_windows)
+        self.views: list[CacheView] = []
+        for need, group in zip(plan.needs, plan.group_of):
+            if isinstance(need, PagedKV):
+                shape = (self.num_pages, need.n_kv_heads, self.page_size, need.head_dim)
+                # Pages are never cleared: what may be read is decided by lengths alone.
+                k = torch.empty(shape, dtype=self.dtype, device=self.device)
+                v = torch.empty(shape, dtype=self.dtype, device=self.device)
+                self.views.append(CacheView(need, group=group, k=k, v=v))
+            elif isinstance(need, FixedState):
+                state = torch.zeros((self.max_requests,) + tuple(need.shape), dtype=torch.float32, device=self.device)
+                self.views.append(CacheView(need, state=state))
+            else:
+                self.views.append(CacheView(None))
+        self.max_blocks = -(-self.max_seq_len // self.page_size)
+        self.stats = EngineStats()
+        self._staging = [self._new_staging() for _ in range(3)]
+        self._staging_at = 0
+
+    # ------------------------------------------------------------------------------------
+    def _new_staging(self):
+        n_groups = len(self.group_windows)
+        cap_t, cap_b = self.max_batch_tokens, self.max_requests
+        words = (cap_t * (4 + n_groups) + cap_b * (5 + n_groups * (self.max_blocks + 8)) + 64) + 4 * 16
+        buf = torch.empty((words,), dtype=torch.int32, pin_memory=True)
+        return {"host": buf, "np": buf.numpy(), "event": None}
+
+    def _next_staging(self):
+        st = self._staging[self._staging_at]
+        self._staging_at = (self._staging_at + 1) % len(self._staging)
+        if st["event"] is not None:
+            st["event"].synchronize()
+        return st
+
+    # ------------------------------------------------------------------------------------
+    def open(self, request: int) -> None:
+        """A new request: takes a state slot and clears its fixed-size state."""
+        slot = self.cache.open(int(request))
+        for view in self.views:
+            if view.state is not None:
+                view.state[slot].zero_()
+
+    def close(self, request: int) -> None:
+        """The request ends; its pages and its state slot may be used again."""
+        self.cache.close(int(request))
+
+    def has(self, request: int) -> bool:
+        return self.cache.has(int(request))
+
+    def length(self, request: int) -> int:
+        return self.cache.length(int(request))
+
+    def free_pages(self) -> list[int]:
+        return [self.cache.free_pages(g) for g in range(self.cache.num_groups)]
+
+    # ------------------------------------------------------------------------------------
+    def validate(self, entries: Sequence[Entry]) -> None:
+        if not entries:
+            raise InvalidInput("a step needs at least one entry")
+        seen = set()
+        total = 0
+        for e in entries:
+            n = len(e.tokens)
+            if e.request in seen:
+                raise InvalidInput(f"request {e.request} appears twice in one step")
+            seen.add(e.request)
+            if n == 0:
+                raise InvalidInput(f"request {e.request}: no tokens in this step")
+            held = self.cache.reserved(e.request) if self.cache.has(e.request) else 0
+            if held + n > self.max_seq_len:
+                raise InvalidInput(f"request {e.request}: {held + n} tokens exceed the maximum sequence length "
+                                   f"{self.max_seq_len}")
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= self.vocab:
+                raise InvalidInput(f"request {e.request}: token id outside [0, {self.vocab})")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise InvalidInput(f"request {e.request}: wanted place {w} outside its {n} tokens")
+            total += n
+        if total > self.max_batch_tokens:
+            raise InvalidInput(f"{total} tokens in one step exceed max_batch_tokens {self.max_batch_tokens}")
+        if len(entries) > self.max_requests:
+            raise InvalidInput(f"{len(entries)} requests in one step exceed max_requests {self.max_requests}")
+
+    def step(self, entries: Sequence[Entry], reserved: bool = False) -> Optional[torch.Tensor]:
+        """Runs one packed batch.  Returns 32-bit logits [wanted, vocab] on the device, in
+        the order of the entries and of their `want`, or None if nothing was wanted.
+
+        With ``reserved`` the caller (the scheduler) has reserved the pages already.
+        """
+        entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        self.validate(entries)
+        opened = []
+        taken = []
+        try:
+            for e in entries:
+                if not self.cache.has(e.request):
+                    self.open(e.request)
+                    opened.append(e.request)
+            if not reserved:
+                for e in entries:
+                    self.cache.reserve(e.request, len(e.tokens))
+                    taken.append(e.request)
+            ctx, logit_rows = self._pack(entries)
+            logits = self.model.forward(ctx, self.views, logit_rows)
+        except Exception:
+            for r in taken:
+                self.cache.rollback(r)
+            for r in opened:
+                self.cache.close(r)
+            raise
+        if not reserved:
+            for e in entries:
+                self.cache.commit(e.request, len(e.tokens))
+        self.stats.steps += 1
+        for e in entries:
+            if len(e.tokens) == 1 and self.cache.reserved(e.request) > 1:
+                self.stats.decode_tokens += 1
+            else:
+                self.stats.prefill_tokens += len(e.tokens)
+        return logits
+
+    # ------------------------------------------------------------------------------------
+    def _pack(self, entries: Sequence[Entry]):
+        pairs = [(int(e.request), len(e.tokens)) for e in entries]
+        T = sum(n for _, n in pairs)
+        B = len(pairs)
+        n_groups = len(self.group_windows)
+        widths = []
+        for g in range(n_groups):
+            ps = self.page_size
+            width = max(-(-self.cache.reserved(r) // ps) for r, _ in pairs)
+            widths.append((width + 7) & ~7)
+        layout = self.cache.layout(T, B, widths)
+        n_want = sum(len(e.want) for e in entries)
+        tok_at = layout.total
+        want_at = tok_at + ((T + 3) & ~3)
+        total = want_at + ((n_want + 3) & ~3)
+        st = self._next_staging()
+        if total > st["np"].shape[0]:
+            raise InvalidInput("step metadata exceeds the staging buffer")
+        host = st["np"]
+        self.cache.pack(pairs, layout, host, 0, 0)
+        row = 0
+        wi = want_at
+        for e in entries:
+            n = len(e.tokens)
+            host[tok_at + row: tok_at + row + n] = np.asarray(e.tokens, dtype=np.int32)
+            for w in e.want:
+                host[wi] = row + w
+                wi += 1
+            row += n
+        dev = torch.empty((total,), dtype=torch.int32, device=self.device)
+        dev.copy_(st["host"][:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        st["event"] = ev
+
+        def view(at, n):
+            return dev[at: at + n]
+
+        q_lens = [n for _, n in pairs]
+        kv_lens = [self.cache.reserved(r) for r, _ in pairs]
+        groups = [GroupView(self.page_size, self.group_windows[g], view(layout.row_slot[g], T),
+                            view(layout.block_table[g], B * widths[g]).view(B, widths[g])) for g in range(n_groups)]
+        ctx = StepContext(
+            dtype=self.dtype, device=self.device, n_tokens=T, n_requests=B,
+            token_ids=view(tok_at, T), row_req=view(layout.row_req, T), row_pos=view(layout.row_pos, T),
+            q_start=view(layout.q_start, B + 1), kv_len=view(layout.kv_len, B), pos0=view(layout.pos0, B),
+            state_slot=view(layout.state_slot, B), groups=groups, q_lens=q_lens, kv_lens=kv_lens,
+            state_slots=[self.cache.state_slot(r) for r, _ in pairs],
+            max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+        logit_rows = view(want_at, n_want) if n_want else None
+        return ctx, logit_rows

@@ -1,0 +1,229 @@
+"""Python face of the CUDA kernels.
+
+Each function checks shapes and types on the host, then calls one ``extern "C"``
+entry point of a library built from ``csrc/kernels`` on the current CUDA stream.
+There is no fallback: without a GPU, or without the built library, a call
+raises.  Tensors are torch tensors on the GPU; a kernel never allocates.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_libs: dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+DEVICE_ERRORS = {1: "a page or slot index outside the pool", 2: "a bounded wait inside a kernel ran out",
+                 3: "a gathered row index outside the batch"}
+
+
+def lib(name: str, defines: dict[str, int] | None = None) -> ctypes.CDLL:
+    key = name + repr(sorted((defines or {}).items()))
+    with _lock:
+        if key in _libs:
+            return _libs[key]
+    path = build.kernel_library(name, defines)
+    handle = ctypes.CDLL(path)
+    with _lock:
+        _libs[key] = handle
+    return handle
+
+
+def require_gpu() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: the engine runs on a B200 only and has no CPU fallback")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported storage type {dtype}: the kernels take float32 or bfloat16")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _on_gpu(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must be CUDA tensors")
+
+
+def take_device_errors() -> None:
+    """Synchronise and raise if any kernel left an error code."""
+    for key, handle in list(_libs.items()):
+        out = ctypes.c_int(0)
+        _check(handle.lab_take_error_word(ctypes.byref(out)), "reading the error word")
+        if out.value:
+            raise KernelError(f"kernel library {key.split('[')[0]} reported: "
+                              f"{DEVICE_ERRORS.get(out.value, out.value)}")
+
+
+# ----------------------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _on_gpu(ids, table)
+    tokens, (vocab, hidden) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=table.dtype, device=table.device)
+    assert ids.dtype == torch.int32 and table.is_contiguous() and out.is_contiguous()
+    _check(lib("rowwise").lab_embed(_ptr(out), _ptr(table), _ptr(ids), tokens, hidden, vocab,
+                                    dtype_code(table.dtype), _stream()), "embed")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, delta: torch.Tensor | None = None,
+                partial: torch.Tensor | None = None, rows: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """x += delta (+ sum of `partial` over its first axis), in place; returns rmsnorm(x) * weight.
+
+    With `rows`, output row i is computed from x[rows[i]] and x is left as it is.
+    """
+    _on_gpu(x, weight, delta, partial, rows)
+    n_in, hidden = x.shape
+    n_out = n_in if rows is None else rows.numel()
+    if out is None:
+        out = torch.empty((n_out, hidden), dtype=x.dtype, device=x.device)
+    assert x.is_contiguous() and weight.dtype == x.dtype and weight.numel() == hidden
+    assert delta is None or (delta.shape == x.shape and delta.dtype == x.dtype and delta.is_contiguous())
+    splits, stride = 0, 0
+    if partial is not None:
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.shape[1:] == x.shape
+        splits, stride = partial.shape[0], n_in * hidden
+    _check(lib("rowwise").lab_add_rmsnorm(_ptr(out), _ptr(x), _ptr(delta), _ptr(partial), splits,
+                                          ctypes.c_longlong(stride), _ptr(weight), _ptr(rows), n_out, n_in, hidden,
+                                          ctypes.c_float(eps), dtype_code(x.dtype), _stream()), "add_rmsnorm")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+                  slots: torch.Tensor | None, cache_k: torch.Tensor | None, cache_v: torch.Tensor | None,
+                  n_q: int, n_kv: int, head_dim: int) -> None:
+    """Rotate q (in place) and k, and write k and v to their cache slots."""
+    _on_gpu(qkv, positions, inv_freq, slots, cache_k, cache_v)
+    tokens = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == (n_q + 2 * n_kv) * head_dim
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2
+    page_size = num_pages = 0
+    if cache_k is not None:
+        num_pages, kvh, page_size, d = cache_k.shape
+        assert kvh == n_kv and d == head_dim and cache_k.is_contiguous() and cache_v.is_contiguous()
+        assert cache_k.dtype == qkv.dtype and cache_v.shape == cache_k.shape and slots is not None
+    _check(lib("rowwise").lab_rope_kv_write(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(inv_freq), rotary_dim,
+                                            _ptr(slots), _ptr(cache_k), _ptr(cache_v), tokens, n_q, n_kv, head_dim,
+                                            page_size, num_pages, dtype_code(qkv.dtype), _stream()), "rope_kv_write")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    tokens, two_i = gate_up.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib("rowwise").lab_silu_mul(_ptr(out), _ptr(gate_up), tokens, inter, dtype_code(gate_up.dtype), _stream()),
+           "silu_mul")
+    return out
+
+
+def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
+               out_f32: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x @ w.T (+ bias) on the ordinary arithmetic units; `gated`: silu(x@wg.T) * (x@wu.T), w = [wg; wu]."""
+    _on_gpu(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0] // 2 if gated else w.shape[0]
+    assert w.shape[1] == K and w.is_contiguous() and x.stride(1) == 1 and w.dtype == x.dtype
+    assert bias is None or (bias.dtype == x.dtype and bias.numel() == N and not gated)
+    odt = torch.float32 if (out_f32 or x.dtype == torch.float32) else x.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=odt, device=x.device)
+    assert out.dtype == odt and out.stride(1) == 1 and out.shape == (M, N)
+    _check(lib("gemm_plain").lab_gemm_plain(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), M, N, K, x.stride(0),
+                                            out.stride(0), int(gated), dtype_code(x.dtype), int(out_f32), _stream()),
+           "gemm_plain")
+    return out
+
+
+def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, row_req: torch.Tensor,
+                    row_pos: torch.Tensor, block_table: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                    window: int, scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of every row over its request's pages; q may be a column slice of the fused projection."""
+    _on_gpu(q, cache_k, cache_v, row_req, row_pos, block_table)
+    tokens = q.shape[0]
+    if out is None:
+        out = torch.empty((tokens, n_q * head_dim), dtype=q.dtype, device=q.device)
+    num_pages, kvh, page_size, d = cache_k.shape
+    assert kvh == n_kv and d == head_dim and q.stride(1) == 1 and cache_k.dtype == q.dtype
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+    _check(lib("attention_plain").lab_attention_plain(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v), _ptr(row_req), _ptr(row_pos),
+        _ptr(block_table), block_table.shape[1], tokens, n_q, n_kv, head_dim, page_size, num_pages, window,
+        ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attention_plain")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seeds: torch.Tensor | None = None,
+           positions: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of 32-bit logits: greedy where temperature is 0 (or None), else Gumbel-max."""
+    _on_gpu(logits, temperature, seeds, positions)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    if temperature is not None:
+        assert temperature.dtype == torch.float32 and seeds.dtype == torch.int32 and positions.dtype == torch.int32
+        assert temperature.numel() == rows and seeds.numel() == rows and positions.numel() == rows
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _check(lib("sampling").lab_sample(_ptr(out), _ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab,
+                                      _ptr(temperature), _ptr(seeds), _ptr(positions), _stream()), "sample")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# Dispatch: which kernel serves a matrix product or an attention call.
+#
+# float32 always runs the plain kernels (a true 32-bit path: no tensor cores, no reduced
+# precision).  bfloat16 runs the tensor-core kernels; `force_plain(True)` sends bfloat16 to
+# the plain kernels as well, which tests use to tell a kernel fault from a model fault.
+# ----------------------------------------------------------------------------------------
+_force_plain = False
+
+
+def force_plain(flag: bool) -> bool:
+    global _force_plain
+    old, _force_plain = _force_plain, bool(flag)
+    return old
+
+
+def linear(x, w, bias=None, out_f32=False, allow_partial=False):
+    """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
+    products [splits, tokens, out] that the following `add_rmsnorm` sums."""
+    return gemm_plain(x, w, bias, out_f32=out_f32)
+
+
+def linear_gated(x, w_gate_up):
+    """silu(x @ wg.T) * (x @ wu.T) with w_gate_up = [wg; wu]."""
+    return gemm_plain(x, w_gate_up, None, gated=True)
+
+
+def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale):
+    return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
+                           window, scale)

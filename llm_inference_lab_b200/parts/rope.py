@@ -1,0 +1,43 @@
+"""Rotary position encoding (split-half pairing) with a theta parameter."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .base import PositionEncoding, register_part
+
+
+class Rope(PositionEncoding):
+    """inv_freq[i] = theta^(-2i/rotary_dim) held in 32-bit; the angle pos * inv_freq is formed
+    in 32-bit on the device (rust/engine/src/runner/model/qwen2/engine.rs:304-311, kernels.rs:587-631).
+    The rotation of q and k is fused with the write of k and v into the cache pages."""
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        self.rotary_dim = int(spec["rotary_dim"])
+        i = np.arange(self.rotary_dim // 2, dtype=np.float64)
+        inv = np.power(float(spec["theta"]), -2.0 * i / self.rotary_dim).astype(np.float32)
+        self.inv_freq = torch.from_numpy(inv).to(device)
+
+    def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim):
+        write = cache is not None and cache.write
+        ops.rope_kv_write(qkv, positions, self.inv_freq, self.rotary_dim, slots if write else None,
+                          cache.k if write else None, cache.v if write else None, n_q, n_kv, head_dim)
+
+
+class NoPosition(PositionEncoding):
+    """No encoding: q and k are used as projected; k and v are still written to the cache."""
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        self.inv_freq = torch.zeros((0,), dtype=torch.float32, device=device)
+
+    def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim):
+        write = cache is not None and cache.write
+        if write:
+            ops.rope_kv_write(qkv, positions, self.inv_freq, 0, slots, cache.k, cache.v, n_q, n_kv, head_dim)
+
+
+register_part("position", "rope", Rope)
+register_part("position", "none", NoPosition)
