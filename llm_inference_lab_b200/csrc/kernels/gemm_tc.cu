@@ -1,0 +1,478 @@
+// Matrix product on the 5th-generation tensor cores of sm_100a: TMA loads into
+// 128-byte-swizzled shared memory, tcgen05.mma with the accumulator in tensor memory,
+// tcgen05.ld for the epilogue.
+//
+//   out[t, n] = OutT( sum_k x[t, k] * w[n, k]  (+ bias[n]) )                 w is [out, in]
+//   gated:      out[t, n] = T( T(silu(T(g))) * T(u) ),  g = x . w[n], u = x . w[inter + n]
+//   split-K:    partial[z, t, n] = sum over the z-th slice of k   (32-bit, summed by the
+//               kernel that consumes it, in a fixed order)
+//
+// Both operands are K-major bfloat16 ([rows, K] row-major), which is how activations and
+// checkpoint weights ([out, in]) already lie, so nothing is transposed.  The operand on the
+// M side of the MMA is cut in tiles of 128 rows, the one on the N side in tiles of BN rows.
+// "Normal" orientation puts tokens on M and output features on N (prefill: many tokens);
+// "swapped" puts output features on M and the few tokens of a decode step on N, so that a
+// step with 1..256 tokens still fills the 128-row MMA and streams every weight once.
+//
+// One CTA computes one output tile: warp 0 issues TMA loads into a ring of stages, warp 1
+// issues the MMAs (one elected lane) and owns the tensor-memory allocation, warps 2-5 read
+// the accumulator back (each its quarter of the 128 lanes) and apply the epilogue.  Every
+// wait on an mbarrier is bounded: when it runs out the kernel records an error code, lets
+// the other roles drain and frees its tensor memory before it returns.
+//
+// Formulas and rounding order: rust/engine/src/runner/model/qwen2/kernels.rs:156-178,
+// 393-418 (32-bit accumulation, bias added in 32-bit, one rounding), 422-448 and 1469-1486
+// (gate/up with the SiLU product), 300-387 (split-K partials merged in 32-bit).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;  // rows of the M-side tile (UMMA M)
+constexpr int BK = 64;   // bf16 elements per k-tile: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after about two seconds and reports it.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > 2000000000ull) {
+      *abort_flag = 1;
+      lab_set_error(LAB_ERR_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, bf16 inputs, 32-bit accumulate.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128B-swizzled:
+// 8-row groups lie 1024 bytes apart (stride byte offset), the leading offset is one 16-byte unit.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);  // start address, bits [0, 14)
+  d |= (uint64_t)1 << 16;                  // leading byte offset (16 bytes), bits [16, 30)
+  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset, bits [32, 46)
+  d |= (uint64_t)1 << 46;                  // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                  // layout: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float silu_gate(float g, float u) {
+  g = bf16_round(g);
+  u = bf16_round(u);
+  return bf16_round(g / (1.f + expf(-g))) * u;
+}
+
+struct Params {
+  void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats
+  const __nv_bfloat16* bias;
+  int m_rows;           // valid rows on the M side (tokens, or features when swapped)
+  int n_rows;           // valid rows on the N side
+  int ld_out;
+  long long split_stride;  // elements between split-K partial planes (0: no split)
+  int k_tiles;          // k-tiles in total
+  int k_tiles_per_split;
+  int up_offset;        // gated: row offset of the "up" half inside the weight matrix
+};
+
+template <int BN, bool GATED, bool SWAP>
+struct Shape {
+  static constexpr int A_TILES = (GATED && SWAP) ? 2 : 1;
+  static constexpr int A_BYTES = A_TILES * BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int ACC_COLS = A_TILES * BN;
+  static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool GATED, bool SWAP, typename OutT>
+__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                          const __grid_constant__ CUtensorMap map_b, Params p) {
+  using S = Shape<BN, GATED, SWAP>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* acc_full = empty + S::STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM;
+  const int n_tile_rows = (GATED && !SWAP) ? BN / 2 : BN;  // rows of the N-side operand per tile
+  const int n0 = blockIdx.y * n_tile_rows;
+  const int kt0 = blockIdx.z * p.k_tiles_per_split;
+  int kt1 = kt0 + p.k_tiles_per_split;
+  if (kt1 > p.k_tiles) kt1 = p.k_tiles;
+  const int n_kt = kt1 - kt0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, S::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: TMA loads ----
+      int issued = 0;
+      for (int i = 0; i < n_kt; ++i) {
+        const int s = i % S::STAGES;
+        const uint32_t ph = (i / S::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + S::A_BYTES;
+        mbar_expect_tx(&full[s], S::STAGE_BYTES);
+        const int kx = (kt0 + i) * BK;
+        tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
+        if (GATED && SWAP) tma_load_2d(a_dst + BM * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
+        if (GATED && !SWAP) {
+          tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
+          tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kx, p.up_offset + n0);
+        } else {
+          tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
+        }
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // Let copies in flight land before the CTA's shared memory goes away.
+        const int first = issued > S::STAGES ? issued - S::STAGES : 0;
+        for (int i = first; i < issued; ++i) {
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&full[i % S::STAGES], (i / S::STAGES) & 1) && global_timer_ns() - t0 < 100000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      constexpr uint32_t idesc = instr_desc(BN);
+      bool ok = true;
+      for (int i = 0; i < n_kt && ok; ++i) {
+        const int s = i % S::STAGES;
+        const uint32_t ph = (i / S::STAGES) & 1;
+        ok = mbar_wait(&full[s], ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t db = smem_desc_sw128(b_addr + k * UMMA_K * 2);
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, acc);
+          if (GATED && SWAP)
+            umma_bf16(tmem_base + BN, smem_desc_sw128(a_addr + BM * BK * 2 + k * UMMA_K * 2), db, idesc, acc);
+        }
+        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(acc_full);     // the accumulator is complete once every MMA has retired
+    }
+  } else {
+    // ---- epilogue: warps 2..5, each reads its quarter of the 128 accumulator lanes ----
+    const int quarter = warp & 3;
+    const bool ok = n_kt > 0 ? mbar_wait(acc_full, 0, abort_flag) : true;
+    tc_fence_after();
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int m = m0 + quarter * 32 + lane;  // this thread's row on the M side
+    const bool partial = p.split_stride != 0;
+    if (ok && !*abort_flag) {
+      if (!SWAP) {
+        // thread = token row m; columns = output features
+        constexpr int OUT_COLS = GATED ? BN / 2 : BN;
+        const int nbase = blockIdx.y * OUT_COLS;
+#pragma unroll 1
+        for (int c = 0; c < OUT_COLS / 16; ++c) {
+          float v[16];
+          if (n_kt > 0) tmem_ld16(lane_addr + c * 16, v);
+          else
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          if (GATED) {
+            float u[16];
+            tmem_ld16(lane_addr + BN / 2 + c * 16, u);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = silu_gate(v[j], u[j]);
+          }
+          const int n = nbase + c * 16;
+          if (m >= p.m_rows || n >= p.n_rows) continue;
+          if (partial) {
+            float* dst = (float*)p.out + blockIdx.z * p.split_stride + (size_t)m * p.ld_out + n;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (n + j < p.n_rows) dst[j] = v[j];
+          } else {
+            if (p.bias)
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n + j < p.n_rows) v[j] += __bfloat162float(p.bias[n + j]);
+            OutT* dst = (OutT*)p.out + (size_t)m * p.ld_out + n;
+            if (sizeof(OutT) == 2 && n + 16 <= p.n_rows && (((uintptr_t)dst) & 15) == 0) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n + j < p.n_rows) dst[j] = from_f32<OutT>(v[j]);
+            }
+          }
+        }
+      } else {
+        // thread = output feature m; columns = tokens
+        const float b = (p.bias && !partial && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 16; ++c) {
+          const int t = n0 + c * 16;
+          if (t >= p.n_rows) break;  // same for the whole warp
+          float v[16];
+          if (n_kt > 0) tmem_ld16(lane_addr + c * 16, v);
+          else
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          if (GATED) {
+            float u[16];
+            tmem_ld16(lane_addr + BN + c * 16, u);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = silu_gate(v[j], u[j]);
+          }
+          if (m >= p.m_rows) continue;
+          if (partial) {
+            float* dst = (float*)p.out + blockIdx.z * p.split_stride + m;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = v[j];
+          } else {
+            OutT* dst = (OutT*)p.out + m;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(v[j] + b);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, S::TMEM_COLS);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// Map of a row-major bf16 matrix [rows, K] with row stride ld (elements); box = [64, box_rows].
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int BN, bool GATED, bool SWAP, typename OutT>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
+  using S = Shape<BN, GATED, SWAP>;
+  static bool configured = false;
+  auto kern = gemm_tc_kernel<BN, GATED, SWAP, OutT>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, THREADS, S::SMEM, stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+template <bool GATED, bool SWAP, typename OutT>
+int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16: if constexpr (SWAP) return launch<16, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 32: if constexpr (SWAP) return launch<32, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 64: return launch<64, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+    case 128: return launch<128, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+    case 256: return launch<256, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+  }
+  return (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// x: [tokens, K] bf16 (row stride ldx), w: [n_out (x2 when gated), K] bf16 contiguous.
+// out: bf16 or f32 [tokens, ld_out]; with splits > 1, `out` is the partial buffer
+// [splits, tokens, ld_out] of floats (no bias, not gated).
+// swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256).
+LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
+                           int ldx, int ld_out, int gated, int out_f32, int swap, int bn, int splits,
+                           cudaStream_t stream) {
+  if (tokens <= 0 || n_out <= 0) return 0;
+  if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA
+  if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return (int)cudaErrorInvalidValue;  // 16-byte bases for TMA
+  if (splits < 1 || (splits > 1 && (gated || !out_f32))) return (int)cudaErrorInvalidValue;
+  const int w_rows = gated ? 2 * n_out : n_out;
+  CUtensorMap ma, mb;
+  Params p;
+  p.out = out;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.ld_out = ld_out;
+  p.k_tiles = (K + BK - 1) / BK;
+  p.k_tiles_per_split = (p.k_tiles + splits - 1) / splits;
+  p.split_stride = splits > 1 ? (long long)tokens * ld_out : 0;
+  p.up_offset = n_out;
+  dim3 grid;
+  int rc;
+  if (!swap) {
+    const int box_b = gated ? bn / 2 : bn;
+    if ((rc = make_map(&ma, x, tokens, K, ldx, BM))) return rc;
+    if ((rc = make_map(&mb, w, w_rows, K, K, box_b))) return rc;
+    p.m_rows = tokens;
+    p.n_rows = n_out;
+    grid = dim3((tokens + BM - 1) / BM, (n_out + box_b - 1) / box_b, splits);
+  } else {
+    if ((rc = make_map(&ma, w, w_rows, K, K, BM))) return rc;
+    if ((rc = make_map(&mb, x, tokens, K, ldx, bn))) return rc;
+    p.m_rows = n_out;
+    p.n_rows = tokens;
+    grid = dim3((n_out + BM - 1) / BM, (tokens + bn - 1) / bn, splits);
+  }
+  // A gated tile whose "gate" rows run past n_out would read "up" rows as gate: tiles are cut so
+  // that valid outputs never mix the halves (rows >= n_out are masked in the epilogue), but the
+  // up half must start at a row the map can address with the same box.
+  if (gated) {
+    if (swap) {
+      if (out_f32) return (int)cudaErrorInvalidValue;
+      return dispatch_bn<true, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+    }
+    if (out_f32) return (int)cudaErrorInvalidValue;
+    return dispatch_bn<true, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+  }
+  if (swap) {
+    if (out_f32) return dispatch_bn<false, true, float>(bn, ma, mb, p, grid, stream);
+    return dispatch_bn<false, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+  }
+  if (out_f32) return dispatch_bn<false, false, float>(bn, ma, mb, p, grid, stream);
+  return dispatch_bn<false, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+}

@@ -1,0 +1,106 @@
+"""The Python entry point: prompts in, generated tokens out.
+
+`LLM` owns an `Engine` (model, cache, step function), the C++ `Scheduler` and a
+`Sampler`, and drives them the way the reference's runner drives its model
+(rust/engine/src/runner/model_runner.rs:698-897): plan a step, run it, accept
+the sampled tokens, finish and free.  Token ids go in and come out; text is
+handled at the command line only.
+"""
+from __future__ import annotations
+
+import dataclasses
+import time
+from typing import Optional, Sequence, Union
+
+from ..cache import manager as cache_mod
+from ..sampling import Sampler, SamplingConfig
+from .engine import Engine, Entry
+
+
+@dataclasses.dataclass
+class GenerationResult:
+    request_id: int
+    prompt_tokens: list[int]
+    tokens: list[int]
+    finish_reason: str          # "length" | "eos" | "capacity" | "invalid" | "cancelled"
+    message: str = ""
+    preemptions: int = 0
+    ttft: Optional[float] = None
+
+
+class LLM:
+    def __init__(self, model_dir: str, dtype: str = "bf16", *, max_batch_tokens: int = 512,
+                 kv_tokens: Optional[int] = None, page_size: int = 16, max_requests: int = 64,
+                 max_seq_len: Optional[int] = None, reserve_future: bool = True, cuda_graph: bool = False,
+                 device: str = "cuda:0"):
+        self.engine = Engine(model_dir, dtype, max_tokens=kv_tokens, page_size=page_size, max_requests=max_requests,
+                             max_batch_tokens=max_batch_tokens, max_seq_len=max_seq_len, device=device)
+        rt = cache_mod.runtime()
+        self.scheduler = rt.Scheduler(self.engine.cache, max_batch_tokens, self.engine.max_seq_len, max_requests,
+                                      reserve_future)
+        self.sampler = Sampler(self.engine.device)
+        self.model_eos = list(self.engine.model.blueprint.eos_token_ids)
+        self.cuda_graph = bool(cuda_graph)
+        self._next_id = 0
+        self.steps = 0
+
+    # ------------------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling: Union[None, SamplingConfig, Sequence[SamplingConfig]] = None) -> list[GenerationResult]:
+        """Runs all prompts to their end with continuous batching; results in prompt order."""
+        if sampling is None:
+            sampling = SamplingConfig()
+        configs = list(sampling) if isinstance(sampling, (list, tuple)) else [sampling] * len(prompts)
+        if len(configs) != len(prompts):
+            raise ValueError("one SamplingConfig per prompt, or one for all")
+        ids = []
+        by_id = {}
+        vocab = self.engine.vocab
+        for prompt, cfg in zip(prompts, configs):
+            cfg.validate()
+            prompt = [int(t) for t in prompt]
+            rid = self._next_id
+            self._next_id += 1
+            ids.append(rid)
+            by_id[rid] = {"cfg": cfg, "prompt": prompt, "t0": time.perf_counter(), "ttft": None}
+            if any(t < 0 or t >= vocab for t in prompt):
+                by_id[rid]["result"] = GenerationResult(rid, prompt, [], "invalid", f"token id outside [0, {vocab})")
+                continue
+            self.scheduler.add(rid, prompt, cfg.max_new_tokens, cfg.eos_ids(self.model_eos), cfg.ignore_eos)
+        self._run(by_id)
+        return [by_id[r]["result"] for r in ids]
+
+    def _collect(self, by_id) -> None:
+        for f in self.scheduler.take_finished():
+            rec = by_id[f.id]
+            rec["result"] = GenerationResult(f.id, rec["prompt"], list(f.generated), f.reason.name, f.message,
+                                             f.preemptions, rec["ttft"])
+
+    def _run(self, by_id) -> None:
+        sched = self.scheduler
+        while True:
+            plan = sched.plan()
+            self._collect(by_id)
+            if not plan:
+                if sched.idle:
+                    return
+                raise RuntimeError("the scheduler has requests left but plans no step")
+            entries = [Entry(e.id, sched.portion(e.id, e.start, e.n), [e.n - 1] if e.sample else []) for e in plan]
+            try:
+                logits = self.engine.step(entries, reserved=True)
+            except Exception:
+                sched.abandon(plan)
+                raise
+            sampled = []
+            if logits is not None:
+                rows = [e for e in plan if e.sample]
+                cfgs = [by_id[e.id]["cfg"] for e in rows]
+                sampled = self.sampler.pick(logits, [c.effective_temperature() for c in cfgs],
+                                            [c.seed for c in cfgs], [e.start + e.n for e in rows])
+                now = time.perf_counter()
+                for e in rows:
+                    if by_id[e.id]["ttft"] is None:
+                        by_id[e.id]["ttft"] = now - by_id[e.id]["t0"]
+            sched.complete(plan, sampled)
+            self.steps += 1
+            self._collect(by_id)

@@ -205,6 +205,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seeds:
 # the plain kernels as well, which tests use to tell a kernel fault from a model fault.
 # ----------------------------------------------------------------------------------------
 _force_plain = False
+SM_COUNT = 148
 
 
 def force_plain(flag: bool) -> bool:
@@ -213,15 +214,77 @@ def force_plain(flag: bool) -> bool:
     return old
 
 
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
+            out_f32: bool = False, swap: bool | None = None, bn: int | None = None, splits: int = 1,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulate).
+
+    `swap` puts output features on the 128-row side of the MMA (few tokens); `bn` is the
+    tile on the other side; `splits` > 1 returns 32-bit partial products [splits, tokens, out].
+    """
+    _on_gpu(x, w, bias, out)
+    T, K = x.shape
+    n_out = w.shape[0] // 2 if gated else w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc takes bfloat16 operands")
+    if K % 8 or x.stride(0) % 8 or x.stride(1) != 1 or not w.is_contiguous() or w.shape[1] != K:
+        raise KernelError(f"gemm_tc: K={K} and the row stride must be multiples of 8 (16-byte rows for TMA)")
+    if x.data_ptr() % 16 or w.data_ptr() % 16:
+        raise KernelError("gemm_tc: operands must start on a 16-byte boundary")
+    if swap is None:
+        swap = T <= 128
+    if bn is None:
+        if swap:
+            bn = 16
+            while bn < min(T, 256):
+                bn *= 2
+        else:
+            bn = 256 if gated else 128
+    if splits > 1:
+        if gated or bias is not None:
+            raise KernelError("split-K takes no bias and no gate")
+        k_tiles = -(-K // 64)
+        per = -(-k_tiles // splits)
+        splits = -(-k_tiles // per)       # no empty split
+    if splits > 1:
+        out = torch.empty((splits, T, n_out), dtype=torch.float32, device=x.device) if out is None else out
+        ld_out, f32 = n_out, True
+    else:
+        odt = torch.float32 if out_f32 else torch.bfloat16
+        if out is None:
+            out = torch.empty((T, n_out), dtype=odt, device=x.device)
+        assert out.dtype == odt and out.stride(1) == 1
+        ld_out, f32 = out.stride(0), out_f32
+    _check(lib("gemm_tc").lab_gemm_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
+                                      int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
+    return out
+
+
+def _pick_splits(T: int, n_out: int, K: int) -> int:
+    """Split K when an output has too few tiles to keep the memory system busy (decode)."""
+    if T > 128:
+        return 1
+    tiles = -(-n_out // 128)
+    k_tiles = -(-K // 64)
+    if tiles >= SM_COUNT // 2 or k_tiles < 8:
+        return 1
+    return max(1, min(k_tiles // 4, SM_COUNT // tiles, 16))
+
+
 def linear(x, w, bias=None, out_f32=False, allow_partial=False):
     """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
     products [splits, tokens, out] that the following `add_rmsnorm` sums."""
-    return gemm_plain(x, w, bias, out_f32=out_f32)
+    if x.dtype == torch.float32 or _force_plain:
+        return gemm_plain(x, w, bias, out_f32=out_f32)
+    splits = _pick_splits(x.shape[0], w.shape[0], x.shape[1]) if (allow_partial and bias is None) else 1
+    return gemm_tc(x, w, bias, out_f32=out_f32, splits=splits)
 
 
 def linear_gated(x, w_gate_up):
     """silu(x @ wg.T) * (x @ wu.T) with w_gate_up = [wg; wu]."""
-    return gemm_plain(x, w_gate_up, None, gated=True)
+    if x.dtype == torch.float32 or _force_plain:
+        return gemm_plain(x, w_gate_up, None, gated=True)
+    return gemm_tc(x, w_gate_up, None, gated=True)
 
 
 def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale):
