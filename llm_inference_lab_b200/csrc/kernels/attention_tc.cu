@@ -1,0 +1,509 @@
+// Attention over the paged cache in bfloat16 on tensor cores, built for one head size
+// (-DLAB_HEAD_DIM=d, a multiple of 16 up to 128): a causal prefill kernel for requests
+// that bring several tokens, and a split-KV decode kernel (plus merge) for requests that
+// bring one.  Both walk a request's block table, so keys and values may lie on any pages.
+//
+//   scores  s_j = (q . k_j) / sqrt(d) for keys j <= query position (and within the window)
+//   softmax online in 32-bit (running max, sum and accumulator), p rounded to bfloat16
+//           before the product with V, o = acc / sum rounded once
+//   split-KV: each split leaves (acc, max, sum); merged as sum_s w_s acc_s / sum_s w_s sum_s
+//           with w_s = exp(max_s - max)
+// as the reference's tensor-core attention does (rust/engine/src/runner/model/qwen2/
+// kernels.rs:946-1124 tile loop, 1134-1256 grouped decode, 1295-1452 prefill, 898-942 merge).
+//
+// The products run on mma.sync.m16n8k16 (bf16 in, f32 out): the score and PV products of a
+// head of 64 are small next to the matrix products of the layer, and the kernels are bound
+// by the softmax arithmetic (prefill) and by reading the cache (decode).
+// Shared-memory rows are padded by 16 bytes, which keeps ldmatrix free of bank conflicts
+// for every head size that is a multiple of 16.
+#include "common.cuh"
+
+#ifndef LAB_HEAD_DIM
+#error "build with -DLAB_HEAD_DIM=<head size>"
+#endif
+
+namespace {
+
+constexpr int D = LAB_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 128, "head size must be a multiple of 16 up to 128");
+constexpr int ROW_BYTES = D * 2 + 16;  // padded shared-memory row
+constexpr int CPR = D / 8;             // 16-byte chunks per row
+constexpr int KSTEPS = D / 16;         // k-steps of q . k
+constexpr int DTILES = D / 8;          // 8-wide column tiles of the output
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Where key `j` of a request lies: element offset of its row in the cache, or -1.
+__device__ __forceinline__ long long key_offset(const int* __restrict__ bt, int j, int kvh, int n_kv, int page_size,
+                                                int num_pages) {
+  const int blk = j / page_size;
+  const int page = bt[blk];
+  if (page < 0) return -1;
+  if (page >= num_pages) {
+    lab_set_error(LAB_ERR_PAGE_RANGE);
+    return -1;
+  }
+  return (((long long)page * n_kv + kvh) * page_size + (j - blk * page_size)) * D;
+}
+
+// One tile of BN keys for 16 query rows held by a warp: scores, masked online softmax, PV.
+//   qf: the rows' q fragments; ks/vs: shared-memory tiles [BN][ROW_BYTES];
+//   rows of this thread: lane/4 (index 0) and lane/4 + 8 (index 1); a key j is visible to row i
+//   iff lo[i] <= j <= hi[i].  m, l, o carry the running max (log2 units), sum and accumulator.
+template <int BN>
+__device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint32_t ks, uint32_t vs,
+                                          float (&o)[DTILES][4], float (&m)[2], float (&l)[2], int key0,
+                                          const int (&lo)[2], const int (&hi)[2], float scale_log2, int lane) {
+  float s[BN / 8][4];
+#pragma unroll
+  for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+  // S = Q K^T
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+#pragma unroll
+    for (int jp = 0; jp < BN / 16; ++jp) {
+      uint32_t b[4];
+      const int key = jp * 16 + (lane & 7) + 8 * (lane >> 4);
+      const int dcol = k * 16 + 8 * ((lane >> 3) & 1);
+      ldmatrix_x4(b, ks + key * ROW_BYTES + dcol * 2);
+      mma_bf16(s[2 * jp], qf[k], b[0], b[1]);
+      mma_bf16(s[2 * jp + 1], qf[k], b[2], b[3]);
+    }
+  }
+  // mask, scale, running max
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + j * 8 + 2 * (lane & 3) + (e & 1);
+      const int r = e >> 1;
+      const bool ok = key >= lo[r] && key <= hi[r];
+      s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+      mx[r] = fmaxf(mx[r], s[j][e]);
+    }
+  float corr[2], base[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float m_new = fmaxf(m[r], mx[r]);
+    base[r] = (m_new == -INFINITY) ? 0.f : m_new;
+    corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - base[r]);
+    m[r] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+  uint32_t pf[BN / 16][4];
+#pragma unroll
+  for (int j = 0; j < BN / 8; ++j) {
+    float p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      p[e] = exp2f(s[j][e] - base[e >> 1]);  // exp2(-inf) = 0 for masked keys
+      sum[e >> 1] += p[e];
+    }
+    pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+    pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) l[r] = l[r] * corr[r] + sum[r];  // quad-reduced at the very end
+#pragma unroll
+  for (int t = 0; t < DTILES; ++t) {
+    o[t][0] *= corr[0];
+    o[t][1] *= corr[0];
+    o[t][2] *= corr[1];
+    o[t][3] *= corr[1];
+  }
+  // O += P V
+#pragma unroll
+  for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+    for (int tp = 0; tp < DTILES / 2; ++tp) {
+      uint32_t b[4];
+      const int key = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+      const int dcol = tp * 16 + 8 * (lane >> 4);
+      ldmatrix_x4_trans(b, vs + key * ROW_BYTES + dcol * 2);
+      mma_bf16(o[2 * tp], pf[kk], b[0], b[1]);
+      mma_bf16(o[2 * tp + 1], pf[kk], b[2], b[3]);
+    }
+  }
+}
+
+// Copies `rows` keys starting at key0 into a shared-memory tile; keys outside [0, kv_len) and
+// keys whose page was given back are filled with zeros (never read as data: masked).
+template <int ROWS, int NTHREADS>
+__device__ __forceinline__ void load_tile(uint32_t dst, const __nv_bfloat16* __restrict__ cache,
+                                          const int* __restrict__ bt, int key0, int first_key, int kv_len, int kvh,
+                                          int n_kv, int page_size, int num_pages, int tid) {
+#pragma unroll
+  for (int c = tid; c < ROWS * CPR; c += NTHREADS) {
+    const int row = c / CPR, col = c - row * CPR;
+    const int j = key0 + row;
+    long long off = -1;
+    if (j >= first_key && j < kv_len) off = key_offset(bt, j, kvh, n_kv, page_size, num_pages);
+    const __nv_bfloat16* src = cache + (off < 0 ? 0 : off) + col * 8;
+    cp_async16(dst + row * ROW_BYTES + col * 16, src, off >= 0);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Prefill: one CTA per (tile of 64 query rows, query head, request); 4 warps x 16 rows.
+// ----------------------------------------------------------------------------------------
+constexpr int PF_BM = 64, PF_BN = 64, PF_THREADS = 128;
+constexpr int PF_TILE_BYTES = PF_BN * ROW_BYTES;
+constexpr int PF_SMEM = PF_BM * ROW_BYTES + 4 * PF_TILE_BYTES;  // Q + 2 stages of (K, V)
+
+__global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
+    __nv_bfloat16* __restrict__ out, int out_stride, const __nv_bfloat16* __restrict__ q, int q_stride,
+    const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
+    const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ pos0_arr,
+    const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
+    float scale_log2, int min_q_len) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qs = q_start[b], ql = q_start[b + 1] - qs;
+  const int r0 = blockIdx.x * PF_BM;
+  if (ql < min_q_len || r0 >= ql) return;
+  const int kvh = h / (n_q / n_kv);
+  const int p0 = pos0_arr[b], kvl = kv_len_arr[b];
+  const int* bt = block_table + (size_t)b * max_blocks;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t q_s = smem_u32(smem);
+  const uint32_t kv_s = q_s + PF_BM * ROW_BYTES;
+
+  // Q tile -> shared memory (rows past the request's tokens are zeros)
+  for (int c = tid; c < PF_BM * CPR; c += PF_THREADS) {
+    const int row = c / CPR, col = c - row * CPR;
+    const bool ok = r0 + row < ql;
+    const __nv_bfloat16* src = q + (size_t)(qs + (ok ? r0 + row : 0)) * q_stride + (size_t)h * D + col * 8;
+    cp_async16(q_s + row * ROW_BYTES + col * 16, src, ok);
+  }
+  cp_async_commit();
+
+  const int last_row = min(r0 + PF_BM, ql) - 1;
+  const int hi_all = p0 + last_row;
+  const int lo_all = window > 0 ? max(0, p0 + r0 - window + 1) : 0;
+  const int t_first = lo_all / PF_BN, t_last = hi_all / PF_BN;
+
+  auto issue = [&](int t, int stage) {
+    const uint32_t kd = kv_s + stage * 2 * PF_TILE_BYTES;
+    load_tile<PF_BN, PF_THREADS>(kd, cache_k, bt, t * PF_BN, lo_all, kvl, kvh, n_kv, page_size, num_pages, tid);
+    load_tile<PF_BN, PF_THREADS>(kd + PF_TILE_BYTES, cache_v, bt, t * PF_BN, lo_all, kvl, kvh, n_kv, page_size,
+                                 num_pages, tid);
+    cp_async_commit();
+  };
+  issue(t_first, 0);
+
+  int lo[2], hi[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = r0 + warp * 16 + (lane >> 2) + 8 * r;
+    const int pos = p0 + row;
+    hi[r] = row < ql ? pos : -1;
+    lo[r] = window > 0 ? max(0, pos - window + 1) : 0;
+  }
+  float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int t = 0; t < DTILES; ++t)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[t][e] = 0.f;
+
+  uint32_t qf[KSTEPS][4];
+  bool have_q = false;
+  for (int t = t_first; t <= t_last; ++t) {
+    const int stage = (t - t_first) & 1;
+    if (t + 1 <= t_last) {
+      issue(t + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (!have_q) {
+#pragma unroll
+      for (int k = 0; k < KSTEPS; ++k) {
+        const int row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int dcol = k * 16 + 8 * (lane >> 4);
+        ldmatrix_x4(qf[k], q_s + row * ROW_BYTES + dcol * 2);
+      }
+      have_q = true;
+    }
+    // A warp whose rows all lie before this tile's first key has nothing to do in it.
+    const int warp_hi = p0 + min(r0 + warp * 16 + 15, ql - 1);
+    if (t * PF_BN <= warp_hi) {
+      const uint32_t kd = kv_s + stage * 2 * PF_TILE_BYTES;
+      tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane);
+    }
+    __syncthreads();  // the stage is refilled by the next iteration's prefetch
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    const int row = r0 + warp * 16 + (lane >> 2) + 8 * r;
+    if (row >= ql) continue;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    __nv_bfloat16* dst = out + (size_t)(qs + row) * out_stride + (size_t)h * D + 2 * (lane & 3);
+#pragma unroll
+    for (int t = 0; t < DTILES; ++t)
+      *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16(o[t][2 * r] * inv, o[t][2 * r + 1] * inv);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Decode: one CTA per (split of the keys, kv head x tile of 16 query heads of its group,
+// request with exactly one new token).  Each of the 4 warps streams its own 32-key tiles
+// through a private ring of shared-memory stages; the warps' softmax states are merged at
+// the end.  With several splits the CTA leaves (acc, max, sum) in scratch for the merge kernel.
+// ----------------------------------------------------------------------------------------
+constexpr int DC_BN = 32, DC_THREADS = 128, DC_WARPS = 4;
+constexpr int DC_STAGES = D <= 64 ? 3 : 2;
+constexpr int DC_TILE_BYTES = DC_BN * ROW_BYTES;
+constexpr int DC_WARP_BYTES = DC_STAGES * 2 * DC_TILE_BYTES;
+constexpr int DC_MERGE_BYTES = DC_WARPS * 16 * (D + 2) * 4;
+constexpr int DC_SMEM = DC_WARPS * DC_WARP_BYTES > DC_MERGE_BYTES ? DC_WARPS * DC_WARP_BYTES : DC_MERGE_BYTES;
+
+__global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
+    __nv_bfloat16* __restrict__ out, int out_stride, const __nv_bfloat16* __restrict__ q, int q_stride,
+    const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
+    const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ block_table,
+    int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window, float scale_log2, int splits,
+    float* __restrict__ part_acc, float* __restrict__ part_ml) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int b = blockIdx.z;
+  const int qs = q_start[b];
+  if (q_start[b + 1] - qs != 1) return;
+  const int group = n_q / n_kv, m_tiles = (group + 15) / 16;
+  const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y - kvh * m_tiles;
+  const int split = blockIdx.x;
+  const int kvl = kv_len_arr[b];
+  const int first = window > 0 ? max(0, kvl - window) : 0;
+  const int* bt = block_table + (size_t)b * max_blocks;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head0 = kvh * group + mt * 16;           // first query head of this CTA
+  const int n_heads = min(16, group - mt * 16);      // valid rows
+
+  // keys of this split: whole 32-key tiles counted from the 32-aligned start
+  const int start = (first / DC_BN) * DC_BN;
+  const int total_tiles = kvl > start ? (kvl - start + DC_BN - 1) / DC_BN : 0;
+  const int tiles_per_split = (total_tiles + splits - 1) / splits;
+  const int tile_lo = split * tiles_per_split;
+  const int tile_hi = min(total_tiles, tile_lo + tiles_per_split);
+
+  // q fragments straight from global memory: row r of the A operand is query head head0 + r
+  uint32_t qf[KSTEPS][4];
+  {
+    const __nv_bfloat16* qrow = q + (size_t)qs * q_stride;
+    const int ra = lane >> 2, rb = ra + 8;
+#pragma unroll
+    for (int k = 0; k < KSTEPS; ++k) {
+      const int c = k * 16 + 2 * (lane & 3);
+      const uint32_t* pa = reinterpret_cast<const uint32_t*>(qrow + (size_t)(head0 + ra) * D + c);
+      const uint32_t* pb = reinterpret_cast<const uint32_t*>(qrow + (size_t)(head0 + rb) * D + c);
+      qf[k][0] = ra < n_heads ? pa[0] : 0u;
+      qf[k][1] = rb < n_heads ? pb[0] : 0u;
+      qf[k][2] = ra < n_heads ? pa[4] : 0u;
+      qf[k][3] = rb < n_heads ? pb[4] : 0u;
+    }
+  }
+  float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int t = 0; t < DTILES; ++t)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[t][e] = 0.f;
+  const int lo[2] = {first, first}, hi[2] = {kvl - 1, kvl - 1};
+
+  const uint32_t ring = smem_u32(smem) + warp * DC_WARP_BYTES;
+  auto issue = [&](int t, int stage) {
+    const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
+    const int key0 = start + t * DC_BN;
+    load_tile<DC_BN, 32>(kd, cache_k, bt, key0, first, kvl, kvh, n_kv, page_size, num_pages, lane);
+    load_tile<DC_BN, 32>(kd + DC_TILE_BYTES, cache_v, bt, key0, first, kvl, kvh, n_kv, page_size, num_pages, lane);
+  };
+  // this warp's tiles: tile_lo + warp, + DC_WARPS, ...
+  int t_issue = tile_lo + warp;
+#pragma unroll
+  for (int s = 0; s < DC_STAGES - 1; ++s) {
+    if (t_issue < tile_hi) issue(t_issue, s);
+    cp_async_commit();
+    t_issue += DC_WARPS;
+  }
+  int stage = 0;
+  for (int t = tile_lo + warp; t < tile_hi; t += DC_WARPS) {
+    // prefetch the tile DC_STAGES - 1 ahead into the stage consumed last iteration
+    const int pre_stage = (stage + DC_STAGES - 1) % DC_STAGES;
+    if (t_issue < tile_hi) issue(t_issue, pre_stage);
+    cp_async_commit();
+    t_issue += DC_WARPS;
+    cp_async_wait<DC_STAGES - 1>();
+    __syncwarp();
+    const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
+    tile_step<DC_BN>(qf, kd, kd + DC_TILE_BYTES, o, m, l, start + t * DC_BN, lo, hi, scale_log2, lane);
+    __syncwarp();
+    stage = (stage + 1) % DC_STAGES;
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  __syncthreads();  // every warp is done with its ring: the memory is reused for the merge
+  float* mg = reinterpret_cast<float*>(smem) + warp * 16 * (D + 2);
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = (lane >> 2) + 8 * r;
+#pragma unroll
+    for (int t = 0; t < DTILES; ++t) {
+      mg[row * (D + 2) + t * 8 + 2 * (lane & 3)] = o[t][2 * r];
+      mg[row * (D + 2) + t * 8 + 2 * (lane & 3) + 1] = o[t][2 * r + 1];
+    }
+    if ((lane & 3) == 0) {
+      mg[row * (D + 2) + D] = m[r];
+      mg[row * (D + 2) + D + 1] = l[r];
+    }
+  }
+  __syncthreads();
+  const float* all = reinterpret_cast<const float*>(smem);
+  for (int i = tid; i < n_heads * D; i += DC_THREADS) {
+    const int row = i / D, dim = i - row * D;
+    float big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) big = fmaxf(big, all[(w * 16 + row) * (D + 2) + D]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) {
+      const float mw = all[(w * 16 + row) * (D + 2) + D];
+      const float wt = (mw == -INFINITY) ? 0.f : exp2f(mw - big);
+      num += wt * all[(w * 16 + row) * (D + 2) + dim];
+      den += wt * all[(w * 16 + row) * (D + 2) + D + 1];
+    }
+    const int head = head0 + row;
+    if (splits == 1) {
+      out[(size_t)qs * out_stride + (size_t)head * D + dim] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else {
+      const size_t slot = ((size_t)b * n_q + head) * splits + split;
+      part_acc[slot * D + dim] = num;
+      if (dim == 0) {
+        part_ml[slot * 2] = big;
+        part_ml[slot * 2 + 1] = den;
+      }
+    }
+  }
+}
+
+// Merge of the splits: one block per (request, query head), D threads.
+__global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, int out_stride,
+                                       const int* __restrict__ q_start, int n_q, int splits,
+                                       const float* __restrict__ part_acc, const float* __restrict__ part_ml) {
+  const int b = blockIdx.x, head = blockIdx.y, dim = threadIdx.x;
+  const int qs = q_start[b];
+  if (q_start[b + 1] - qs != 1) return;
+  const size_t slot0 = ((size_t)b * n_q + head) * splits;
+  float big = -INFINITY;
+  for (int s = 0; s < splits; ++s) big = fmaxf(big, part_ml[(slot0 + s) * 2]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(slot0 + s) * 2];
+    const float wt = (ms == -INFINITY) ? 0.f : exp2f(ms - big);
+    num += wt * part_acc[(slot0 + s) * D + dim];
+    den += wt * part_ml[(slot0 + s) * 2 + 1];
+  }
+  out[(size_t)qs * out_stride + (size_t)head * D + dim] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+}
+
+}  // namespace
+
+LAB_EXPORT int lab_attention_head_dim() { return D; }
+
+// Scratch the decode kernel needs with `splits` > 1: floats for part_acc and part_ml.
+LAB_EXPORT long long lab_attention_decode_scratch_floats(int requests, int n_q, int splits) {
+  return splits > 1 ? (long long)requests * n_q * splits * (D + 2) : 0;
+}
+
+LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
+                                     const void* cache_v, const int* q_start, const int* kv_len, const int* pos0,
+                                     const int* block_table, int max_blocks, int requests, int max_q_len, int n_q,
+                                     int n_kv, int page_size, int num_pages, int window, float scale, int min_q_len,
+                                     cudaStream_t stream) {
+  if (requests <= 0 || max_q_len <= 0) return 0;
+  if (n_q % n_kv || q_stride % 8 || (((uintptr_t)q) & 15)) return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_q_len + PF_BM - 1) / PF_BM, n_q, requests);
+  attention_prefill_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(
+      (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache_k,
+      (const __nv_bfloat16*)cache_v, q_start, kv_len, pos0, block_table, max_blocks, n_q, n_kv, page_size, num_pages,
+      window, scale * LOG2E, min_q_len);
+  LAB_LAUNCH_CHECK();
+}
+
+// scratch: lab_attention_decode_scratch_floats(...) floats when splits > 1 (may be null otherwise).
+LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
+                                    const void* cache_v, const int* q_start, const int* kv_len,
+                                    const int* block_table, int max_blocks, int requests, int n_q, int n_kv,
+                                    int page_size, int num_pages, int window, float scale, int splits, float* scratch,
+                                    cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  if (n_q % n_kv || splits < 1 || (splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int group = n_q / n_kv, m_tiles = (group + 15) / 16;
+  float* part_acc = scratch;
+  float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
+  dim3 grid(splits, n_kv * m_tiles, requests);
+  attention_decode_kernel<<<grid, DC_THREADS, DC_SMEM, stream>>>(
+      (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache_k,
+      (const __nv_bfloat16*)cache_v, q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
+      scale * LOG2E, splits, part_acc, part_ml);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (splits > 1) {
+    attention_merge_kernel<<<dim3(requests, n_q), D, 0, stream>>>((__nv_bfloat16*)out, out_stride, q_start, n_q,
+                                                                   splits, part_acc, part_ml);
+  }
+  LAB_LAUNCH_CHECK();
+}

@@ -287,6 +287,58 @@ def linear_gated(x, w_gate_up):
     return gemm_tc(x, w_gate_up, None, gated=True)
 
 
+def attention_tc_supported(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int) -> int:
+    """How many ways the keys of a decoding request are split across CTAs: enough CTAs to
+    fill the GPU, but at least 256 keys each (the reference splits 1..16 ways,
+    rust/engine/src/runner/model/qwen2/engine.rs:1597-1617)."""
+    ctas = max(1, n_decode * n_kv * (-(-group // 16)))
+    want = max(1, (2 * SM_COUNT) // ctas)
+    return int(max(1, min(want, -(-max_kv_len // 256), 32)))
+
+
+def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requests, q_lens, max_kv_len,
+                 n_q, n_kv, head_dim, window, scale, out=None, splits=None, scratch=None):
+    """Tensor-core attention: the prefill kernel serves requests with several new tokens,
+    the split-KV decode kernel those with one."""
+    _on_gpu(q, cache_k, cache_v, q_start, kv_len, pos0, block_table)
+    if q.dtype != torch.bfloat16 or not attention_tc_supported(head_dim):
+        raise KernelError(f"attention_tc: bfloat16 and a head size multiple of 16 up to 128, got {q.dtype}, {head_dim}")
+    tokens = q.shape[0]
+    if out is None:
+        out = torch.empty((tokens, n_q * head_dim), dtype=q.dtype, device=q.device)
+    num_pages, kvh, page_size, d = cache_k.shape
+    assert kvh == n_kv and d == head_dim and q.stride(1) == 1 and q.stride(0) % 8 == 0
+    assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.shape[0] >= n_requests
+    L = lib("attention_tc", {"LAB_HEAD_DIM": head_dim})
+    max_q = max(q_lens)
+    n_decode = sum(1 for n in q_lens if n == 1)
+    if max_q > 1:
+        _check(L.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
+                                       _ptr(q_start), _ptr(kv_len), _ptr(pos0), _ptr(block_table),
+                                       block_table.shape[1], n_requests, max_q, n_q, n_kv, page_size, num_pages,
+                                       window, ctypes.c_float(scale), 2, _stream()), "attention_prefill")
+    if n_decode:
+        if splits is None:
+            span = min(max_kv_len, window) if window else max_kv_len
+            splits = decode_splits(n_decode, n_kv, n_q // n_kv, span)
+        if splits > 1:
+            need = n_requests * n_q * splits * (head_dim + 2)
+            if scratch is None or scratch.numel() < need:
+                scratch = torch.empty((need,), dtype=torch.float32, device=q.device)
+        _check(L.lab_attention_decode(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
+                                      _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1],
+                                      n_requests, n_q, n_kv, page_size, num_pages, window, ctypes.c_float(scale),
+                                      splits, _ptr(scratch if splits > 1 else None), _stream()), "attention_decode")
+    return out
+
+
 def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale):
+    if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim):
+        return attention_tc(q, cache_k, cache_v, ctx.q_start, ctx.kv_len, ctx.pos0, group.block_table,
+                            ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale)
     return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
                            window, scale)

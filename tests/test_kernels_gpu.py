@@ -1,0 +1,380 @@
+"""Each CUDA kernel alone against a plain reference of the same operation, at sizes other
+than the engine's tiny or benchmark configurations."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain_qwen2 import plain_rms_norm, plain_rope, plain_sample, plain_silu
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def ops():
+    from llm_inference_lab_b200.kernels import ops as _ops
+    return _ops
+
+
+def rel_err(got, ref):
+    got = got.detach().double().cpu().numpy() if torch.is_tensor(got) else np.asarray(got, dtype=np.float64)
+    ref = ref.detach().double().cpu().numpy() if torch.is_tensor(ref) else np.asarray(ref, dtype=np.float64)
+    assert np.isfinite(got).all(), "non-finite output"
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1e-2}
+
+
+# ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [24, 100, 896])
+def test_embed(dtype, hidden):
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(77, hidden, generator=g).to(dtype).to(DEV)
+    ids = torch.tensor([0, 76, 5, 5, 33, 200, -3], dtype=torch.int32, device=DEV)   # out of range ids are clamped
+    out = ops().embed(ids, table)
+    want = table[ids.long().clamp(0, 76)]
+    assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,eps", [(40, 1e-6), (200, 1e-5), (1536, 3e-6)])
+def test_add_rmsnorm(dtype, hidden, eps):
+    g = torch.Generator().manual_seed(2)
+    T = 13
+    x = (torch.randn(T, hidden, generator=g) * 3).to(dtype)
+    delta = torch.randn(T, hidden, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype)
+    # plain norm
+    xd = x.clone().to(DEV)
+    y = ops().add_rmsnorm(xd, w.to(DEV), eps)
+    assert torch.equal(xd.cpu(), x), "x must stay as it is without a delta"
+    assert rel_err(y, plain_rms_norm(x.double().numpy(), w.double().numpy(), eps)) < TOL[dtype]
+    # with the residual add: x is updated in place with the rounded sum
+    xd = x.clone().to(DEV)
+    y = ops().add_rmsnorm(xd, w.to(DEV), eps, delta=delta.to(DEV))
+    r = (x.float() + delta.float()).to(dtype)
+    assert torch.equal(xd.cpu(), r)
+    assert rel_err(y, plain_rms_norm(r.double().numpy(), w.double().numpy(), eps)) < TOL[dtype]
+    # with split-K partials and a gather of rows: x untouched
+    part = torch.randn(3, T, hidden, generator=g)
+    rows = torch.tensor([12, 0, 7, 7], dtype=torch.int32)
+    xd = x.clone().to(DEV)
+    y = ops().add_rmsnorm(xd, w.to(DEV), eps, partial=part.to(DEV), rows=rows.to(DEV))
+    assert torch.equal(xd.cpu(), x)
+    r = (x.float() + part.sum(0)).to(dtype)[rows.long()]
+    assert rel_err(y, plain_rms_norm(r.double().numpy(), w.double().numpy(), eps)) < TOL[dtype] * 2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,d,rot,theta", [(3, 1, 16, 16, 1e4), (5, 5, 48, 48, 5e4), (8, 2, 64, 32, 1e6),
+                                                 (2, 2, 128, 128, 1e6)])
+def test_rope_kv_write(dtype, n_q, n_kv, d, rot, theta):
+    g = torch.Generator().manual_seed(3)
+    T, ps, pages = 11, 4, 9
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * d, generator=g).to(dtype)
+    pos = torch.tensor([0, 1, 2, 3, 500, 501, 77, 4095, 9, 10, 11], dtype=torch.int32)
+    slots = torch.tensor([35, 2, 7, 1, 0, 20, 21, 22, 23, 12, 30], dtype=torch.int32)
+    inv = torch.from_numpy(np.power(theta, -2.0 * np.arange(rot // 2) / rot).astype(np.float32))
+    ck = torch.full((pages, n_kv, ps, d), float("nan"), dtype=dtype, device=DEV)
+    cv = torch.full((pages, n_kv, ps, d), float("nan"), dtype=dtype, device=DEV)
+    dq = qkv.clone().to(DEV)
+    ops().rope_kv_write(dq, pos.to(DEV), inv.to(DEV), rot, slots.to(DEV), ck, cv, n_q, n_kv, d)
+    q = qkv[:, : n_q * d].double().reshape(T, n_q, d).numpy()
+    k = qkv[:, n_q * d: (n_q + n_kv) * d].double().reshape(T, n_kv, d).numpy()
+    v = qkv[:, (n_q + n_kv) * d:].reshape(T, n_kv, d)
+
+    def rotated(x):
+        out = x.copy()
+        out[..., :rot] = plain_rope(x[..., :rot], pos.numpy(), theta)
+        return out
+
+    tol = 3e-6 if dtype == torch.float32 else 2e-2
+    assert rel_err(dq[:, : n_q * d].reshape(T, n_q, d), rotated(q)) < tol
+    page, off = slots.long() // ps, slots.long() % ps
+    assert rel_err(ck[page, :, off, :], rotated(k)) < tol
+    assert torch.equal(cv[page, :, off, :].cpu(), v)
+    # nothing else was written
+    written = torch.zeros(pages, ps, dtype=torch.bool)
+    written[page, off] = True
+    untouched = (~written)[:, None, :, None].expand(pages, n_kv, ps, d)
+    assert torch.isnan(ck.float().cpu()[untouched]).all() and torch.isnan(cv.float().cpu()[untouched]).all()
+    # v columns of the activation stay as they were; a read-only call writes no cache
+    assert torch.equal(dq[:, (n_q + n_kv) * d:].cpu(), qkv[:, (n_q + n_kv) * d:])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 5, 3), (7, 130, 65), (70, 33, 200), (129, 64, 48)])
+def test_gemm_plain_exact(dtype, M, N, K):
+    # Small integers over a power of two: every product and partial sum is exact in 32-bit,
+    # so the result must be equal whatever the order (the reference's own trick,
+    # rust/engine/src/runner/model/qwen2/engine.rs:3704).
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randint(-8, 9, (M, K), generator=g).float() / 8).to(dtype)
+    w = (torch.randint(-8, 9, (N, K), generator=g).float() / 4).to(dtype)
+    b = (torch.randint(-8, 9, (N,), generator=g).float() / 2).to(dtype)
+    out = ops().gemm_plain(x.to(DEV), w.to(DEV), b.to(DEV), out_f32=True)
+    want = x.double() @ w.double().T + b.double()
+    assert torch.equal(out.double().cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_plain_gated(dtype):
+    g = torch.Generator().manual_seed(5)
+    M, I, K = 19, 72, 40
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = (torch.randn(2 * I, K, generator=g) * 0.3).to(dtype)
+    out = ops().gemm_plain(x.to(DEV), w.to(DEV), gated=True)
+    gu = x.double() @ w.double().T
+    want = plain_silu(gu[:, :I].numpy()) * gu[:, I:].numpy()
+    assert rel_err(out, want) < (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+GEMM_TC_SHAPES = [
+    # tokens, out, K, gated, bias, swap, bn, splits
+    (128, 128, 64, False, False, False, 128, 1),
+    (16, 128, 64, False, False, True, 16, 1),
+    (1, 40, 8, False, True, None, None, 1),
+    (3, 264, 104, False, True, None, None, 1),
+    (50, 1000, 200, False, True, True, 64, 1),
+    (200, 896, 896, False, False, True, 256, 1),
+    (130, 72, 136, False, True, False, 64, 1),
+    (300, 504, 200, False, True, False, 128, 1),
+    (513, 300, 320, False, False, False, 256, 1),
+    (5, 200, 104, True, False, None, None, 1),
+    (333, 200, 104, True, False, False, 64, 1),
+    (260, 520, 72, True, False, False, 256, 1),
+    (9, 136, 1000, False, False, None, None, 5),
+    (70, 130, 4864, False, False, None, None, 16),
+]
+
+
+@pytest.mark.parametrize("T,N,K,gated,bias,swap,bn,splits", GEMM_TC_SHAPES)
+def test_gemm_tc_exact(T, N, K, gated, bias, swap, bn, splits):
+    """tcgen05 product with exactly representable inputs: equal to the 64-bit product."""
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randint(-4, 5, (T, K), generator=g).float() / 4).bfloat16()
+    w = (torch.randint(-4, 5, (N * (2 if gated else 1), K), generator=g).float() / 8).bfloat16()
+    b = (torch.randint(-8, 9, (N,), generator=g).float() / 2).bfloat16() if bias else None
+    out = ops().gemm_tc(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), gated=gated,
+                        out_f32=not gated, swap=swap, bn=bn, splits=splits)
+    ops().take_device_errors()
+    ref = x.double() @ w.double().T
+    if splits > 1:
+        assert out.shape[1:] == (T, N) and out.dtype == torch.float32
+        assert torch.equal(out.double().sum(0).cpu(), ref)
+        return
+    if gated:
+        gq, uq = ref[:, :N].bfloat16().double(), ref[:, N:].bfloat16().double()
+        want = torch.from_numpy(plain_silu(gq.numpy())).bfloat16().double() * uq
+        assert rel_err(out, want) < 1e-2
+        return
+    if bias:
+        ref = ref + b.double()
+    assert torch.equal(out.double().cpu(), ref)
+
+
+def test_gemm_tc_guards():
+    """Outputs beyond the valid rows and columns are not touched (NaN-prefilled buffer)."""
+    g = torch.Generator().manual_seed(7)
+    T, N, K = 37, 100, 72
+    x = torch.randn(T, K, generator=g).bfloat16().to(DEV)
+    w = torch.randn(N, K, generator=g).bfloat16().to(DEV)
+    for swap, bn in ((False, 128), (True, 64)):
+        buf = torch.full((T + 5, N + 12), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops().gemm_tc(x, w, swap=swap, bn=bn, out=buf[:T, :N])
+        assert torch.isnan(buf[T:].float()).all() and torch.isnan(buf[:, N:].float()).all()
+        assert rel_err(buf[:T, :N], x.double() @ w.double().T) < 1e-2
+    with pytest.raises(Exception):
+        ops().gemm_tc(x[:, :70], w[:, :70].contiguous())   # K is not a multiple of 8: refused, not wrong
+
+
+# ----------------------------------------------------------------------------------------
+# Attention over pages
+# ----------------------------------------------------------------------------------------
+
+def build_paged(rng, requests, n_kv, d, ps, dtype, spare_pages=3):
+    """Scatter each request's keys/values over shuffled pages; unused slots hold NaN."""
+    blocks = [-(-kv // ps) for kv, _ in requests]
+    n_pages = sum(blocks) + spare_pages
+    perm = rng.permutation(n_pages)
+    ck = torch.full((n_pages, n_kv, ps, d), float("nan"), dtype=dtype)
+    cv = torch.full((n_pages, n_kv, ps, d), float("nan"), dtype=dtype)
+    width = max(blocks) + 2
+    bt = np.full((len(requests), width), -1, dtype=np.int32)
+    ks, vs = [], []
+    at = 0
+    for b, (kv, _) in enumerate(requests):
+        k = torch.from_numpy(rng.standard_normal((kv, n_kv, d)).astype(np.float32)).to(dtype)
+        v = torch.from_numpy(rng.standard_normal((kv, n_kv, d)).astype(np.float32)).to(dtype)
+        ks.append(k)
+        vs.append(v)
+        for blk in range(blocks[b]):
+            page = int(perm[at])
+            at += 1
+            bt[b, blk] = page
+            n = min(ps, kv - blk * ps)
+            ck[page, :, :n, :] = k[blk * ps: blk * ps + n].transpose(0, 1)
+            cv[page, :, :n, :] = v[blk * ps: blk * ps + n].transpose(0, 1)
+    return ck, cv, bt, ks, vs
+
+
+def ref_attention(q, k, v, pos0, window, scale):
+    """q: [ql, n_q, d] rows at positions pos0..; k, v: [kv, n_kv, d] (float64 numpy)."""
+    ql, n_q, d = q.shape
+    n_kv = k.shape[1]
+    out = np.zeros_like(q)
+    for r in range(ql):
+        p = pos0 + r
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(n_q):
+            g = h // (n_q // n_kv)
+            s = (k[lo:p + 1, g, :] @ q[r, h, :]) * scale
+            w = np.exp(s - s.max())
+            out[r, h] = (w / w.sum()) @ v[lo:p + 1, g, :]
+    return out
+
+
+def run_attention(kind, requests, n_q, n_kv, d, ps, window, dtype, seed=0, splits=None, tweak=None):
+    """requests: list of (kv_len after the step, q_len).  Returns (got, want) lists per request."""
+    rng = np.random.default_rng(seed)
+    ck, cv, bt, ks, vs = build_paged(rng, requests, n_kv, d, ps, dtype)
+    qs = [torch.from_numpy(rng.standard_normal((ql, n_q, d)).astype(np.float32)).to(dtype) for _, ql in requests]
+    if tweak:
+        tweak(qs, ks, vs, ck, cv, bt)
+    T = sum(ql for _, ql in requests)
+    q_all = torch.cat([q.reshape(q.shape[0], -1) for q in qs], 0)
+    row_req = np.concatenate([np.full(ql, b) for b, (_, ql) in enumerate(requests)]).astype(np.int32)
+    row_pos = np.concatenate([np.arange(kv - ql, kv) for kv, ql in requests]).astype(np.int32)
+    q_start = np.concatenate([[0], np.cumsum([ql for _, ql in requests])]).astype(np.int32)
+    kv_len = np.array([kv for kv, _ in requests], dtype=np.int32)
+    pos0 = np.array([kv - ql for kv, ql in requests], dtype=np.int32)
+    scale = 1.0 / math.sqrt(d)
+    dev = lambda a: (a if torch.is_tensor(a) else torch.from_numpy(a)).to(DEV)  # noqa: E731
+    if kind == "plain":
+        out = ops().attention_plain(dev(q_all), dev(ck), dev(cv), dev(row_req), dev(row_pos), dev(bt), n_q, n_kv, d,
+                                    window, scale)
+    else:
+        out = ops().attention_tc(dev(q_all), dev(ck), dev(cv), dev(q_start), dev(kv_len), dev(pos0), dev(bt),
+                                 len(requests), [ql for _, ql in requests], int(kv_len.max()), n_q, n_kv, d, window,
+                                 scale, splits=splits)
+    ops().take_device_errors()
+    assert out.shape == (T, n_q * d)
+    got, want = [], []
+    for b, (kv, ql) in enumerate(requests):
+        got.append(out[q_start[b]: q_start[b + 1]].reshape(ql, n_q, d))
+        want.append(ref_attention(qs[b].double().numpy(), ks[b].double().numpy(), vs[b].double().numpy(), kv - ql,
+                                  window, scale))
+    return got, want
+
+
+ATT_CASES = [
+    # n_q, n_kv, d, page, window, requests [(kv_len, q_len)]
+    (4, 2, 16, 4, 0, [(5, 5), (9, 9), (17, 17)]),
+    (6, 1, 32, 16, 0, [(1, 1), (7, 7), (33, 33), (70, 70)]),
+    (14, 2, 64, 16, 0, [(300, 1), (301, 2), (64, 64), (257, 130), (1, 1)]),
+    (3, 3, 48, 8, 20, [(100, 1), (100, 37), (19, 19), (20, 1), (21, 1), (45, 3)]),
+    (8, 2, 128, 32, 0, [(129, 129), (1000, 1), (96, 31)]),
+    (5, 5, 80, 4, 7, [(30, 30), (8, 1), (7, 1), (6, 1)]),
+    (32, 1, 64, 16, 0, [(200, 1), (90, 4)]),
+]
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,ps,window,requests", ATT_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_plain(dtype, n_q, n_kv, d, ps, window, requests):
+    got, want = run_attention("plain", requests, n_q, n_kv, d, ps, window, dtype)
+    for g, w in zip(got, want):
+        assert rel_err(g, w) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,ps,window,requests", ATT_CASES)
+def test_attention_tc(n_q, n_kv, d, ps, window, requests):
+    got, want = run_attention("tc", requests, n_q, n_kv, d, ps, window, torch.bfloat16)
+    for g, w in zip(got, want):
+        assert rel_err(g, w) < 2e-2
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
+def test_attention_decode_splits(splits):
+    """Every way of splitting the keys gives the same result, also with splits that get no keys."""
+    requests = [(777, 1), (31, 1), (32, 1), (33, 1), (1, 1), (500, 1)]
+    got, want = run_attention("tc", requests, 14, 2, 64, 16, 0, torch.bfloat16, splits=splits)
+    for g, w in zip(got, want):
+        assert rel_err(g, w) < 2e-2
+
+
+@pytest.mark.parametrize("kind,dtype", [("plain", torch.float32), ("plain", torch.bfloat16), ("tc", torch.bfloat16)])
+@pytest.mark.parametrize("needle", ["first", "page_end", "page_start", "last", "window_first", "window_out"])
+def test_attention_needle(kind, dtype, needle):
+    """One far key among hundreds carries all the weight: its score stands far above the
+    rest and its value is unlike any other, so a key that is skipped, read from the wrong
+    page or let in from outside the window changes the output by its full size."""
+    n_q, n_kv, d, ps = 4, 2, 64, 16
+    window = 100 if needle.startswith("window") else 0
+    kv, ql = 411, 3                      # rows at positions 408, 409, 410
+    where = {"first": 0, "page_end": 16 * 9 - 1, "page_start": 16 * 9, "last": 410,
+             "window_first": 408 - window + 1, "window_out": 408 - window}[needle]
+
+    def tweak(qs, ks, vs, ck, cv, bt):
+        for b in range(len(qs)):
+            q, k, v = qs[b], ks[b], vs[b]
+            for g in range(n_kv):
+                direction = q[0, g * (n_q // n_kv)].float()
+                k[where, g] = (direction / direction.norm() * 40.0).to(k.dtype)
+                v[where, g] = 5.0
+            blk, off = where // ps, where % ps
+            ck[bt[b, blk], :, off, :] = k[where]
+            cv[bt[b, blk], :, off, :] = v[where]
+
+    # the tensor-core path is tried with a portion of three rows and with a single decoded row
+    requests = [(kv, ql), (kv, 1)] if kind == "tc" else [(kv, ql)]
+    got, want = run_attention(kind, requests, n_q, n_kv, d, ps, window, dtype, seed=11, tweak=tweak)
+    for g, w in zip(got, want):
+        assert rel_err(g, w) < (1e-5 if dtype == torch.float32 else 2e-2)
+    row0 = np.abs(want[0][0, 0]).mean()
+    if needle == "window_out":
+        assert row0 < 2.0, "the needle lies just outside the window of the first row"
+    elif needle != "last":
+        assert row0 > 4.0, "the needle must dominate the first row"
+
+
+# ----------------------------------------------------------------------------------------
+# Sampling
+# ----------------------------------------------------------------------------------------
+
+def test_sample_greedy_ties_and_nan():
+    V = 5003
+    logits = torch.full((4, V), -1.0)
+    logits[0, 700] = 3.0
+    logits[0, 4000] = 3.0                      # tie: the smaller index wins
+    logits[1, 5002] = 9.0
+    logits[1, 17] = float("nan")               # a NaN never wins
+    logits[2, :] = float("nan")                # nothing finite: reported as invalid
+    logits[3, 0] = 0.5
+    out = ops().sample(logits.to(DEV)).cpu().tolist()
+    assert out[0] == 700 and out[1] == 5002 and out[3] == 0
+    assert out[2] == 2**31 - 1
+
+
+@pytest.mark.parametrize("vocab", [503, 151936])
+def test_sample_temperature_matches_plain(vocab):
+    g = torch.Generator().manual_seed(8)
+    rows = 6
+    logits = torch.randn(rows, vocab, generator=g) * 2
+    temps = [0.8, 0.0, 1.3, 0.8, 0.05, 2.0]
+    seeds = [7, 7, 123456789, 8, 0, 2**31 - 1]
+    positions = [5, 5, 70, 5, 0, 4095]
+    out = ops().sample(logits.to(DEV), torch.tensor(temps).to(DEV), torch.tensor(seeds, dtype=torch.int32).to(DEV),
+                       torch.tensor(positions, dtype=torch.int32).to(DEV)).cpu().tolist()
+    for r in range(rows):
+        tok, scores = plain_sample(logits[r].numpy(), temps[r], seeds[r], positions[r])
+        if out[r] != tok:   # only a near-tie of the perturbed scores may differ (32-bit log vs 64-bit)
+            assert scores is not None and abs(scores[out[r]] - scores[tok]) < 1e-4
+    # the draw depends on seed and position, not on the row or the batch
+    again = ops().sample(logits[3:4].to(DEV), torch.tensor(temps[3:4]).to(DEV),
+                         torch.tensor(seeds[3:4], dtype=torch.int32).to(DEV),
+                         torch.tensor(positions[3:4], dtype=torch.int32).to(DEV)).cpu().tolist()
+    assert again[0] == out[3]
