@@ -43,6 +43,7 @@ class LLM:
         self.cuda_graph = bool(cuda_graph)
         self._next_id = 0
         self.steps = 0
+        self.trace = None      # optional callable taking one dict per step (the CLI's --trace-steps)
 
     # ------------------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]],
@@ -103,4 +104,8 @@ class LLM:
                         by_id[e.id]["ttft"] = now - by_id[e.id]["t0"]
             sched.complete(plan, sampled)
             self.steps += 1
+            if self.trace is not None:
+                self.trace({"event": "step_completed", "step": self.steps, "requests": len(plan),
+                            "tokens": sum(e.n for e in plan), "sampled": len(sampled),
+                            "free_pages": self.engine.free_pages()})
             self._collect(by_id)

@@ -13,6 +13,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Iterable
 
 import torch
@@ -77,7 +78,10 @@ class SafetensorsFile:
         e = self.entries[name]
         if e["numel"] == 0:
             return torch.empty(e["shape"], dtype=e["dtype"])
-        t = torch.frombuffer(self._map, dtype=e["dtype"], count=e["numel"], offset=self._base + e["begin"])
+        with warnings.catch_warnings():
+            # The mapping is read-only on purpose; every consumer copies (to the device or to a cast).
+            warnings.simplefilter("ignore", UserWarning)
+            t = torch.frombuffer(self._map, dtype=e["dtype"], count=e["numel"], offset=self._base + e["begin"])
         return t.reshape(e["shape"])
 
 

@@ -239,3 +239,21 @@ def worst_error(got, want_by_name):
         if err > worst:
             worst, where = err, (name, pos)
     return worst, scale, where
+
+
+def error_stats(got, want_by_name):
+    """(max abs error / max |ref|, rms error / rms ref, where the worst lies)."""
+    worst, where = 0.0, None
+    se, sr, peak = 0.0, 0.0, 0.0
+    for (name, pos), row in got.items():
+        ref = want_by_name[name][pos]
+        diff = row.astype(np.float64) - ref
+        if not np.isfinite(diff).all():
+            return float("inf"), float("inf"), (name, pos)
+        peak = max(peak, float(np.abs(ref).max()))
+        se += float((diff * diff).sum())
+        sr += float((ref * ref).sum())
+        err = float(np.abs(diff).max())
+        if err > worst:
+            worst, where = err, (name, pos)
+    return worst / max(peak, 1e-30), (se / max(sr, 1e-30)) ** 0.5, where

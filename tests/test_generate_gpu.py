@@ -1,0 +1,153 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation: greedy tokens, temperature sampling with a seed, continuous batching with
+portions of prompts, end-of-sequence, and preemption when pages run out."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import ROOT, TINY, make_model_folder, random_tokens
+from plain_qwen2 import plain_forward, plain_greedy, plain_sample, read_model_folder
+
+pytestmark = pytest.mark.gpu
+_folders = {}
+
+
+def folder_of(tmp_path_factory, name, dtype):
+    if (name, dtype) not in _folders:
+        cfg, opt = TINY[name]
+        f = str(tmp_path_factory.mktemp(f"gen{name}{dtype}"))
+        make_model_folder(f, cfg, opt["seed"], dtype)
+        _folders[(name, dtype)] = f
+    return _folders[(name, dtype)]
+
+
+def check_teacher_forced(folder, prompt, tokens, temperature, seed, slack):
+    """Every generated token is what the plain implementation picks at its position, given the
+    tokens before it; where two candidates lie within `slack` of each other either may win."""
+    cfg, w = read_model_folder(folder)
+    logits = plain_forward(cfg, w, list(prompt) + list(tokens))
+    for i, tok in enumerate(tokens):
+        pos = len(prompt) + i
+        row = logits[pos - 1]
+        want, scores = plain_sample(row, temperature, seed, pos)
+        if tok != want:
+            s = scores if scores is not None else row
+            assert abs(s[tok] - s[want]) <= slack, f"token {i}: got {tok}, plain picks {want}"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_equals_plain_in_32_bit(tmp_path_factory, name):
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY[name]
+    folder = folder_of(tmp_path_factory, name, "float32")
+    rng = np.random.default_rng(0)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (5, 9, 17)]
+    llm = LLM(folder, "f32", page_size=opt["page_size"], kv_tokens=256, max_requests=4)
+    results = llm.generate(prompts, SamplingConfig(max_new_tokens=8, ignore_eos=True))
+    pcfg, w = read_model_folder(folder)
+    for prompt, res in zip(prompts, results):
+        assert res.finish_reason == "length" and res.prompt_tokens == prompt
+        assert res.tokens == plain_greedy(pcfg, w, prompt, 8)
+    assert llm.engine.cache.live_requests == 0 and llm.engine.free_pages()[0] == llm.engine.num_pages
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 0.25)])
+def test_mixed_batch_with_temperature(tmp_path_factory, dtype, slack):
+    """Configuration B's workload: four requests with prompts of 1/7/33/70 tokens, portions of at
+    most 8 tokens, 12 new tokens each at temperature 0.8 with seed 7."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY["B"]
+    folder = folder_of(tmp_path_factory, "B", dtype)
+    rng = np.random.default_rng(1)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (1, 7, 33, 70)]
+    llm = LLM(folder, dtype, max_batch_tokens=8, page_size=16, kv_tokens=512, max_requests=4)
+    sampling = SamplingConfig(max_new_tokens=12, do_sample=True, temperature=0.8, seed=7, ignore_eos=True)
+    results = llm.generate(prompts, sampling)
+    assert llm.steps > 14, "prompts were cut into portions"
+    for prompt, res in zip(prompts, results):
+        assert len(res.tokens) == 12
+        check_teacher_forced(folder, prompt, res.tokens, 0.8, 7, slack)
+    again = llm.generate(prompts[2:3], sampling)[0]
+    assert again.tokens == results[2].tokens, "the draw depends on seed and position, not on the batch"
+    other = llm.generate(prompts[2:3], SamplingConfig(max_new_tokens=12, do_sample=True, temperature=0.8, seed=8,
+                                                      ignore_eos=True))[0]
+    assert other.tokens != results[2].tokens
+
+
+def test_bfloat16_greedy_is_near_plain(tmp_path_factory):
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY["C"]
+    folder = folder_of(tmp_path_factory, "C", "bfloat16")
+    prompts = [random_tokens(np.random.default_rng(2), n, cfg["vocab_size"]) for n in (3, 40, 64)]
+    llm = LLM(folder, "bf16", page_size=8, kv_tokens=512, max_requests=4, max_batch_tokens=16)
+    for prompt, res in zip(prompts, llm.generate(prompts, SamplingConfig(max_new_tokens=30))):
+        check_teacher_forced(folder, prompt, res.tokens, 0.0, 0, 0.2)
+
+
+def test_eos_and_options(tmp_path_factory):
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY["B"]
+    folder = folder_of(tmp_path_factory, "B", "float32")
+    prompt = random_tokens(np.random.default_rng(3), 6, cfg["vocab_size"])
+    llm = LLM(folder, "f32", kv_tokens=256, max_requests=2)
+    free = llm.generate([prompt], SamplingConfig(max_new_tokens=6))[0].tokens
+    stop = llm.generate([prompt], SamplingConfig(max_new_tokens=6, eos_token_id=free[2]))[0]
+    assert stop.tokens == free[:3] and stop.finish_reason == "eos", "the end token is returned and counted"
+    assert llm.generate([prompt], SamplingConfig())[0].tokens == free[:1], "max_new_tokens defaults to 1"
+    with pytest.raises(ValueError, match="top_k"):
+        llm.generate([prompt], SamplingConfig(top_k=5))
+    bad = llm.generate([[cfg["vocab_size"]], prompt], SamplingConfig(max_new_tokens=2))
+    assert bad[0].finish_reason == "invalid" and bad[1].tokens == free[:2], "an invalid peer does not stop the others"
+    assert llm.engine.cache.live_requests == 0
+
+
+def test_pages_run_out_preempt_and_recompute(tmp_path_factory):
+    """Optimistic admission with a pool too small for all: requests are preempted and recomputed,
+    and every request still gets the tokens it gets alone."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY["A"]
+    folder = folder_of(tmp_path_factory, "A", "float32")
+    rng = np.random.default_rng(4)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (20, 24, 9, 30)]
+    sampling = SamplingConfig(max_new_tokens=20, ignore_eos=True)
+    roomy = LLM(folder, "f32", page_size=4, kv_tokens=1024, max_requests=4)
+    alone = [r.tokens for r in roomy.generate(prompts, sampling)]
+    tight = LLM(folder, "f32", page_size=4, kv_tokens=112, max_requests=4, reserve_future=False, max_batch_tokens=32)
+    results = tight.generate(prompts, sampling)
+    assert tight.scheduler.preemptions >= 1 and sum(r.preemptions for r in results) >= 1
+    assert [r.tokens for r in results] == alone
+    assert tight.engine.cache.live_requests == 0 and tight.engine.free_pages()[0] == tight.engine.num_pages
+    # with reservation (the default) the same pool makes requests wait instead
+    waiting = LLM(folder, "f32", page_size=4, kv_tokens=112, max_requests=4, max_batch_tokens=32)
+    assert [r.tokens for r in waiting.generate(prompts, sampling)] == alone and waiting.scheduler.preemptions == 0
+
+
+def test_command_line(tmp_path_factory):
+    cfg, opt = TINY["A"]
+    folder = folder_of(tmp_path_factory, "A", "float32")
+    prompt = random_tokens(np.random.default_rng(5), 7, cfg["vocab_size"])
+    cmd = [sys.executable, "-m", "llm_inference_lab_b200.cli", "--model-dir", folder, "--dtype", "f32",
+           "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5", "--repeat", "2", "--trace-steps"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    pcfg, w = read_model_folder(folder)
+    expect = plain_greedy(pcfg, w, prompt, 5, eos=[255])
+    assert line["generated_ids"] == expect and line["kv_released"] is True and line["input_ids"] == prompt
+    assert line["dtype"] == "f32" and line["generated_tokens"] == len(expect)
+    steps = [json.loads(s) for s in proc.stderr.splitlines() if s.startswith('{"event"')]
+    assert len(steps) >= len(expect)

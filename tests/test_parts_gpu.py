@@ -1,0 +1,256 @@
+"""Each part of a layer alone against the plain function of the same part, and the proof that
+the framework takes a new kind of part without a change to its files: a toy mixer with a
+state of its own, a toy architecture that uses it beside attention, both defined here."""
+import dataclasses
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TINY, make_model_folder, random_tokens
+from plain_qwen2 import (plain_attention_part, plain_block, plain_embedding, plain_gated_mlp, plain_linear,
+                         plain_rms_norm, read_model_folder)
+
+pytestmark = pytest.mark.gpu
+
+
+def engine_and_ctx(tmp_path, name, dtype, lengths):
+    """An engine of a tiny configuration and the context of one step that holds whole prompts."""
+    from llm_inference_lab_b200.engine import Engine, Entry
+
+    cfg, opt = TINY[name]
+    folder = make_model_folder(str(tmp_path / f"{name}{dtype}"), cfg, opt["seed"], dtype)
+    engine = Engine(folder, dtype, max_tokens=512, page_size=opt["page_size"], max_requests=4)
+    rng = np.random.default_rng(0)
+    entries = [Entry(i, random_tokens(rng, n, cfg["vocab_size"]), [n - 1]) for i, n in enumerate(lengths)]
+    for e in entries:
+        engine.open(e.request)
+        engine.cache.reserve(e.request, len(e.tokens))
+    ctx, rows = engine._pack(entries)
+    return engine, folder, cfg, ctx, rows, entries
+
+
+def close(a, b, dtype):
+    a = a.double().cpu().numpy()
+    err = np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+    assert np.isfinite(a).all() and err < (2e-5 if dtype == "float32" else 3e-2), err
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_parts_alone(tmp_path, name, dtype):
+    lengths = [19, 6, 33]
+    engine, folder, cfg, ctx, rows, entries = engine_and_ctx(tmp_path, name, dtype, lengths)
+    pcfg, w = read_model_folder(folder)
+    model = engine.model
+    T, H = sum(lengths), cfg["hidden_size"]
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(T, H, generator=g).to(tdt)
+    xd = x.double().numpy()
+    bounds = np.concatenate([[0], np.cumsum(lengths)])
+
+    # embedding
+    ids = np.concatenate([e.tokens for e in entries])
+    assert torch.equal(model.embedding.forward(ctx.token_ids).cpu(),
+                       torch.from_numpy(plain_embedding(ids, w["model.embed_tokens.weight"])).to(tdt))
+    # norm, alone and fused with the residual add
+    block = model.blocks[-1]
+    layer = len(model.blocks) - 1
+    p = f"model.layers.{layer}."
+    close(block.norms[0].forward(x.cuda()), plain_rms_norm(xd, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"]),
+          dtype)
+    delta = torch.randn(T, H, generator=g).to(tdt)
+    xs = x.clone().cuda()
+    y = block.norms[1].forward_add(xs, delta.cuda())
+    summed = (x.float() + delta.float()).to(tdt)
+    assert torch.equal(xs.cpu(), summed)
+    close(y, plain_rms_norm(summed.double().numpy(), w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]),
+          dtype)
+    # feed-forward
+    close(block.ffn.forward(x.cuda(), ctx),
+          plain_gated_mlp(xd, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"]),
+          dtype)
+    # mixer: attention of whole prompts, each request on its own
+    view = engine.views[layer]
+    out = block.mixer.forward(x.cuda(), ctx, view)
+    if out.dim() == 3:
+        out = out.sum(0)
+    window = cfg["sliding_window"] if cfg.get("use_sliding_window") and layer >= cfg["max_window_layers"] else 0
+    want = np.concatenate([plain_attention_part(xd[a:b], w, p + "self_attn.", pcfg, np.arange(b - a), window)
+                           for a, b in zip(bounds[:-1], bounds[1:])])
+    close(out, want, dtype)
+    # whole block: residual stream in, (residual, pending product) out
+    xs = x.clone().cuda()
+    res, pending = block.forward(xs, None, ctx, view)
+    if pending.dim() == 3:
+        pending = pending.sum(0)
+    want = np.concatenate([plain_block(xd[a:b], w, layer, pcfg, np.arange(b - a))
+                           for a, b in zip(bounds[:-1], bounds[1:])])
+    close(res.float() + pending.float(), want, dtype)
+    # head at gathered rows
+    h = torch.randn(3, H, generator=g).to(tdt)
+    head_w = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
+    logits = model.head.forward(h.cuda())
+    assert logits.dtype == torch.float32
+    close(logits, plain_linear(h.double().numpy(), head_w), "float32" if dtype == "float32" else "bfloat16")
+
+
+# ----------------------------------------------------------------------------------------
+# A toy mixer with a state of its own, and a toy architecture, defined in this test only.
+# ----------------------------------------------------------------------------------------
+
+def define_toy():
+    from llm_inference_lab_b200 import register_architecture
+    from llm_inference_lab_b200.config.base import ModelConfig, optional, positive, required
+    from llm_inference_lab_b200.parts import (FixedState, LayerCall, LayerSpec, Mixer, ModelBlueprint, PartSpec,
+                                              TensorSpec, register_part)
+
+    class RunningMean(Mixer):
+        """out[t] = w * mean(x[0..t]): the state per request is the running sum and the count."""
+
+        @classmethod
+        def tensors(cls, spec):
+            return [TensorSpec(spec.prefix + "mix.weight", (spec["hidden"],), init="norm")]
+
+        @classmethod
+        def cache_need(cls, spec):
+            return FixedState((spec["hidden"] + 1,))
+
+        def __init__(self, spec, weights, dtype, device):
+            super().__init__(spec, weights, dtype, device)
+            self.w = self._weight(weights, "mix.weight").float()
+            self.h = spec["hidden"]
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            at = 0
+            for n, slot in zip(ctx.q_lens, ctx.state_slots):
+                state = cache.state[slot]
+                sums = state[: self.h] + torch.cumsum(x[at: at + n].float(), dim=0)
+                counts = state[self.h] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                out[at: at + n] = (sums / counts[:, None] * self.w).to(x.dtype)
+                if cache.write:
+                    state[: self.h] = sums[-1]
+                    state[self.h] = counts[-1]
+                at += n
+            return out
+
+    register_part("mixer", "running_mean", RunningMean)
+
+    @dataclasses.dataclass
+    class ToyConfig(ModelConfig):
+        architecture = "ToyStateLM"
+        vocab_size: int = required(int, positive)
+        hidden_size: int = required(int, positive)
+        num_layers: int = required(int, positive)
+        inner_size: int = required(int, positive)
+        heads: int = optional(int, 2)
+        eps: float = optional(float, 1e-5)
+        max_positions: int = optional(int, 256)
+
+    def blueprint(cfg):
+        layers = []
+        for i in range(cfg.num_layers):
+            p = f"blocks.{i}."
+            if i % 2 == 0:
+                mixer = PartSpec("running_mean", {"hidden": cfg.hidden_size}, prefix=p)
+            else:
+                mixer = PartSpec("gqa_attention", {
+                    "hidden": cfg.hidden_size, "n_heads": cfg.heads, "n_kv_heads": 1,
+                    "head_dim": cfg.hidden_size // cfg.heads, "qkv_bias": False, "out_bias": False, "window": 0,
+                    "position": PartSpec("none", {})}, prefix=p + "attn.")
+            ffn = PartSpec("gated_mlp", {"hidden": cfg.hidden_size, "intermediate": cfg.inner_size, "act": "silu"},
+                           prefix=p + "ff.")
+            norms = tuple(PartSpec("rmsnorm", {"hidden": cfg.hidden_size, "eps": cfg.eps}, prefix=p + f"n{j}.")
+                          for j in range(2))
+            layers.append(LayerSpec("prenorm", mixer, ffn, norms, hidden=cfg.hidden_size))
+        # layer 0 runs a second time at the end, with a state of its own (cache id num_layers)
+        order = tuple(LayerCall(i, i) for i in range(cfg.num_layers)) + (LayerCall(0, cfg.num_layers),)
+        return ModelBlueprint(
+            hidden=cfg.hidden_size, vocab=cfg.vocab_size,
+            embedding=PartSpec("token_embedding", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size}, prefix="emb."),
+            layers=tuple(layers), order=order,
+            final_norm=PartSpec("rmsnorm", {"hidden": cfg.hidden_size, "eps": cfg.eps}, prefix="out_norm."),
+            head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size, "tied_to": "emb.weight"},
+                          prefix="head."),
+            max_positions=cfg.max_positions)
+
+    register_architecture("ToyStateLM", ToyConfig, blueprint)
+    return ToyConfig
+
+
+def toy_reference(folder, ids):
+    """The toy model on one whole sequence, in plain NumPy."""
+    from plain_qwen2 import plain_attention
+    import json
+    cfg = json.load(open(f"{folder}/config.json"))
+    _, w = read_model_folder(folder)
+    H, heads = cfg["hidden_size"], cfg["heads"]
+    x = w["emb.weight"][np.asarray(ids)]
+    T = len(ids)
+
+    def run(i, x):
+        p = f"blocks.{i}."
+        h = plain_rms_norm(x, w[p + "n0.weight"], cfg["eps"])
+        if i % 2 == 0:
+            a = np.cumsum(h, axis=0) / np.arange(1, T + 1)[:, None] * w[p + "mix.weight"]
+        else:
+            d = H // heads
+            q = plain_linear(h, w[p + "attn.q_proj.weight"]).reshape(T, heads, d)
+            k = plain_linear(h, w[p + "attn.k_proj.weight"]).reshape(T, 1, d)
+            v = plain_linear(h, w[p + "attn.v_proj.weight"]).reshape(T, 1, d)
+            a = plain_linear(plain_attention(q, k, v, np.arange(T)).reshape(T, H), w[p + "attn.o_proj.weight"])
+        r = x + a
+        return r + plain_gated_mlp(plain_rms_norm(r, w[p + "n1.weight"], cfg["eps"]), w[p + "ff.gate_proj.weight"],
+                                   w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+
+    for i in list(range(cfg["num_layers"])) + [0]:
+        x = run(i, x)
+    return plain_linear(plain_rms_norm(x, w["out_norm.weight"], cfg["eps"]), w["emb.weight"])
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    from llm_inference_lab_b200.engine import Engine, Entry
+    from llm_inference_lab_b200.weights import write_random_model
+
+    ToyConfig = define_toy()
+    cfg = ToyConfig.from_dict(dict(vocab_size=97, hidden_size=32, num_layers=3, inner_size=48, heads=2))
+    folder = write_random_model(cfg, str(tmp_path / "toy"), seed=3, dtype=torch.float32, std=0.08)
+    engine = Engine(folder, "float32", max_tokens=256, page_size=8, max_requests=3)
+    plan = engine.model.cache_plan
+    assert [type(n).__name__ for n in plan.needs] == ["FixedState", "PagedKV", "FixedState", "FixedState"]
+    rng = np.random.default_rng(0)
+    seqs = {0: random_tokens(rng, 37, 97), 1: random_tokens(rng, 12, 97)}
+    want = {k: toy_reference(folder, ids) for k, ids in seqs.items()}
+    got = {k: [] for k in seqs}
+    # request 0 in portions of changing size beside request 1 token by token
+    cuts0 = [5, 2, 9, 1, 1, 7, 3, 9]
+    at0 = at1 = 0
+    for n0 in cuts0:
+        entries = [Entry(0, seqs[0][at0: at0 + n0], list(range(n0)))]
+        if at1 < len(seqs[1]):
+            entries.append(Entry(1, seqs[1][at1: at1 + 1], [0]))
+        logits = engine.step(entries).cpu().numpy()
+        got[0].append(logits[:n0])
+        if len(entries) == 2:
+            got[1].append(logits[n0:])
+            at1 += 1
+        at0 += n0
+    assert at0 == 37
+    engine.close(0)
+    while at1 < len(seqs[1]):   # request 1 goes on alone; a new request takes request 0's state slot
+        entries = [Entry(1, seqs[1][at1: at1 + 1], [0])]
+        if at1 == 9:
+            entries.append(Entry(2, seqs[0][:4], [3]))
+        logits = engine.step(entries).cpu().numpy()
+        got[1].append(logits[:1])
+        if len(entries) == 2:
+            assert np.abs(logits[1] - want[0][3]).max() < 1e-4, "a state slot used again starts from zero"
+        at1 += 1
+    for k in seqs:
+        err = np.abs(np.concatenate(got[k]) - want[k]).max()
+        assert err < 1e-4, (k, err)
+    engine.close(1), engine.close(2)
+    assert engine.cache.free_state_slots == 3

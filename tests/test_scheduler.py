@@ -1,0 +1,203 @@
+"""The scheduler's decisions with a scripted step instead of a model (no GPU): admission,
+portions under the token budget, decoding, finishing and freeing, and what happens when
+pages run out.  The method follows the reference's `SteppedModel` tests
+(rust/engine/src/runner/model_runner.rs:987-1106, 1209-2683)."""
+import pytest
+
+from llm_inference_lab_b200.cache import CacheManager, GroupConfig
+from llm_inference_lab_b200.cache.manager import runtime
+
+
+def make(pages=64, page_size=4, max_requests=8, budget=8, reserve_future=True, max_seq_len=0, window=0):
+    cache = CacheManager([GroupConfig(page_size, window, pages)], max_requests)
+    sched = runtime().Scheduler(cache, budget, max_seq_len, 0, reserve_future)
+    return cache, sched
+
+
+def run(sched, next_token=lambda rid, pos: 100 + rid, max_steps=10_000):
+    """Drives the scheduler to the end; returns (plans, {id: Finished})."""
+    plans, done = [], {}
+    for _ in range(max_steps):
+        plan = sched.plan()
+        for f in sched.take_finished():
+            done[f.id] = f
+        if not plan:
+            assert sched.idle, "requests are left but nothing is planned"
+            break
+        plans.append([(e.id, e.start, e.n, e.sample) for e in plan])
+        sampled = [next_token(e.id, e.start + e.n) for e in plan if e.sample]
+        sched.complete(plan, sampled)
+        for f in sched.take_finished():
+            done[f.id] = f
+    return plans, done
+
+
+def test_one_request_prefill_then_decode():
+    cache, sched = make(budget=8)
+    sched.add(1, list(range(5)), 3)
+    plans, done = run(sched)
+    assert plans == [[(1, 0, 5, True)], [(1, 5, 1, True)], [(1, 6, 1, True)]]
+    assert done[1].generated == [101, 101, 101] and done[1].reason.name == "length"
+    assert cache.free_pages(0) == 64 and cache.live_requests == 0, "the last token needs no cache entry"
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    cache, sched = make(budget=4)
+    sched.add(1, list(range(10)), 2)
+    plans, done = run(sched)
+    assert plans == [[(1, 0, 4, False)], [(1, 4, 4, False)], [(1, 8, 2, True)], [(1, 10, 1, True)]]
+    assert len(done[1].generated) == 2
+
+
+def test_decode_tokens_come_first_and_prefill_takes_the_rest():
+    cache, sched = make(budget=6)
+    sched.add(1, [1, 2, 3], 4)
+    plan = sched.plan()
+    sched.complete(plan, [7])                          # request 1 now decodes
+    sched.add(2, list(range(20)), 1)
+    sched.add(3, list(range(4)), 1)
+    plan = sched.plan()
+    assert [(e.id, e.start, e.n, e.sample) for e in plan] == [(1, 3, 1, True), (2, 0, 5, False)]
+    sched.complete(plan, [7])
+    plan = sched.plan()
+    assert [(e.id, e.n) for e in plan] == [(1, 1), (2, 5)], "request 3 waits for budget, in order"
+    sched.complete(plan, [7])
+    plans, done = run(sched)
+    assert set(done) == {1, 2, 3} and cache.free_pages(0) == 64
+
+
+def test_budget_one_two_three_give_the_same_tokens():
+    outs = []
+    for budget in (1, 2, 3, 50):
+        cache, sched = make(budget=budget)
+        sched.add(1, [5, 6, 7, 8, 9], 4)
+        sched.add(2, [1], 3)
+        _, done = run(sched, next_token=lambda rid, pos: 10 * rid + pos)
+        outs.append({k: v.generated for k, v in done.items()})
+    assert all(o == outs[0] for o in outs) and outs[0][2] == [21, 22, 23]
+
+
+def test_eos_finishes_and_counts_the_token():
+    cache, sched = make()
+    sched.add(1, [1, 2], 10, eos=[42, 43])
+    sched.add(2, [1, 2], 3, eos=[42], ignore_eos=True)
+    toks = {1: iter([5, 43, 6]), 2: iter([42, 42, 42])}
+    _, done = run(sched, next_token=lambda rid, pos: next(toks[rid]))
+    assert done[1].generated == [5, 43] and done[1].reason.name == "eos"
+    assert done[2].generated == [42, 42, 42] and done[2].reason.name == "length"
+
+
+def test_invalid_and_trivial_requests():
+    cache, sched = make(max_seq_len=16)
+    sched.add(1, [], 2)
+    sched.add(2, list(range(10)), 8)                   # 10 + 8 - 1 = 17 > 16
+    sched.add(3, list(range(10)), 7)                   # 16: fits
+    sched.add(4, [1, 2], 0)
+    _, done = run(sched)
+    assert done[1].reason.name == "invalid" and "empty" in done[1].message
+    assert done[2].reason.name == "invalid" and "maximum sequence length" in done[2].message
+    assert done[3].reason.name == "length" and len(done[3].generated) == 7
+    assert done[4].reason.name == "length" and done[4].generated == []
+
+
+def test_admission_protects_the_future_of_running_requests():
+    """With reservation a request is admitted only if the pages for its whole life are free
+    beyond what running requests will still take; a later, smaller request may pass it."""
+    cache, sched = make(pages=6, page_size=4, budget=64)         # 24 tokens of cache
+    sched.add(1, list(range(4)), 9)                              # life: 12 tokens = 3 pages
+    sched.add(2, list(range(12)), 5)                             # life: 16 tokens = 4 pages: does not fit beside 1
+    sched.add(3, list(range(5)), 4)                              # life: 8 tokens = 2 pages: fits
+    plan = sched.plan()
+    assert [e.id for e in plan] == [1, 3] and sched.num_waiting == 1
+    sched.complete(plan, [9, 9])
+    plans, done = run(sched)
+    assert set(done) == {1, 2, 3} and all(f.reason.name == "length" for f in done.values())
+    assert sched.preemptions == 0 and all(f.preemptions == 0 for f in done.values())
+    first_of_2 = next(i for i, p in enumerate(plans) if any(e[0] == 2 for e in p))
+    assert all(any(e[0] == 1 for e in p) or any(e[0] == 3 for e in p) for p in plans[:first_of_2])
+    assert cache.free_pages(0) == 6
+
+
+def test_request_that_can_never_fit_fails_at_once():
+    cache, sched = make(pages=4, page_size=4)
+    sched.add(1, list(range(30)), 1)
+    sched.add(2, list(range(3)), 2)
+    _, done = run(sched)
+    assert done[1].reason.name == "capacity" and done[2].reason.name == "length"
+
+
+def test_pages_run_out_without_reservation_youngest_is_preempted_and_recomputed():
+    """Optimistic admission: both requests start, pages run out while they decode, the younger
+    one gives its pages back, waits, and later recomputes prompt + tokens so far.  Every
+    request still gets all its tokens, the same ones as alone."""
+    def token(rid, pos):
+        return 1000 * rid + pos
+
+    alone = {}
+    for rid, prompt, n in ((1, list(range(6)), 14), (2, list(range(7)), 12)):
+        cache, sched = make(pages=64, budget=16, reserve_future=False)
+        sched.add(rid, prompt, n)
+        alone[rid] = run(sched, token)[1][rid].generated
+    cache, sched = make(pages=7, page_size=4, budget=16, reserve_future=False)    # 28 tokens of cache
+    sched.add(1, list(range(6)), 14)                             # grows to 19 tokens
+    sched.add(2, list(range(7)), 12)                             # grows to 18 tokens
+    plans, done = run(sched, token)
+    assert sched.preemptions >= 1 and done[2].preemptions >= 1 and done[1].preemptions == 0
+    assert done[1].generated == alone[1] and done[2].generated == alone[2]
+    assert done[1].reason.name == "length" and done[2].reason.name == "length"
+    recompute = [p for p in plans if any(e[0] == 2 and e[1] == 0 and e[2] > 7 for e in p)]
+    assert recompute, "request 2 came back with prompt + generated tokens as one prompt"
+    assert cache.free_pages(0) == 7 and cache.live_requests == 0
+    cache.check_consistency()
+
+
+def test_alone_and_still_too_large_fails_with_capacity():
+    cache, sched = make(pages=3, page_size=4, budget=8, reserve_future=False)
+    sched.add(1, list(range(6)), 20)                             # would grow to 25 tokens > 12
+    _, done = run(sched)
+    assert done[1].reason.name == "capacity" and 0 < len(done[1].generated) < 20
+    assert cache.free_pages(0) == 3
+
+
+def test_failed_step_gives_reserved_pages_back():
+    cache, sched = make(pages=8, budget=16)
+    sched.add(1, list(range(9)), 2)
+    plan = sched.plan()
+    assert cache.free_pages(0) == 5
+    sched.abandon(plan)
+    assert cache.free_pages(0) == 8 and cache.reserved(1) == 0
+    plan = sched.plan()                                           # the same step is planned again
+    assert [(e.start, e.n) for e in plan] == [(0, 9)]
+
+
+def test_cancel_waiting_and_running():
+    cache, sched = make()
+    sched.add(1, [1, 2, 3], 5)
+    sched.add(2, [1, 2, 3], 5)
+    plan = sched.plan()
+    sched.complete(plan, [4, 4])
+    assert sched.cancel(1) and not sched.cancel(99)
+    sched.add(3, [1], 1)
+    assert sched.cancel(3)
+    _, done = run(sched)
+    assert done[1].reason.name == "cancelled" and done[3].reason.name == "cancelled"
+    assert done[2].reason.name == "length" and cache.free_pages(0) == 64
+
+
+def test_state_slots_bound_the_number_of_running_requests():
+    cache, sched = make(max_requests=2)
+    for rid in range(5):
+        sched.add(rid, [1, 2], 2)
+    plan = sched.plan()
+    assert len(plan) == 2 and sched.num_waiting == 3
+    sched.complete(plan, [0, 0])
+    _, done = run(sched)
+    assert len(done) == 5 and cache.free_state_slots == 2
+
+
+def test_windowed_group_is_budgeted_by_its_peak():
+    cache, sched = make(pages=6, page_size=4, window=6, budget=4)
+    sched.add(1, list(range(40)), 20)            # 59 tokens, far more than 24 slots, but the window needs 4 pages
+    _, done = run(sched)
+    assert done[1].reason.name == "length" and len(done[1].generated) == 20
+    assert cache.free_pages(0) == 6
