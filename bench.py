@@ -1,0 +1,301 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens/s and prefill tokens/s for the Qwen2.5-0.5B shape with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+
+A "step" is one decode step of a batch of requests (default 8) that each hold a prompt of
+512 tokens; W untimed warm-up steps, then exactly K timed steps between CUDA events.
+`value` is decoded tokens per second with the sampled ids staying on the device (the
+reference's --gpu-feedback mode, rust/engine/benches/qwen2.rs:182-229); `e2e` is the same
+through the Python entry point `LLM.generate`, with host token ids going in and coming out
+every step.  The line also carries a 2,048-token prefill, the decode step's HBM roofline
+fraction, decode at batch 1 and 64, the GPU's clocks during the timed region and the number
+of this repository's kernel launches inside it.  Inputs are larger than the L2 cache: a
+decode step streams about 1 GB of weights, so nothing is flushed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Layer sizes of the Qwen2.5-0.5B shape (random weights, seed 0, N(0, 0.02)).
+QWEN25_05B = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=151936, hidden_size=896,
+    intermediate_size=4864, num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=4096, hidden_act="silu",
+    tie_word_embeddings=True, use_sliding_window=False, eos_token_id=151645)
+PROMPT_LEN, NEW_TOKENS, PREFILL_TOKENS, PAGE_SIZE = 512, 256, 2048, 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            raw = json.load(open(path))
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"])}, "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = [int(r[0]) for r in self.rows if r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def model_folder(cfg_dict, layers):
+    """A random-weights model folder for the configuration (made once per machine and size)."""
+    import torch
+    from llm_inference_lab_b200.registry import resolve
+    from llm_inference_lab_b200.weights import write_random_model
+
+    cfg_dict = dict(cfg_dict, num_hidden_layers=layers)
+    folder = os.path.join(tempfile.gettempdir(), f"lab_b200_bench_qwen2_L{layers}_{os.getuid()}")
+    marker = os.path.join(folder, ".complete")
+    if not os.path.exists(marker):
+        cfg = resolve(cfg_dict).config_class.from_dict(cfg_dict)
+        write_random_model(cfg, folder, seed=0, dtype=torch.bfloat16, std=0.02, norm_std=0.0)
+        open(marker, "w").write("ok")
+    return folder
+
+
+def decode_bytes(cfg, layers, batch, mean_ctx):
+    """Bytes a decode step has to read: every weight once, and the cache of the live requests."""
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    d = h // cfg["num_attention_heads"]
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    per_layer = (nq + 2 * nkv) * d * h + (nq + 2 * nkv) * d + nq * d * h + 3 * h * i + 2 * h
+    weights = 2 * (layers * per_layer + v * h + h)
+    cache = 2 * batch * mean_ctx * layers * 2 * nkv * d
+    return weights + cache
+
+
+def prefill_flops(cfg, layers, tokens):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    d = h // cfg["num_attention_heads"]
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    linear = 2 * tokens * layers * ((nq + 2 * nkv) * d * h + nq * d * h + 3 * h * i) + 2 * v * h
+    attention = layers * nq * 2 * 2 * d * tokens * (tokens + 1) // 2
+    return linear + attention
+
+
+def run_decode(engine, graphs, batch, steps, warmup, rng, clocks=None):
+    """Prefill `batch` prompts of PROMPT_LEN tokens, then time `steps` decode steps (device feedback)."""
+    import torch
+    from llm_inference_lab_b200.engine import Entry
+    from llm_inference_lab_b200.kernels import ops
+
+    ids = list(range(batch))
+    vocab = engine.vocab
+    first = []
+    for r in ids:
+        prompt = [int(t) for t in rng.integers(0, vocab, PROMPT_LEN)]
+        logits = engine.step([Entry(r, prompt, [PROMPT_LEN - 1])])
+        first.append(int(logits.argmax(dim=-1).item()))
+    out = graphs.step(ids, tokens=first)
+    for _ in range(max(warmup - 1, 0)):
+        out = graphs.step(ids)
+    torch.cuda.synchronize()
+    ctx0 = engine.cache.length(ids[0])
+    launches0 = ops.COUNTER.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if clocks is not None:
+        clocks.__enter__()
+    e0.record()
+    for _ in range(steps):
+        out = graphs.step(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.__exit__(None, None, None)
+    ms = e0.elapsed_time(e1)
+    launches = ops.COUNTER.launches - launches0
+    tokens = out.cpu().tolist()
+    assert all(0 <= t < vocab for t in tokens), "decode produced an invalid token"
+    mean_ctx = ctx0 + (steps + 1) / 2.0
+    ops.take_device_errors()
+    for r in ids:
+        engine.close(r)
+    return ms, launches, mean_ctx
+
+
+def run_prefill(engine, rng, repeats=5):
+    import torch
+    from llm_inference_lab_b200.engine import Entry
+
+    times = []
+    for it in range(3 + repeats):
+        prompt = [int(t) for t in rng.integers(0, engine.vocab, PREFILL_TOKENS)]
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        logits = engine.step([Entry(1000 + it, prompt, [PREFILL_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        assert bool(torch.isfinite(logits).all())
+        engine.close(1000 + it)
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def run_e2e(folder, batch, steps, warmup):
+    """Decode tokens/s through LLM.generate: host ids in and out every step."""
+    import numpy as np
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    llm = LLM(folder, "bf16", max_batch_tokens=8192, page_size=PAGE_SIZE,
+              kv_tokens=batch * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE), max_requests=max(batch, 1),
+              max_seq_len=4096, cuda_graph=True)
+    rng = np.random.default_rng(1)
+    prompts = [[int(t) for t in rng.integers(0, llm.engine.vocab, PROMPT_LEN)] for _ in range(batch)]
+    n_new = min(NEW_TOKENS, warmup + steps + 2)
+    llm.generate(prompts, SamplingConfig(max_new_tokens=4, ignore_eos=True))          # compiles and captures
+    llm.step_log.clear()
+    results = llm.generate(prompts, SamplingConfig(max_new_tokens=n_new, ignore_eos=True))
+    assert all(len(r.tokens) == n_new for r in results)
+    decode = [(t, n) for t, n, is_decode in llm.step_log if is_decode and n == batch]
+    timed = decode[warmup: warmup + steps + 1]
+    k = len(timed) - 1
+    seconds = timed[-1][0] - timed[0][0]
+    meta_words = llm.graphs.cached[next(iter(llm.graphs.cached))].layout.total
+    return {"value": batch * k / seconds, "unit": "tokens/s", "steps": k,
+            "h2d_bytes_per_step": 4 * (meta_words + 3 * batch), "d2h_bytes_per_step": 4 * batch}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"],
+                    help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the prefill")
+    ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through LLM.generate")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pochenai/llm-inference-lab is a Rust + cuTile engine: no cargo/rustc or cuTile toolchain "
+                          "offline, and pip cannot install it (its pyproject.toml holds no engine)"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
+        return 2
+    warmup = max(args.warmup, 3)
+    steps = max(1, min(args.steps, NEW_TOKENS - warmup - 2))
+
+    import numpy as np
+    import torch
+    from llm_inference_lab_b200.engine import Engine
+    from llm_inference_lab_b200.engine.decode_graph import DecodeGraphs
+
+    cfg = QWEN25_05B
+    folder = model_folder(cfg, args.layers)
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(0)
+    engine = Engine(folder, "bf16", max_tokens=64 * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + 4096, page_size=PAGE_SIZE,
+                    max_requests=64, max_batch_tokens=8192, max_seq_len=4096)
+    graphs = DecodeGraphs(engine)
+
+    clocks = ClockSampler()
+    ms, launches, mean_ctx = run_decode(engine, graphs, args.batch, steps, warmup, rng, clocks)
+    value = args.batch * steps / (ms / 1e3)
+    nbytes = decode_bytes(cfg, args.layers, args.batch, mean_ctx)
+    achieved = nbytes / (ms / steps / 1e3) / 1e9
+
+    line = {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-0.5B)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02) seed 0, uniform-random token ids",
+        "config": {
+            "model": "Qwen2.5-0.5B shape", "global_batch": args.batch, "seq_len": 4096, "parallelism": "single-gpu",
+            "layers": args.layers, "layers_of_config": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_embeddings": True,
+            "prompt_len": PROMPT_LEN, "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE,
+            "decode": "cuda-graph, device feedback", "l2": "inputs larger than L2 (1 GB of weights per step)",
+            "peaks": pk_src},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+    }
+    if not args.skip_points:
+        pms = run_prefill(engine, rng)
+        flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+        line["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                           "ms": round(pms, 4), "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        points = {}
+        for b in (1, 64):
+            k = min(steps, 100)
+            bms, _, _ = run_decode(engine, graphs, b, k, warmup, rng)
+            points[f"decode_b{b}"] = round(b * k / (bms / 1e3), 1)
+        line["points"] = points
+    del graphs, engine
+    torch.cuda.empty_cache()
+    if not args.skip_e2e:
+        try:
+            line["e2e"] = {k: (round(v, 1) if isinstance(v, float) else v)
+                           for k, v in run_e2e(folder, args.batch, steps, warmup).items()}
+        except Exception as exc:  # noqa: BLE001 - the device-timed number stands on its own
+            line["e2e"] = {"error": f"{type(exc).__name__}: {exc}"}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,167 @@
+"""Decode steps replayed from CUDA graphs.
+
+A step in which every request brings exactly one token has the same launches
+every time; only the metadata (positions, cache slots, block tables, lengths)
+and the token ids change.  Such a step is captured once per (batch size, number
+of key splits) into a CUDA graph over fixed buffers; later steps copy their
+metadata into those buffers and replay the graph.  The sampled tokens stay in a
+device buffer that is also the next step's input, so a run of decode steps
+needs no copy back to the host unless the caller wants the tokens.
+
+The reference does the same for pure-decode steps: fixed metadata and source
+buffers uploaded before replay, graphs keyed by (slot table, batch, splits), a
+handful cached (rust/engine/src/runner/model/qwen2/graph.rs:18-151; capture in
+rust/engine/src/runner/model/qwen2/engine.rs:467-640, replay 713-752).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from ..parts.base import GroupView, StepContext
+
+
+@dataclasses.dataclass
+class _Captured:
+    graph: torch.cuda.CUDAGraph
+    layout: object
+    dev: torch.Tensor           # int32 metadata on the device
+    tokens: torch.Tensor        # [B] int32: input ids of the step, overwritten with the sampled ids
+    temps: torch.Tensor         # [B] float32
+    seeds: torch.Tensor         # [B] int32
+    rows: torch.Tensor          # [B] int32: 0..B-1, the rows whose logits are computed
+    logits: Optional[torch.Tensor] = None   # [B, vocab] float32 of the last replay (lives in the graph's pool)
+    launches: int = 0           # kernels the graph holds
+
+
+class DecodeGraphs:
+    MAX_CACHED = 16
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.cached: dict[tuple, _Captured] = {}
+        self.replays = 0
+        self.captures = 0
+
+    # ------------------------------------------------------------------------------------
+    def _key(self, n_requests: int, max_kv_len: int):
+        bucket = 256
+        while bucket < max_kv_len:
+            bucket *= 2
+        return (n_requests, bucket)
+
+    def _context(self, cap: _Captured, B: int, kv_bucket: int) -> StepContext:
+        eng, L, dev = self.engine, cap.layout, cap.dev
+        n_groups = len(eng.group_windows)
+
+        def view(at, n):
+            return dev[at: at + n]
+
+        width = eng.max_blocks
+        groups = [GroupView(eng.page_size, eng.group_windows[g], view(L.row_slot[g], B),
+                            view(L.block_table[g], B * width).view(B, width)) for g in range(n_groups)]
+        return StepContext(
+            dtype=eng.dtype, device=eng.device, n_tokens=B, n_requests=B, token_ids=cap.tokens,
+            row_req=view(L.row_req, B), row_pos=view(L.row_pos, B), q_start=view(L.q_start, B + 1),
+            kv_len=view(L.kv_len, B), pos0=view(L.pos0, B), state_slot=view(L.state_slot, B), groups=groups,
+            q_lens=[1] * B, kv_lens=[kv_bucket] * B, state_slots=[], max_q_len=1, max_kv_len=kv_bucket)
+
+    def _run(self, cap: _Captured, ctx: StepContext) -> torch.Tensor:
+        logits = self.engine.model.forward(ctx, self.engine.views, cap.rows)
+        # position of the token being drawn = tokens held after this step
+        ops.sample(logits, cap.temps, cap.seeds, ctx.kv_len, out=cap.tokens)
+        return logits
+
+    def _new_capture(self, key):
+        eng = self.engine
+        B, kv_bucket = key
+        n_groups = len(eng.group_windows)
+        layout = eng.cache.layout(B, B, [eng.max_blocks] * n_groups)
+        dev = torch.zeros((layout.total,), dtype=torch.int32, device=eng.device)
+        cap = _Captured(graph=torch.cuda.CUDAGraph(), layout=layout, dev=dev,
+                        tokens=torch.zeros((B,), dtype=torch.int32, device=eng.device),
+                        temps=torch.zeros((B,), dtype=torch.float32, device=eng.device),
+                        seeds=torch.zeros((B,), dtype=torch.int32, device=eng.device),
+                        rows=torch.arange(B, dtype=torch.int32, device=eng.device))
+        return cap, self._context(cap, B, kv_bucket)
+
+    # ------------------------------------------------------------------------------------
+    def step(self, requests: Sequence[int], tokens: Optional[Sequence[int]] = None,
+             temps: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
+             reserved: bool = False) -> torch.Tensor:
+        """One decode step for `requests` (each brings one token).  `tokens` are the input ids
+        on the host; None means: the ids the previous step of the same batch sampled, which
+        are still on the device.  Returns the device buffer [B] of sampled ids (valid until
+        the next step of this batch size)."""
+        eng = self.engine
+        B = len(requests)
+        pairs = [(int(r), 1) for r in requests]
+        if not reserved:
+            done = []
+            try:
+                for r, _ in pairs:
+                    eng.cache.reserve(r, 1)
+                    done.append(r)
+            except Exception:
+                for r in done:
+                    eng.cache.rollback(r)
+                raise
+        max_kv = max(eng.cache.reserved(r) for r, _ in pairs)
+        if max_kv > eng.max_seq_len:
+            raise ValueError("a request exceeds the maximum sequence length")
+        key = self._key(B, max_kv)
+        fresh = key not in self.cached
+        if fresh:
+            if len(self.cached) >= self.MAX_CACHED:
+                self.cached.pop(next(iter(self.cached)))
+            cap, ctx = self._new_capture(key)
+        else:
+            cap = self.cached[key]
+        st = eng._next_staging()
+        eng.cache.pack(pairs, cap.layout, st["np"], 0, 0)
+        n_meta = cap.layout.total
+        cap.dev.copy_(st["host"][:n_meta], non_blocking=True)
+        if tokens is not None:
+            st["np"][n_meta: n_meta + B] = np.asarray(tokens, dtype=np.int32)
+            cap.tokens.copy_(st["host"][n_meta: n_meta + B], non_blocking=True)
+        if temps is not None:
+            host_f = st["host"][n_meta + B: n_meta + 2 * B].view(torch.float32)
+            host_f.copy_(torch.tensor(list(temps), dtype=torch.float32))
+            cap.temps.copy_(host_f, non_blocking=True)
+            st["np"][n_meta + 2 * B: n_meta + 3 * B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
+            cap.seeds.copy_(st["host"][n_meta + 2 * B: n_meta + 3 * B], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        st["event"] = ev
+        if fresh:
+            # One eager run configures the kernels and fills the allocator, then the capture.
+            keep = cap.tokens.clone()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._run(cap, ctx)
+            torch.cuda.current_stream().wait_stream(side)
+            cap.tokens.copy_(keep)
+            before = ops.COUNTER.launches
+            with torch.cuda.graph(cap.graph):
+                cap.logits = self._run(cap, ctx)
+            cap.launches = ops.COUNTER.launches - before
+            ops.COUNTER.launches = before            # captured, not yet run
+            self.cached[key] = cap
+            self.captures += 1
+        cap.graph.replay()
+        ops.COUNTER.launches += cap.launches
+        self.replays += 1
+        if not reserved:
+            for r, _ in pairs:
+                eng.cache.commit(r, 1)
+        eng.stats.steps += 1
+        eng.stats.decode_tokens += B
+        return cap.tokens
+
+    def last_logits(self, n_requests: int, max_kv_len: int) -> torch.Tensor:
+        return self.cached[self._key(n_requests, max_kv_len)].logits

@@ -14,6 +14,7 @@ from typing import Optional, Sequence, Union
 
 from ..cache import manager as cache_mod
 from ..sampling import Sampler, SamplingConfig
+from .decode_graph import DecodeGraphs
 from .engine import Engine, Entry
 
 
@@ -41,6 +42,8 @@ class LLM:
         self.sampler = Sampler(self.engine.device)
         self.model_eos = list(self.engine.model.blueprint.eos_token_ids)
         self.cuda_graph = bool(cuda_graph)
+        self.graphs = DecodeGraphs(self.engine) if self.cuda_graph else None
+        self.step_log: list[tuple[float, int, bool]] = []   # (time the step's tokens reached the host, tokens, decode?)
         self._next_id = 0
         self.steps = 0
         self.trace = None      # optional callable taking one dict per step (the CLI's --trace-steps)
@@ -86,22 +89,32 @@ class LLM:
                 if sched.idle:
                     return
                 raise RuntimeError("the scheduler has requests left but plans no step")
-            entries = [Entry(e.id, sched.portion(e.id, e.start, e.n), [e.n - 1] if e.sample else []) for e in plan]
+            rows = [e for e in plan if e.sample]
+            cfgs = [by_id[e.id]["cfg"] for e in rows]
+            temps = [c.effective_temperature() for c in cfgs]
+            seeds = [c.seed for c in cfgs]
+            pure_decode = all(e.n == 1 and e.sample for e in plan)
+            sampled = []
             try:
-                logits = self.engine.step(entries, reserved=True)
+                if self.graphs is not None and pure_decode:
+                    # every request brings one token: replay the step from a CUDA graph
+                    tokens = [sched.portion(e.id, e.start, 1)[0] for e in plan]
+                    out = self.graphs.step([e.id for e in plan], tokens, temps, seeds, reserved=True)
+                    sampled = self.sampler.check(out.cpu().tolist(), self.engine.vocab)
+                else:
+                    entries = [Entry(e.id, sched.portion(e.id, e.start, e.n), [e.n - 1] if e.sample else [])
+                               for e in plan]
+                    logits = self.engine.step(entries, reserved=True)
+                    if logits is not None:
+                        sampled = self.sampler.pick(logits, temps, seeds, [e.start + e.n for e in rows])
             except Exception:
                 sched.abandon(plan)
                 raise
-            sampled = []
-            if logits is not None:
-                rows = [e for e in plan if e.sample]
-                cfgs = [by_id[e.id]["cfg"] for e in rows]
-                sampled = self.sampler.pick(logits, [c.effective_temperature() for c in cfgs],
-                                            [c.seed for c in cfgs], [e.start + e.n for e in rows])
-                now = time.perf_counter()
-                for e in rows:
-                    if by_id[e.id]["ttft"] is None:
-                        by_id[e.id]["ttft"] = now - by_id[e.id]["t0"]
+            now = time.perf_counter()
+            self.step_log.append((now, sum(e.n for e in plan), pure_decode))
+            for e in rows:
+                if by_id[e.id]["ttft"] is None:
+                    by_id[e.id]["ttft"] = now - by_id[e.id]["t0"]
             sched.complete(plan, sampled)
             self.steps += 1
             if self.trace is not None:

@@ -60,9 +60,18 @@ def _ptr(t) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
-def _check(code: int, what: str) -> None:
+class _Counter:
+    """Kernel launches issued through this module (a graph replay adds what it captured)."""
+    launches = 0
+
+
+COUNTER = _Counter()
+
+
+def _check(code: int, what: str, launches: int = 1) -> None:
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code}")
+    COUNTER.launches += launches
 
 
 def _on_gpu(*tensors) -> None:
@@ -332,7 +341,8 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
         _check(L.lab_attention_decode(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                       _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1],
                                       n_requests, n_q, n_kv, page_size, num_pages, window, ctypes.c_float(scale),
-                                      splits, _ptr(scratch if splits > 1 else None), _stream()), "attention_decode")
+                                      splits, _ptr(scratch if splits > 1 else None), _stream()), "attention_decode",
+               2 if splits > 1 else 1)
     return out
 
 

@@ -68,9 +68,14 @@ class Sampler:
             out = ops.sample(logits, meta[0], ints[0], ints[1])
         else:
             out = ops.sample(logits)
-        tokens = out.cpu().tolist()
-        for r, t in enumerate(tokens):
-            if not 0 <= t < logits.shape[1]:
-                raise RuntimeError(f"row {r}: non-finite logits or invalid argmax")
+        tokens = self.check(out.cpu().tolist(), logits.shape[1])
         assert len(tokens) == rows
+        return tokens
+
+    @staticmethod
+    def check(tokens: list[int], vocab: int) -> list[int]:
+        """A row without any finite candidate comes back as INT32_MAX (sampling.cu)."""
+        for r, t in enumerate(tokens):
+            if not 0 <= t < vocab:
+                raise RuntimeError(f"row {r}: non-finite logits or invalid argmax")
         return tokens
