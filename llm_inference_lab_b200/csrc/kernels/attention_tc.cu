@@ -507,3 +507,60 @@ LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, in
   }
   LAB_LAUNCH_CHECK();
 }
+
+// ----------------------------------------------------------------------------------------
+// Split-KV decode attention for callers that must not allocate (declared in
+// attention_noalloc.h; this entry point has no counterpart in the reference).
+//
+// The partial results of the splits normally live in a buffer the caller allocates.  Here
+// they live in a fixed array that is part of this library's image on the device, so the
+// call needs no allocation at all: no cudaMalloc, no cudaFree, no allocating library call.
+// Every GPU that loads this library holds the array (LAB_NOALLOC_MAX_FLOATS floats, 4 MiB)
+// until the process exits.
+// ----------------------------------------------------------------------------------------
+#define LAB_NOALLOC_MAX_FLOATS (1ll << 20)
+#define LAB_NOALLOC_MAX_DEVICES 64
+#define LAB_NOALLOC_TOO_LARGE (-2)
+#define LAB_NOALLOC_BAD_DEVICE (-3)
+
+static __device__ __align__(256) float g_noalloc_scratch[LAB_NOALLOC_MAX_FLOATS];
+// In host code the array's name only stands for the symbol; its device address is looked up
+// once per device and kept here.
+static float* g_noalloc_address[LAB_NOALLOC_MAX_DEVICES];
+
+LAB_EXPORT long long lab_attention_decode_noalloc_max_floats() { return LAB_NOALLOC_MAX_FLOATS; }
+
+LAB_EXPORT const char* lab_attention_decode_noalloc_strerror(int code) {
+  if (code == LAB_NOALLOC_TOO_LARGE)
+    return "requests * query heads * splits * (head size + 2) exceeds the fixed scratch of 1048576 floats: "
+           "use fewer splits or requests, or the entry point that takes a caller's buffer";
+  if (code == LAB_NOALLOC_BAD_DEVICE) return "the current device's ordinal is beyond the 64 this entry point keeps addresses for";
+  if (code == 0) return "ok";
+  return cudaGetErrorString((cudaError_t)code);
+}
+
+LAB_EXPORT int lab_attention_decode_noalloc(void* out, int out_stride, const void* q, int q_stride,
+                                            const void* cache_k, const void* cache_v, const int* q_start,
+                                            const int* kv_len, const int* block_table, int max_blocks, int requests,
+                                            int n_q, int n_kv, int page_size, int num_pages, int window, float scale,
+                                            int splits, cudaStream_t stream) {
+  if (splits < 1 || requests < 0 || n_q <= 0) return (int)cudaErrorInvalidValue;
+  if (lab_attention_decode_scratch_floats(requests, n_q, splits) > LAB_NOALLOC_MAX_FLOATS) return LAB_NOALLOC_TOO_LARGE;
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= LAB_NOALLOC_MAX_DEVICES) return LAB_NOALLOC_BAD_DEVICE;
+  if (g_noalloc_address[device] == nullptr) {
+    // Set-up, once per device, with that device current: the first call on a device does it,
+    // so that call should come before any stream capture.
+    float* address = nullptr;
+    e = cudaGetSymbolAddress((void**)&address, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_address[device] = address;
+  }
+  // Every split writes its (acc, max, sum) before the merge reads it, splits without keys
+  // included, so nothing in the array has to start at zero and nothing is cleared.
+  return lab_attention_decode(out, out_stride, q, q_stride, cache_k, cache_v, q_start, kv_len, block_table, max_blocks,
+                              requests, n_q, n_kv, page_size, num_pages, window, scale, splits,
+                              g_noalloc_address[device], stream);
+}
