@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int d, int page_size, int num_pages,
     int window, float scale) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   float* qs = smem;                      // [d]
   float* part = smem + d;                // [WARPS][d + 2]
   const int t = blockIdx.x, h = blockIdx.y, kvh = h / (n_q / n_kv);
@@ -114,13 +116,11 @@ LAB_EXPORT int lab_attention_plain(void* out, int out_stride, const void* q, int
   dim3 grid(tokens, n_q);
   const size_t smem = (size_t)(d + WARPS * (d + 2)) * sizeof(float);
   if (dtype == LAB_F32)
-    attention_plain_kernel<float><<<grid, WARPS * 32, smem, stream>>>(
-        (float*)out, out_stride, (const float*)q, q_stride, (const float*)cache_k, (const float*)cache_v, row_req,
-        row_pos, block_table, max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale);
-  else
-    attention_plain_kernel<__nv_bfloat16><<<grid, WARPS * 32, smem, stream>>>(
-        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache_k,
-        (const __nv_bfloat16*)cache_v, row_req, row_pos, block_table, max_blocks, n_q, n_kv, d, page_size, num_pages,
-        window, scale);
-  LAB_LAUNCH_CHECK();
+    return (int)lab_launch(attention_plain_kernel<float>, grid, dim3(WARPS * 32), smem, stream, (float*)out, out_stride,
+                           (const float*)q, q_stride, (const float*)cache_k, (const float*)cache_v, row_req, row_pos,
+                           block_table, max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale);
+  return (int)lab_launch(attention_plain_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, stream,
+                         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
+                         (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, row_req, row_pos, block_table,
+                         max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale);
 }

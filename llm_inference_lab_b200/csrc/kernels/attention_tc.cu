@@ -60,21 +60,25 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Where key `j` of a request lies: element offset of its row in the cache, or -1.
+// Where key `j` of a request lies: element offset of its row in the cache, -1 if its page was
+// given back, -2 if the block table names a page outside the pool (reported by the caller).
 __device__ __forceinline__ long long key_offset(const int* __restrict__ bt, int j, int kvh, int n_kv, int page_size,
                                                 int num_pages) {
   const int blk = j / page_size;
   const int page = bt[blk];
   if (page < 0) return -1;
-  if (page >= num_pages) {
-    lab_set_error(LAB_ERR_PAGE_RANGE);
-    return -1;
-  }
+  if (page >= num_pages) return -2;
   return (((long long)page * n_kv + kvh) * page_size + (j - blk * page_size)) * D;
 }
 
@@ -85,7 +89,8 @@ __device__ __forceinline__ long long key_offset(const int* __restrict__ bt, int 
 template <int BN>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint32_t ks, uint32_t vs,
                                           float (&o)[DTILES][4], float (&m)[2], float (&l)[2], int key0,
-                                          const int (&lo)[2], const int (&hi)[2], float scale_log2, int lane) {
+                                          const int (&lo)[2], const int (&hi)[2], float scale_log2, int lane,
+                                          bool all_visible = false) {
   float s[BN / 8][4];
 #pragma unroll
   for (int j = 0; j < BN / 8; ++j)
@@ -112,7 +117,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint3
     for (int e = 0; e < 4; ++e) {
       const int key = key0 + j * 8 + 2 * (lane & 3) + (e & 1);
       const int r = e >> 1;
-      const bool ok = key >= lo[r] && key <= hi[r];
+      const bool ok = all_visible || (key >= lo[r] && key <= hi[r]);
       s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
       mx[r] = fmaxf(mx[r], s[j][e]);
     }
@@ -123,7 +128,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint3
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     const float m_new = fmaxf(m[r], mx[r]);
     base[r] = (m_new == -INFINITY) ? 0.f : m_new;
-    corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - base[r]);
+    corr[r] = (m[r] == -INFINITY) ? 0.f : fast_exp2(m[r] - base[r]);
     m[r] = m_new;
   }
   float sum[2] = {0.f, 0.f};
@@ -133,7 +138,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint3
     float p[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      p[e] = exp2f(s[j][e] - base[e >> 1]);  // exp2(-inf) = 0 for masked keys
+      p[e] = fast_exp2(s[j][e] - base[e >> 1]);  // exp2(-inf) = 0 for masked keys
       sum[e >> 1] += p[e];
     }
     pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
@@ -163,20 +168,31 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint3
   }
 }
 
-// Copies `rows` keys starting at key0 into a shared-memory tile; keys outside [0, kv_len) and
-// keys whose page was given back are filled with zeros (never read as data: masked).
-template <int ROWS, int NTHREADS>
-__device__ __forceinline__ void load_tile(uint32_t dst, const __nv_bfloat16* __restrict__ cache,
-                                          const int* __restrict__ bt, int key0, int first_key, int kv_len, int kvh,
-                                          int n_kv, int page_size, int num_pages, int tid) {
+// R consecutive keys (R <= 32) and their values copied by one warp: lane r < R looks up the page
+// of key0 + r once, then the lanes share the row offsets by shuffle, so that a tile costs one
+// page lookup per lane and no 64-bit arithmetic per 16-byte chunk.  Keys outside
+// [first_key, kv_len) and keys whose page was given back become rows of zeros (they are masked).
+template <int R>
+__device__ __forceinline__ void load_kv_rows_warp(uint32_t dst_k, uint32_t dst_v,
+                                                  const __nv_bfloat16* __restrict__ cache_k,
+                                                  const __nv_bfloat16* __restrict__ cache_v,
+                                                  const int* __restrict__ bt, int key0, int first_key, int kv_len,
+                                                  int kvh, int n_kv, int page_size, int num_pages, int lane) {
+  const int j = key0 + lane;
+  long long mine = -1;
+  if (lane < R && j >= first_key && j < kv_len) mine = key_offset(bt, j, kvh, n_kv, page_size, num_pages);
+  if (mine == -2) lab_set_error(LAB_ERR_PAGE_RANGE);
+  constexpr int CHUNKS = R * CPR;
+  constexpr int PASSES = (CHUNKS + 31) / 32;
 #pragma unroll
-  for (int c = tid; c < ROWS * CPR; c += NTHREADS) {
-    const int row = c / CPR, col = c - row * CPR;
-    const int j = key0 + row;
-    long long off = -1;
-    if (j >= first_key && j < kv_len) off = key_offset(bt, j, kvh, n_kv, page_size, num_pages);
-    const __nv_bfloat16* src = cache + (off < 0 ? 0 : off) + col * 8;
-    cp_async16(dst + row * ROW_BYTES + col * 16, src, off >= 0);
+  for (int i = 0; i < PASSES; ++i) {
+    const int idx = i * 32 + lane;
+    const int row = idx / CPR, col = idx - row * CPR;
+    const long long off = __shfl_sync(0xffffffffu, mine, row & 31);
+    if (idx >= CHUNKS) continue;
+    const long long o = off < 0 ? 0 : off;
+    cp_async16(dst_k + row * ROW_BYTES + col * 16, cache_k + o + col * 8, off >= 0);
+    cp_async16(dst_v + row * ROW_BYTES + col * 16, cache_v + o + col * 8, off >= 0);
   }
 }
 
@@ -194,9 +210,13 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
     float scale_log2, int min_q_len) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.z, h = blockIdx.y;
   const int qs = q_start[b], ql = q_start[b + 1] - qs;
-  const int r0 = blockIdx.x * PF_BM;
+  // Later rows see more keys: their tiles are scheduled first, so that the longest CTAs do not
+  // start last.
+  const int r0 = (gridDim.x - 1 - blockIdx.x) * PF_BM;
   if (ql < min_q_len || r0 >= ql) return;
   const int kvh = h / (n_q / n_kv);
   const int p0 = pos0_arr[b], kvl = kv_len_arr[b];
@@ -221,9 +241,9 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
 
   auto issue = [&](int t, int stage) {
     const uint32_t kd = kv_s + stage * 2 * PF_TILE_BYTES;
-    load_tile<PF_BN, PF_THREADS>(kd, cache_k, bt, t * PF_BN, lo_all, kvl, kvh, n_kv, page_size, num_pages, tid);
-    load_tile<PF_BN, PF_THREADS>(kd + PF_TILE_BYTES, cache_v, bt, t * PF_BN, lo_all, kvl, kvh, n_kv, page_size,
-                                 num_pages, tid);
+    constexpr int RW = PF_BN / (PF_THREADS / 32);  // rows of the tile each warp copies
+    load_kv_rows_warp<RW>(kd + warp * RW * ROW_BYTES, kd + PF_TILE_BYTES + warp * RW * ROW_BYTES, cache_k, cache_v, bt,
+                          t * PF_BN + warp * RW, lo_all, kvl, kvh, n_kv, page_size, num_pages, lane);
     cp_async_commit();
   };
   issue(t_first, 0);
@@ -266,7 +286,11 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const int warp_hi = p0 + min(r0 + warp * 16 + 15, ql - 1);
     if (t * PF_BN <= warp_hi) {
       const uint32_t kd = kv_s + stage * 2 * PF_TILE_BYTES;
-      tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane);
+      // A tile that lies wholly before the warp's first row (and inside every row's window) needs no mask.
+      const int first_row = r0 + warp * 16;
+      const bool all_visible = first_row + 15 < ql && t * PF_BN + PF_BN - 1 <= p0 + first_row &&
+                               (window == 0 || t * PF_BN >= p0 + first_row + 15 - window + 1);
+      tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane, all_visible);
     }
     __syncthreads();  // the stage is refilled by the next iteration's prefetch
   }
@@ -305,6 +329,8 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window, float scale_log2, int splits,
     float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.z;
   const int qs = q_start[b];
   if (q_start[b + 1] - qs != 1) return;
@@ -352,8 +378,8 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   auto issue = [&](int t, int stage) {
     const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
     const int key0 = start + t * DC_BN;
-    load_tile<DC_BN, 32>(kd, cache_k, bt, key0, first, kvl, kvh, n_kv, page_size, num_pages, lane);
-    load_tile<DC_BN, 32>(kd + DC_TILE_BYTES, cache_v, bt, key0, first, kvl, kvh, n_kv, page_size, num_pages, lane);
+    load_kv_rows_warp<DC_BN>(kd, kd + DC_TILE_BYTES, cache_k, cache_v, bt, key0, first, kvl, kvh, n_kv, page_size,
+                             num_pages, lane);
   };
   // this warp's tiles: tile_lo + warp, + DC_WARPS, ...
   int t_issue = tile_lo + warp;
@@ -373,7 +399,10 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     cp_async_wait<DC_STAGES - 1>();
     __syncwarp();
     const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
-    tile_step<DC_BN>(qf, kd, kd + DC_TILE_BYTES, o, m, l, start + t * DC_BN, lo, hi, scale_log2, lane);
+    const int key0 = start + t * DC_BN;
+    // every key of an inner tile is visible to the one query row: no mask to evaluate
+    tile_step<DC_BN>(qf, kd, kd + DC_TILE_BYTES, o, m, l, key0, lo, hi, scale_log2, lane,
+                     key0 >= first && key0 + DC_BN <= kvl);
     __syncwarp();
     stage = (stage + 1) % DC_STAGES;
   }
@@ -431,6 +460,8 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, int out_stride,
                                        const int* __restrict__ q_start, int n_q, int splits,
                                        const float* __restrict__ part_acc, const float* __restrict__ part_ml) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x, head = blockIdx.y, dim = threadIdx.x;
   const int qs = q_start[b];
   if (q_start[b + 1] - qs != 1) return;
@@ -470,11 +501,10 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
     configured = true;
   }
   dim3 grid((max_q_len + PF_BM - 1) / PF_BM, n_q, requests);
-  attention_prefill_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(
-      (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache_k,
-      (const __nv_bfloat16*)cache_v, q_start, kv_len, pos0, block_table, max_blocks, n_q, n_kv, page_size, num_pages,
-      window, scale * LOG2E, min_q_len);
-  LAB_LAUNCH_CHECK();
+  return (int)lab_launch(attention_prefill_kernel, grid, dim3(PF_THREADS), (size_t)PF_SMEM, stream,
+                         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
+                         (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, q_start, kv_len, pos0,
+                         block_table, max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, min_q_len);
 }
 
 // scratch: lab_attention_decode_scratch_floats(...) floats when splits > 1 (may be null otherwise).
@@ -495,17 +525,16 @@ LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, in
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
   dim3 grid(splits, n_kv * m_tiles, requests);
-  attention_decode_kernel<<<grid, DC_THREADS, DC_SMEM, stream>>>(
-      (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache_k,
-      (const __nv_bfloat16*)cache_v, q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
-      scale * LOG2E, splits, part_acc, part_ml);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = lab_launch(attention_decode_kernel, grid, dim3(DC_THREADS), (size_t)DC_SMEM, stream,
+                             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
+                             (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, q_start, kv_len, block_table,
+                             max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, splits, part_acc,
+                             part_ml);
   if (e != cudaSuccess) return (int)e;
-  if (splits > 1) {
-    attention_merge_kernel<<<dim3(requests, n_q), D, 0, stream>>>((__nv_bfloat16*)out, out_stride, q_start, n_q,
-                                                                   splits, part_acc, part_ml);
-  }
-  LAB_LAUNCH_CHECK();
+  if (splits > 1)
+    e = lab_launch(attention_merge_kernel, dim3(requests, n_q), dim3(D), 0, stream, (__nv_bfloat16*)out, out_stride,
+                   q_start, n_q, splits, (const float*)part_acc, (const float*)part_ml);
+  return (int)e;
 }
 
 // ----------------------------------------------------------------------------------------

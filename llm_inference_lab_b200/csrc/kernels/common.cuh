@@ -64,6 +64,36 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 #define LAB_LAUNCH_CHECK() return (int)cudaGetLastError()
 
+// ---- programmatic dependent launch --------------------------------------------------------
+// Kernels of a step run back to back on one stream, each tiny next to its launch latency.
+// Launched with the programmatic-serialization attribute, a kernel may start while its
+// predecessor still runs: it signals `pdl_trigger()` at its top (its own successor may be
+// scheduled), does whatever does not depend on earlier kernels of the step (barrier set-up,
+// prefetch of weights), and calls `pdl_wait()` before it touches anything an earlier kernel
+// wrote or may still read.  `pdl_wait()` returns once the predecessor grid has completed and
+// its memory is visible; without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static int g_lab_pdl = 1;
+LAB_EXPORT void lab_set_pdl(int on) { g_lab_pdl = on; }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t lab_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_lab_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Reads the error word of this library and clears it.  Synchronises the device.
 LAB_EXPORT int lab_take_error_word(int* out) {
   int zero = 0;

@@ -18,6 +18,8 @@ template <typename T, typename OutT, bool GATED>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out, const T* __restrict__ x,
                                                          const T* __restrict__ w, const T* __restrict__ bias, int M,
                                                          int N, int K, int ldx, int ldo) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float xs[BK][BM + PAD];
   __shared__ float ws[GATED ? 2 : 1][BK][BN + PAD];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -86,12 +88,10 @@ int launch(void* out, const void* x, const void* w, const void* bias, int M, int
            cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (gated)
-    gemm_plain_kernel<T, OutT, true><<<grid, 256, 0, stream>>>((OutT*)out, (const T*)x, (const T*)w, nullptr, M, N, K,
-                                                               ldx, ldo);
-  else
-    gemm_plain_kernel<T, OutT, false><<<grid, 256, 0, stream>>>((OutT*)out, (const T*)x, (const T*)w, (const T*)bias,
-                                                                M, N, K, ldx, ldo);
-  return (int)cudaGetLastError();
+    return (int)lab_launch(gemm_plain_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
+                           (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo);
+  return (int)lab_launch(gemm_plain_kernel<T, OutT, false>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
+                         (const T*)w, (const T*)bias, M, N, K, ldx, ldo);
 }
 }  // namespace
 

@@ -14,6 +14,11 @@
 // "swapped" puts output features on M and the few tokens of a decode step on N, so that a
 // step with 1..256 tokens still fills the 128-row MMA and streams every weight once.
 //
+// Gated product: the weight matrix holds the gate rows, then the up rows.  In normal
+// orientation a tile's N side is half gate rows, half up rows (two TMA loads), so a thread's
+// accumulator row holds both; in swapped orientation a tile's M side is 64 gate rows over 64 up
+// rows of the same features, and the epilogue warps exchange them through shared memory.
+//
 // One CTA computes one output tile: warp 0 issues TMA loads into a ring of stages, warp 1
 // issues the MMAs (one elected lane) and owns the tensor-memory allocation, warps 2-5 read
 // the accumulator back (each its quarter of the 128 lanes) and apply the epilogue.  Every
@@ -160,15 +165,17 @@ struct Params {
 
 template <int BN, bool GATED, bool SWAP>
 struct Shape {
-  static constexpr int A_TILES = (GATED && SWAP) ? 2 : 1;
-  static constexpr int A_BYTES = A_TILES * BM * BK * 2;
+  static constexpr int A_TILES = 1;
+  static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int ACC_COLS = A_TILES * BN;
+  static constexpr int ACC_COLS = BN;
   static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // gated + swapped: the epilogue exchanges gate and up values through the (by then idle) stages
+  static_assert(!(GATED && SWAP) || STAGES * STAGE_BYTES >= BM * (BN + 1) * 4, "exchange buffer must fit");
 };
 
 template <int BN, bool GATED, bool SWAP, typename OutT>
@@ -183,8 +190,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM;
+  constexpr int M_ROWS = (GATED && SWAP) ? BM / 2 : BM;  // output rows (features) per tile on the M side
+  const int m0 = blockIdx.x * M_ROWS;
   const int n_tile_rows = (GATED && !SWAP) ? BN / 2 : BN;  // rows of the N-side operand per tile
   const int n0 = blockIdx.y * n_tile_rows;
   const int kt0 = blockIdx.z * p.k_tiles_per_split;
@@ -210,23 +219,45 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: TMA loads ----
+      // Weights do not depend on earlier kernels of the step: the first stages' weight tiles are
+      // requested before the wait on the predecessor, the activation tiles after it.
+      auto load_weights = [&](int s, int kx) {
+        uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + S::A_BYTES;
+        if (SWAP) {
+          if (GATED) {
+            tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
+            tma_load_2d(a_dst + (BM / 2) * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
+          } else {
+            tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
+          }
+        } else {
+          tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
+          if (GATED) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kx, p.up_offset + n0);
+        }
+      };
+      auto load_activations = [&](int s, int kx) {
+        uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
+        if (SWAP) tma_load_2d(a_dst + S::A_BYTES, &map_b, &full[s], kx, n0);
+        else tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
+      };
       int issued = 0;
-      for (int i = 0; i < n_kt; ++i) {
+      const int ahead = n_kt < S::STAGES ? n_kt : S::STAGES;
+      for (int i = 0; i < ahead; ++i) {  // the ring is empty: no wait
+        mbar_expect_tx(&full[i], S::STAGE_BYTES);
+        load_weights(i, (kt0 + i) * BK);
+      }
+      pdl_wait();
+      for (int i = 0; i < ahead; ++i) load_activations(i, (kt0 + i) * BK);
+      issued = ahead;
+      for (int i = ahead; i < n_kt; ++i) {
         const int s = i % S::STAGES;
         const uint32_t ph = (i / S::STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
-        uint8_t* b_dst = a_dst + S::A_BYTES;
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
         const int kx = (kt0 + i) * BK;
-        tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
-        if (GATED && SWAP) tma_load_2d(a_dst + BM * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
-        if (GATED && !SWAP) {
-          tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
-          tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kx, p.up_offset + n0);
-        } else {
-          tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
-        }
+        load_weights(s, kx);
+        load_activations(s, kx);
         issued = i + 1;
       }
       if (*abort_flag) {
@@ -257,8 +288,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           const uint64_t db = smem_desc_sw128(b_addr + k * UMMA_K * 2);
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
           umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, acc);
-          if (GATED && SWAP)
-            umma_bf16(tmem_base + BN, smem_desc_sw128(a_addr + BM * BK * 2 + k * UMMA_K * 2), db, idesc, acc);
         }
         umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
       }
@@ -267,12 +296,16 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   } else {
     // ---- epilogue: warps 2..5, each reads its quarter of the 128 accumulator lanes ----
     const int quarter = warp & 3;
+    pdl_wait();  // the output may still be read by an earlier kernel until it has completed
     const bool ok = n_kt > 0 ? mbar_wait(acc_full, 0, abort_flag) : true;
     tc_fence_after();
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int m = m0 + quarter * 32 + lane;  // this thread's row on the M side
     const bool partial = p.split_stride != 0;
-    if (ok && !*abort_flag) {
+    // Decided once per thread; the gated swapped epilogue meets at a named barrier, which every
+    // epilogue thread reaches whatever it decided.
+    const bool go = ok && !*abort_flag;
+    if (go || (SWAP && GATED)) {
       if (!SWAP) {
         // thread = token row m; columns = output features
         constexpr int OUT_COLS = GATED ? BN / 2 : BN;
@@ -321,33 +354,55 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         }
       } else {
         // thread = output feature m; columns = tokens
-        const float b = (p.bias && !partial && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
+        if (GATED) {
+          // lanes 0..63 hold gate values, lanes 64..127 the up values of the same 64 features:
+          // all go through shared memory (the pipeline stages are idle by now), then each of the
+          // 128 threads finishes one feature for half of the tokens.
+          float* ex = reinterpret_cast<float*>(tiles);
+          const int lane_global = quarter * 32 + lane;
+          const bool go_warp = __all_sync(0xffffffffu, go);
 #pragma unroll 1
-        for (int c = 0; c < BN / 16; ++c) {
-          const int t = n0 + c * 16;
-          if (t >= p.n_rows) break;  // same for the whole warp
-          float v[16];
-          if (n_kt > 0) tmem_ld16(lane_addr + c * 16, v);
-          else
+          for (int c = 0; c < BN / 16 && go_warp; ++c) {
+            if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
+            float v[16];
+            tmem_ld16(lane_addr + c * 16, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          if (GATED) {
-            float u[16];
-            tmem_ld16(lane_addr + BN + c * 16, u);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_gate(v[j], u[j]);
+            for (int j = 0; j < 16; ++j) ex[lane_global * (BN + 1) + c * 16 + j] = v[j];
           }
-          if (m >= p.m_rows) continue;
-          if (partial) {
-            float* dst = (float*)p.out + blockIdx.z * p.split_stride + m;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int t = threadIdx.x - 64, f = t & 63, h = t >> 6;
+          if (go && m0 + f < p.m_rows) {
+            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + m0 + f;
+            for (int col = h * (BN / 2); col < (h + 1) * (BN / 2); ++col) {
+              const int tok = n0 + col;
+              if (tok >= p.n_rows) break;
+              dst[(size_t)tok * p.ld_out] =
+                  __float2bfloat16_rn(silu_gate(ex[f * (BN + 1) + col], ex[(64 + f) * (BN + 1) + col]));
+            }
+          }
+        } else {
+          const float b = (p.bias && !partial && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
+#pragma unroll 1
+          for (int c = 0; c < BN / 16; ++c) {
+            const int t = n0 + c * 16;
+            if (t >= p.n_rows) break;  // same for the whole warp
+            float v[16];
+            if (n_kt > 0) tmem_ld16(lane_addr + c * 16, v);
+            else
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = v[j];
-          } else {
-            OutT* dst = (OutT*)p.out + m;
+              for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            if (m >= p.m_rows) continue;
+            if (partial) {
+              float* dst = (float*)p.out + blockIdx.z * p.split_stride + m;
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(v[j] + b);
+              for (int j = 0; j < 16; ++j)
+                if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = v[j];
+            } else {
+              OutT* dst = (OutT*)p.out + m;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(v[j] + b);
+            }
           }
         }
       }
@@ -403,8 +458,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, THREADS, S::SMEM, stream>>>(ma, mb, p);
-  return (int)cudaGetLastError();
+  return (int)lab_launch(kern, grid, dim3(THREADS), (size_t)S::SMEM, stream, ma, mb, p);
 }
 
 template <bool GATED, bool SWAP, typename OutT>
@@ -452,11 +506,12 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
     p.n_rows = n_out;
     grid = dim3((tokens + BM - 1) / BM, (n_out + box_b - 1) / box_b, splits);
   } else {
-    if ((rc = make_map(&ma, w, w_rows, K, K, BM))) return rc;
+    const int m_rows_tile = gated ? BM / 2 : BM;
+    if ((rc = make_map(&ma, w, w_rows, K, K, m_rows_tile))) return rc;
     if ((rc = make_map(&mb, x, tokens, K, ldx, bn))) return rc;
     p.m_rows = n_out;
     p.n_rows = tokens;
-    grid = dim3((n_out + BM - 1) / BM, (tokens + bn - 1) / bn, splits);
+    grid = dim3((n_out + m_rows_tile - 1) / m_rows_tile, (tokens + bn - 1) / bn, splits);
   }
   // A gated tile whose "gate" rows run past n_out would read "up" rows as gate: tiles are cut so
   // that valid outputs never mix the halves (rows >= n_out are masked in the epilogue), but the

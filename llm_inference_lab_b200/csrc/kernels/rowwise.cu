@@ -16,6 +16,8 @@
 template <typename T>
 __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
                              int hidden, int vocab) {
+  pdl_trigger();
+  pdl_wait();  // the ids may come from the previous step's sampling kernel
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -35,11 +37,10 @@ LAB_EXPORT int lab_embed(void* out, const void* table, const int* ids, int token
                          cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (dtype == LAB_F32)
-    embed_kernel<float><<<tokens, 128, 0, stream>>>((float*)out, (const float*)table, ids, hidden, vocab);
-  else
-    embed_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids,
-                                                            hidden, vocab);
-  LAB_LAUNCH_CHECK();
+    return (int)lab_launch(embed_kernel<float>, dim3(tokens), dim3(128), 0, stream, (float*)out, (const float*)table,
+                           ids, hidden, vocab);
+  return (int)lab_launch(embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, (__nv_bfloat16*)out,
+                         (const __nv_bfloat16*)table, ids, hidden, vocab);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -51,6 +52,23 @@ LAB_EXPORT int lab_embed(void* out, const void* table, const int* ids, int token
 // `partial` (optional) holds `splits` 32-bit partial products [splits, tokens, hidden]
 // of the preceding matrix product, summed here in a fixed order.
 // ----------------------------------------------------------------------------------------
+// Sum of the split-K partial products of one element, in ascending split order; the loads of
+// four splits are issued together so that their latencies overlap.
+__device__ __forceinline__ float sum_partials(const float* __restrict__ p, int splits, size_t stride) {
+  float acc = 0.f;
+  int s = 0;
+  for (; s + 4 <= splits; s += 4) {
+    const float a0 = p[(size_t)s * stride], a1 = p[(size_t)(s + 1) * stride], a2 = p[(size_t)(s + 2) * stride],
+                a3 = p[(size_t)(s + 3) * stride];
+    acc += a0;
+    acc += a1;
+    acc += a2;
+    acc += a3;
+  }
+  for (; s < splits; ++s) acc += p[(size_t)s * stride];
+  return acc;
+}
+
 template <typename T>
 __global__ void add_rmsnorm_kernel(T* __restrict__ y, T* __restrict__ x, const T* __restrict__ delta,
                                    const float* __restrict__ partial, int splits, size_t split_stride,
@@ -58,6 +76,8 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, T* __restrict__ x, const T
                                    float eps) {
   __shared__ float scratch[32];
   extern __shared__ float rowbuf[];  // hidden floats
+  pdl_trigger();
+  pdl_wait();
   int in_row = blockIdx.x;
   if (rows) {
     in_row = rows[blockIdx.x];
@@ -67,15 +87,14 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, T* __restrict__ x, const T
     }
   }
   T* xr = x + (size_t)in_row * hidden;
+  // The norm weight does not depend on the row's sum: its first element per thread is fetched now,
+  // so that its latency runs beside the loads and the reduction below.
+  const float w_first = threadIdx.x < hidden ? to_f32<T>(w[threadIdx.x]) : 0.f;
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = to_f32<T>(xr[i]);
     if (delta) v += to_f32<T>(delta[(size_t)in_row * hidden + i]);
-    if (partial) {
-      float p = 0.f;
-      for (int s = 0; s < splits; ++s) p += partial[s * split_stride + (size_t)in_row * hidden + i];
-      v += p;
-    }
+    if (partial) v += sum_partials(partial + (size_t)in_row * hidden + i, splits, split_stride);
     if (delta || partial) {
       v = round_to<T>(v);
       if (!rows) xr[i] = from_f32<T>(v);
@@ -88,7 +107,100 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, T* __restrict__ x, const T
   T* yr = y + (size_t)blockIdx.x * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float n = round_to<T>(rowbuf[i] * inv);
-    yr[i] = from_f32<T>(n * to_f32<T>(w[i]));
+    yr[i] = from_f32<T>(n * (i == (int)threadIdx.x ? w_first : to_f32<T>(w[i])));
+  }
+}
+
+// The same for bfloat16 rows whose width is a multiple of 8, for steps with many rows: a thread
+// owns chunks of 8 elements (16-byte loads and stores) and keeps them in registers.
+constexpr int NORM_VEC_THREADS = 128;
+constexpr int NORM_VEC_MAX_CHUNKS = 8;  // per thread: widths up to 128 * 8 * 8 = 8192
+
+__global__ void __launch_bounds__(NORM_VEC_THREADS) add_rmsnorm_vec_kernel(
+    __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+    const float* __restrict__ partial, int splits, size_t split_stride, const __nv_bfloat16* __restrict__ w,
+    const int* __restrict__ rows, int n_in_rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  int in_row = blockIdx.x;
+  if (rows) {
+    in_row = rows[blockIdx.x];
+    if (in_row < 0 || in_row >= n_in_rows) {
+      if (threadIdx.x == 0) lab_set_error(LAB_ERR_ROW_RANGE);
+      in_row = 0;
+    }
+  }
+  const int chunks = hidden / 8;
+  const size_t base = (size_t)in_row * hidden;
+  float v[NORM_VEC_MAX_CHUNKS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NORM_VEC_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * NORM_VEC_THREADS;
+    if (c >= chunks) break;
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + base + c * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      v[k][2 * e] = f.x;
+      v[k][2 * e + 1] = f.y;
+    }
+    if (delta) {
+      const uint4 rd = *reinterpret_cast<const uint4*>(delta + base + c * 8);
+      const __nv_bfloat162* hd = reinterpret_cast<const __nv_bfloat162*>(&rd);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(hd[e]);
+        v[k][2 * e] += f.x;
+        v[k][2 * e + 1] += f.y;
+      }
+    }
+    if (partial) {
+      float p[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < splits; ++s) {  // ascending split order, as the scalar kernel
+        const float4 a = *reinterpret_cast<const float4*>(partial + s * split_stride + base + c * 8);
+        const float4 b = *reinterpret_cast<const float4*>(partial + s * split_stride + base + c * 8 + 4);
+        p[0] += a.x; p[1] += a.y; p[2] += a.z; p[3] += a.w;
+        p[4] += b.x; p[5] += b.y; p[6] += b.z; p[7] += b.w;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[k][e] += p[e];
+    }
+    if (delta || partial) {
+      uint4 packed;
+      __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        hp[e] = __floats2bfloat162_rn(v[k][2 * e], v[k][2 * e + 1]);
+        const float2 f = __bfloat1622float2(hp[e]);
+        v[k][2 * e] = f.x;
+        v[k][2 * e + 1] = f.y;
+      }
+      if (!rows) *reinterpret_cast<uint4*>(x + base + c * 8) = packed;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[k][e] * v[k][e];
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  __nv_bfloat16* yr = y + (size_t)blockIdx.x * hidden;
+#pragma unroll
+  for (int k = 0; k < NORM_VEC_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * NORM_VEC_THREADS;
+    if (c >= chunks) break;
+    const uint4 rw = *reinterpret_cast<const uint4*>(w + c * 8);
+    const __nv_bfloat162* hw = reinterpret_cast<const __nv_bfloat162*>(&rw);
+    uint4 packed;
+    __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 fw = __bfloat1622float2(hw[e]);
+      const float n0 = round_to<__nv_bfloat16>(v[k][2 * e] * inv), n1 = round_to<__nv_bfloat16>(v[k][2 * e + 1] * inv);
+      hp[e] = __floats2bfloat162_rn(n0 * fw.x, n1 * fw.y);
+    }
+    *reinterpret_cast<uint4*>(yr + c * 8) = packed;
   }
 }
 
@@ -96,23 +208,28 @@ LAB_EXPORT int lab_add_rmsnorm(void* y, void* x, const void* delta, const float*
                                long long split_stride, const void* w, const int* rows, int n_out_rows, int n_in_rows,
                                int hidden, float eps, int dtype, cudaStream_t stream) {
   if (n_out_rows <= 0) return 0;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const bool aligned = ((((uintptr_t)y) | ((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)partial) | ((uintptr_t)w)) & 15) == 0;
+  if (dtype == LAB_BF16 && n_out_rows > 64 && hidden % 8 == 0 && aligned &&
+      hidden <= NORM_VEC_THREADS * NORM_VEC_MAX_CHUNKS * 8 && (split_stride % 4) == 0)
+    return (int)lab_launch(add_rmsnorm_vec_kernel, dim3(n_out_rows), dim3(NORM_VEC_THREADS), 0, stream,
+                           (__nv_bfloat16*)y, (__nv_bfloat16*)x, (const __nv_bfloat16*)delta, partial, splits,
+                           (size_t)split_stride, (const __nv_bfloat16*)w, rows, n_in_rows, hidden, eps);
+  int threads = (hidden + 31) / 32 * 32;   // one element per thread where the row allows it
+  threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (dtype == LAB_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<float><<<n_out_rows, threads, smem, stream>>>(
-        (float*)y, (float*)x, (const float*)delta, partial, splits, (size_t)split_stride, (const float*)w, rows,
-        n_in_rows, hidden, eps);
-  } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<__nv_bfloat16><<<n_out_rows, threads, smem, stream>>>(
-        (__nv_bfloat16*)y, (__nv_bfloat16*)x, (const __nv_bfloat16*)delta, partial, splits, (size_t)split_stride,
-        (const __nv_bfloat16*)w, rows, n_in_rows, hidden, eps);
+    return (int)lab_launch(add_rmsnorm_kernel<float>, dim3(n_out_rows), dim3(threads), smem, stream, (float*)y,
+                           (float*)x, (const float*)delta, partial, splits, (size_t)split_stride, (const float*)w,
+                           rows, n_in_rows, hidden, eps);
   }
-  LAB_LAUNCH_CHECK();
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return (int)lab_launch(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_out_rows), dim3(threads), smem, stream,
+                         (__nv_bfloat16*)y, (__nv_bfloat16*)x, (const __nv_bfloat16*)delta, partial, splits,
+                         (size_t)split_stride, (const __nv_bfloat16*)w, rows, n_in_rows, hidden, eps);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -122,75 +239,98 @@ LAB_EXPORT int lab_add_rmsnorm(void* y, void* x, const void* delta, const float*
 //        q is rotated in place.
 //   cache_k / cache_v: [num_pages, n_kv, page_size, d]; slot = page * page_size + offset.
 // ----------------------------------------------------------------------------------------
+// The fused projection arrives either rounded to T in `qkv` (q is then rotated in place), or
+// as `splits` 32-bit split-K partial products in `partial` ([splits, tokens, row_stride]) with
+// the bias still to be added: the kernel sums them in ascending order, adds the bias in 32-bit,
+// rounds once (the value the projection would have stored) and writes rotated q to `q_out`
+// ([tokens, n_q * d]).
+// Block (t, g) serves token t and heads [g * heads_per_block, ...): one head per block when a
+// step has few tokens (more blocks in flight), all heads per block when it has many.
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ partial,
+                                     int splits, size_t split_stride, const T* __restrict__ bias,
+                                     T* __restrict__ q_out, const int* __restrict__ positions,
                                      const float* __restrict__ inv_freq, int rotary_dim,
                                      const int* __restrict__ slots, T* __restrict__ cache_k, T* __restrict__ cache_v,
-                                     int n_q, int n_kv, int d, int page_size, int num_pages) {
+                                     int n_q, int n_kv, int d, int page_size, int num_pages, int heads_per_block) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
-  const int head = blockIdx.y;  // [0, n_q) q heads, then n_kv k heads, then n_kv v heads
-  T* src = qkv + (size_t)t * row_stride + (size_t)head * d;
+  const int n_heads = n_q + 2 * n_kv;  // [0, n_q) q heads, then n_kv k heads, then n_kv v heads
+  const int head_lo = blockIdx.y * heads_per_block;
+  const int head_hi = min(n_heads, head_lo + heads_per_block);
+  auto value = [&](size_t col) -> float {
+    if (partial) {
+      float v = sum_partials(partial + (size_t)t * row_stride + col, splits, split_stride);
+      if (bias) v += to_f32<T>(bias[col]);
+      return round_to<T>(v);
+    }
+    return to_f32<T>(qkv[(size_t)t * row_stride + col]);
+  };
   const float pos = (float)positions[t];
-  const int half = rotary_dim / 2;
-  if (head < n_q + n_kv) {
-    T* dst = src;
-    if (head >= n_q) {
-      if (cache_k == nullptr) return;
-      const int slot = slots[t];
-      if (slot < 0) return;
+  long long cache_row = -1;  // element offset of (page, kv head 0, offset) in the cache, or -1: no write
+  if (cache_k != nullptr && head_hi > n_q) {
+    const int slot = slots[t];
+    if (slot >= 0) {
       const int page = slot / page_size, off = slot - page * page_size;
       if (page >= num_pages) {
         if (threadIdx.x == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
-        return;
-      }
-      dst = cache_k + (((size_t)page * n_kv + (head - n_q)) * page_size + off) * d;
-    }
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      if (i < half) {
-        const float ang = pos * inv_freq[i];
-        float sn, cs;
-        sincosf(ang, &sn, &cs);
-        const float c = round_to<T>(cs), s = round_to<T>(sn);
-        const float lo = to_f32<T>(src[i]), hi = to_f32<T>(src[i + half]);
-        const float a = round_to<T>(round_to<T>(lo * c) - round_to<T>(hi * s));
-        const float b = round_to<T>(round_to<T>(hi * c) + round_to<T>(lo * s));
-        // Both halves are read before either is written: a thread owns the pair (i, i + half).
-        dst[i] = from_f32<T>(a);
-        dst[i + half] = from_f32<T>(b);
-      } else if (i >= rotary_dim) {
-        dst[i] = src[i];
+      } else {
+        cache_row = ((long long)page * n_kv * page_size + off) * d;
       }
     }
-  } else {
-    if (cache_v == nullptr) return;
-    const int slot = slots[t];
-    if (slot < 0) return;
-    const int page = slot / page_size, off = slot - page * page_size;
-    if (page >= num_pages) {
-      if (threadIdx.x == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
-      return;
+  }
+  const int items = (head_hi - head_lo) * d;
+  for (int e = threadIdx.x; e < items; e += blockDim.x) {
+    const int head = head_lo + e / d, i = e % d;
+    const size_t col0 = (size_t)head * d;
+    T* dst;
+    if (head < n_q) {
+      dst = partial ? q_out + (size_t)t * n_q * d + col0 : qkv + (size_t)t * row_stride + col0;
+    } else {
+      if (cache_row < 0) continue;
+      const bool is_k = head < n_q + n_kv;
+      const int kvh = is_k ? head - n_q : head - n_q - n_kv;
+      dst = (is_k ? cache_k : cache_v) + cache_row + (long long)kvh * page_size * d;
     }
-    T* dst = cache_v + (((size_t)page * n_kv + (head - n_q - n_kv)) * page_size + off) * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+    const int half = (head < n_q + n_kv) ? rotary_dim / 2 : 0;  // v is not rotated
+    if (i < half) {
+      const float ang = pos * inv_freq[i];
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+      const float c = round_to<T>(cs), sv = round_to<T>(sn);
+      // Both halves are read before either is written: a thread owns the pair (i, i + half).
+      const float lo = value(col0 + i), hi = value(col0 + i + half);
+      const float a = round_to<T>(round_to<T>(lo * c) - round_to<T>(hi * sv));
+      const float b = round_to<T>(round_to<T>(hi * c) + round_to<T>(lo * sv));
+      dst[i] = from_f32<T>(a);
+      dst[i + half] = from_f32<T>(b);
+    } else if (i >= 2 * half) {
+      dst[i] = from_f32<T>(value(col0 + i));
+    }
   }
 }
 
-LAB_EXPORT int lab_rope_kv_write(void* qkv, int row_stride, const int* positions, const float* inv_freq,
+LAB_EXPORT int lab_rope_kv_write(void* qkv, int row_stride, const float* partial, int splits, long long split_stride,
+                                 const void* bias, void* q_out, const int* positions, const float* inv_freq,
                                  int rotary_dim, const int* slots, void* cache_k, void* cache_v, int tokens, int n_q,
                                  int n_kv, int d, int page_size, int num_pages, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (rotary_dim % 2 || rotary_dim > d) return (int)cudaErrorInvalidValue;
-  dim3 grid(tokens, n_q + 2 * n_kv);
-  const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
+  if (partial && (q_out == nullptr || dtype == LAB_F32)) return (int)cudaErrorInvalidValue;
+  const int n_heads = n_q + 2 * n_kv;
+  const int heads_per_block = tokens >= 128 ? n_heads : 1;
+  dim3 grid(tokens, (n_heads + heads_per_block - 1) / heads_per_block);
+  const int threads = heads_per_block > 1 ? 256 : (d >= 128 ? 128 : (d >= 64 ? 64 : 32));
   if (dtype == LAB_F32)
-    rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, row_stride, positions, inv_freq, rotary_dim,
-                                                              slots, (float*)cache_k, (float*)cache_v, n_q, n_kv, d,
-                                                              page_size, num_pages);
-  else
-    rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-        (__nv_bfloat16*)qkv, row_stride, positions, inv_freq, rotary_dim, slots, (__nv_bfloat16*)cache_k,
-        (__nv_bfloat16*)cache_v, n_q, n_kv, d, page_size, num_pages);
-  LAB_LAUNCH_CHECK();
+    return (int)lab_launch(rope_kv_write_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, row_stride,
+                           partial, splits, (size_t)split_stride, (const float*)bias, (float*)q_out, positions,
+                           inv_freq, rotary_dim, slots, (float*)cache_k, (float*)cache_v, n_q, n_kv, d, page_size,
+                           num_pages, heads_per_block);
+  return (int)lab_launch(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)qkv,
+                         row_stride, partial, splits, (size_t)split_stride, (const __nv_bfloat16*)bias,
+                         (__nv_bfloat16*)q_out, positions, inv_freq, rotary_dim, slots, (__nv_bfloat16*)cache_k,
+                         (__nv_bfloat16*)cache_v, n_q, n_kv, d, page_size, num_pages, heads_per_block);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -199,6 +339,8 @@ LAB_EXPORT int lab_rope_kv_write(void* qkv, int row_stride, const int* positions
 // ----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / inter, c = i - t * inter;
@@ -214,9 +356,8 @@ LAB_EXPORT int lab_silu_mul(void* out, const void* gate_up, int tokens, int inte
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   if (dtype == LAB_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
-  else
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up,
-                                                                  inter, total);
-  LAB_LAUNCH_CHECK();
+    return (int)lab_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)out,
+                           (const float*)gate_up, inter, total);
+  return (int)lab_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out,
+                         (const __nv_bfloat16*)gate_up, inter, total);
 }

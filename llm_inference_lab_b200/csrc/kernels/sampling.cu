@@ -23,13 +23,23 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
-__global__ void __launch_bounds__(1024) sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits,
-                                                      long long ld, int vocab, const float* __restrict__ temperature,
-                                                      const uint32_t* __restrict__ seeds,
-                                                      const int* __restrict__ positions) {
+constexpr int CHUNK = 4096;   // vocabulary entries per block (the reference's argmax tile, kernels.rs:1489-1518)
+constexpr int THREADS = 256;
+
+// One block per (chunk of the vocabulary, row).  Each block leaves the best candidate of its
+// chunk in `part_val/part_idx`; the block that finishes last for a row (counted in
+// `counters`, which it sets back to zero) reduces the row's candidates and writes the token.
+__global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits,
+                                                         long long ld, int vocab, const float* __restrict__ temperature,
+                                                         const uint32_t* __restrict__ seeds,
+                                                         const int* __restrict__ positions, float* __restrict__ part_val,
+                                                         int* __restrict__ part_idx, int* __restrict__ counters) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  const int row = blockIdx.x;
+  __shared__ int is_last;
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.y, chunk = blockIdx.x, n_chunks = gridDim.x;
   const float* lr = logits + (size_t)row * ld;
   const float temp = temperature ? temperature[row] : 0.f;
   uint32_t key = 0;
@@ -40,7 +50,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(int* __restrict__ tokens, 
   }
   float bv = -INFINITY;
   int bi = INT_MAX;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  const int end = min(vocab, (chunk + 1) * CHUNK);
+  for (int i = chunk * CHUNK + threadIdx.x; i < end; i += THREADS) {
     float v = lr[i];
     if (temp > 0.f) {
       const uint32_t h = mix32(key + (uint32_t)i * 0x85EBCA6Bu);
@@ -49,34 +60,68 @@ __global__ void __launch_bounds__(1024) sample_kernel(int* __restrict__ tokens, 
     }
     if (better(v, i, bv, bi)) { bv = v; bi = i; }  // a NaN compares false and never wins
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-  }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
-  __syncthreads();
-  if (warp == 0) {
-    const int nw = (blockDim.x + 31) >> 5;
-    bv = lane < nw ? sv[lane] : -INFINITY;
-    bi = lane < nw ? si[lane] : INT_MAX;
+  auto block_best = [&]() {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) tokens[row] = bi;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+      bv = lane < THREADS / 32 ? sv[lane] : -INFINITY;
+      bi = lane < THREADS / 32 ? si[lane] : INT_MAX;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+      }
+    }
+  };
+  block_best();
+  if (n_chunks == 1) {
+    if (threadIdx.x == 0) tokens[row] = bi;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    part_val[(size_t)row * n_chunks + chunk] = bv;
+    part_idx[(size_t)row * n_chunks + chunk] = bi;
+    __threadfence();
+    is_last = atomicAdd(&counters[row], 1) == n_chunks - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  bv = -INFINITY;
+  bi = INT_MAX;
+  for (int c = threadIdx.x; c < n_chunks; c += THREADS) {
+    const float v = part_val[(size_t)row * n_chunks + c];
+    const int i = part_idx[(size_t)row * n_chunks + c];
+    if (better(v, i, bv, bi)) { bv = v; bi = i; }
+  }
+  block_best();
+  if (threadIdx.x == 0) {
+    tokens[row] = bi;
+    counters[row] = 0;   // ready for the next call
   }
 }
 }  // namespace
 
+LAB_EXPORT int lab_sample_chunks(int vocab) { return (vocab + CHUNK - 1) / CHUNK; }
+
 // temperature, seeds, positions: per row; temperature == nullptr or 0 means greedy.
+// scratch: rows * chunks floats (part_val), rows * chunks ints (part_idx), rows ints (counters, zero
+// before the first call; the kernel leaves them zero).  May be null when the vocabulary fits one chunk.
 LAB_EXPORT int lab_sample(int* tokens, const float* logits, long long ld, int rows, int vocab, const float* temperature,
-                          const uint32_t* seeds, const int* positions, cudaStream_t stream) {
+                          const uint32_t* seeds, const int* positions, float* part_val, int* part_idx, int* counters,
+                          cudaStream_t stream) {
   if (rows <= 0) return 0;
-  sample_kernel<<<rows, 1024, 0, stream>>>(tokens, logits, ld, vocab, temperature, seeds, positions);
-  LAB_LAUNCH_CHECK();
+  const int chunks = (vocab + CHUNK - 1) / CHUNK;
+  if (chunks > 1 && (!part_val || !part_idx || !counters)) return (int)cudaErrorInvalidValue;
+  return (int)lab_launch(sample_kernel, dim3(chunks, rows), dim3(THREADS), 0, stream, tokens, logits, ld, vocab,
+                         temperature, seeds, positions, part_val, part_idx, counters);
 }

@@ -128,20 +128,41 @@ def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, delta: torch.
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
                   slots: torch.Tensor | None, cache_k: torch.Tensor | None, cache_v: torch.Tensor | None,
-                  n_q: int, n_kv: int, head_dim: int) -> None:
-    """Rotate q (in place) and k, and write k and v to their cache slots."""
-    _on_gpu(qkv, positions, inv_freq, slots, cache_k, cache_v)
-    tokens = qkv.shape[0]
-    assert qkv.stride(1) == 1 and qkv.shape[1] == (n_q + 2 * n_kv) * head_dim
+                  n_q: int, n_kv: int, head_dim: int, bias: torch.Tensor | None = None,
+                  q_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate q and k, and write k and v to their cache slots.  Returns the rotated q.
+
+    `qkv` is the fused projection [tokens, (n_q + 2 n_kv) * d] rounded to the storage type (q is
+    rotated in place and the q columns are returned), or its 32-bit split-K partial products
+    [splits, tokens, ...] with `bias` still to add (rotated q goes to a new tensor).
+    """
+    _on_gpu(qkv, positions, inv_freq, slots, cache_k, cache_v, bias, q_out)
+    width = (n_q + 2 * n_kv) * head_dim
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2
     page_size = num_pages = 0
     if cache_k is not None:
         num_pages, kvh, page_size, d = cache_k.shape
         assert kvh == n_kv and d == head_dim and cache_k.is_contiguous() and cache_v.is_contiguous()
-        assert cache_k.dtype == qkv.dtype and cache_v.shape == cache_k.shape and slots is not None
-    _check(lib("rowwise").lab_rope_kv_write(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(inv_freq), rotary_dim,
-                                            _ptr(slots), _ptr(cache_k), _ptr(cache_v), tokens, n_q, n_kv, head_dim,
-                                            page_size, num_pages, dtype_code(qkv.dtype), _stream()), "rope_kv_write")
+        assert cache_v.shape == cache_k.shape and slots is not None
+    if qkv.dim() == 3:
+        splits, tokens = qkv.shape[0], qkv.shape[1]
+        assert qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[2] == width
+        dt = cache_k.dtype if cache_k is not None else torch.bfloat16
+        if q_out is None:
+            q_out = torch.empty((tokens, n_q * head_dim), dtype=dt, device=qkv.device)
+        _check(lib("rowwise").lab_rope_kv_write(
+            None, width, _ptr(qkv), splits, ctypes.c_longlong(tokens * width), _ptr(bias), _ptr(q_out),
+            _ptr(positions), _ptr(inv_freq), rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v), tokens, n_q, n_kv,
+            head_dim, page_size, num_pages, dtype_code(dt), _stream()), "rope_kv_write")
+        return q_out
+    tokens = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == width and bias is None
+    assert cache_k is None or cache_k.dtype == qkv.dtype
+    _check(lib("rowwise").lab_rope_kv_write(
+        _ptr(qkv), qkv.stride(0), None, 0, ctypes.c_longlong(0), None, None, _ptr(positions), _ptr(inv_freq),
+        rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v), tokens, n_q, n_kv, head_dim, page_size, num_pages,
+        dtype_code(qkv.dtype), _stream()), "rope_kv_write")
+    return qkv[:, : n_q * head_dim]
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -190,6 +211,23 @@ def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tenso
     return out
 
 
+_sample_scratch: dict = {}
+
+
+def _sample_buffers(device, rows: int, chunks: int):
+    """Scratch of the sampling kernel, kept per device (its counters must stay zero between calls)."""
+    key = str(device)
+    need = rows * chunks
+    buf = _sample_scratch.get(key)
+    if buf is None or buf[0].numel() < need or buf[2].numel() < rows:
+        cap_rows, cap = max(rows, 256), max(need, 256 * chunks)
+        buf = (torch.empty((cap,), dtype=torch.float32, device=device),
+               torch.empty((cap,), dtype=torch.int32, device=device),
+               torch.zeros((cap_rows,), dtype=torch.int32, device=device))
+        _sample_scratch[key] = buf
+    return buf
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seeds: torch.Tensor | None = None,
            positions: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """One token per row of 32-bit logits: greedy where temperature is 0 (or None), else Gumbel-max."""
@@ -201,8 +239,13 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seeds:
         assert temperature.numel() == rows and seeds.numel() == rows and positions.numel() == rows
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    _check(lib("sampling").lab_sample(_ptr(out), _ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab,
-                                      _ptr(temperature), _ptr(seeds), _ptr(positions), _stream()), "sample")
+    L = lib("sampling")
+    chunks = L.lab_sample_chunks(vocab)
+    pv = pi = cnt = None
+    if chunks > 1:
+        pv, pi, cnt = _sample_buffers(logits.device, rows, chunks)
+    _check(L.lab_sample(_ptr(out), _ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab, _ptr(temperature),
+                        _ptr(seeds), _ptr(positions), _ptr(pv), _ptr(pi), _ptr(cnt), _stream()), "sample")
     return out
 
 
@@ -282,11 +325,14 @@ def _pick_splits(T: int, n_out: int, K: int) -> int:
 
 def linear(x, w, bias=None, out_f32=False, allow_partial=False):
     """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
-    products [splits, tokens, out] that the following `add_rmsnorm` sums."""
+    products [splits, tokens, out], without the bias, that the consumer sums (`add_rmsnorm`,
+    `rope_kv_write`)."""
     if x.dtype == torch.float32 or _force_plain:
         return gemm_plain(x, w, bias, out_f32=out_f32)
-    splits = _pick_splits(x.shape[0], w.shape[0], x.shape[1]) if (allow_partial and bias is None) else 1
-    return gemm_tc(x, w, bias, out_f32=out_f32, splits=splits)
+    splits = _pick_splits(x.shape[0], w.shape[0], x.shape[1]) if allow_partial else 1
+    if splits > 1:
+        return gemm_tc(x, w, None, splits=splits)     # the consumer adds the bias
+    return gemm_tc(x, w, bias, out_f32=out_f32)
 
 
 def linear_gated(x, w_gate_up):
@@ -301,12 +347,14 @@ def attention_tc_supported(head_dim: int) -> bool:
 
 
 def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int) -> int:
-    """How many ways the keys of a decoding request are split across CTAs: enough CTAs to
-    fill the GPU, but at least 256 keys each (the reference splits 1..16 ways,
+    """How many ways the keys of a decoding request are split across CTAs.  A warp needs about
+    two microseconds per 32-key tile (its instructions depend on one another), so for latency a
+    CTA's four warps should get two tiles each at most: 256 keys per CTA, as far as the GPU has
+    room for the CTAs (the reference splits 1..16 ways,
     rust/engine/src/runner/model/qwen2/engine.rs:1597-1617)."""
     ctas = max(1, n_decode * n_kv * (-(-group // 16)))
-    want = max(1, (2 * SM_COUNT) // ctas)
-    return int(max(1, min(want, -(-max_kv_len // 256), 32)))
+    room = max(1, (4 * SM_COUNT) // ctas)
+    return int(max(1, min(room, -(-max_kv_len // 256), 32)))
 
 
 def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requests, q_lens, max_kv_len,

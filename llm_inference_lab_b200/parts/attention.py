@@ -59,10 +59,12 @@ class GQAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         group = ctx.groups[cache.group]
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
-        self.position.rotate_and_store(qkv, ctx.row_pos, group.row_slot, cache, self.n_q, self.n_kv, self.d)
-        attn = ops.attention(qkv[:, : self.n_q * self.d], cache.k, cache.v, ctx, group, self.n_q, self.n_kv, self.d,
-                             self.window, self.scale)
+        # With few tokens the product may come back as split-K partial sums (bias not yet added);
+        # the position encoding then sums them, adds the bias and rounds once.
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv, allow_partial=True)
+        q = self.position.rotate_and_store(qkv, ctx.row_pos, group.row_slot, cache, self.n_q, self.n_kv, self.d,
+                                           bias=self.b_qkv if qkv.dim() == 3 else None)
+        attn = ops.attention(q, cache.k, cache.v, ctx, group, self.n_q, self.n_kv, self.d, self.window, self.scale)
         return ops.linear(attn, self.w_o, self.b_o, allow_partial=self.b_o is None)
 
 

@@ -116,7 +116,11 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    def rotate_and_store(self, qkv, positions, slots, cache: CacheView, n_q: int, n_kv: int, head_dim: int) -> None:
+    def rotate_and_store(self, qkv, positions, slots, cache: CacheView, n_q: int, n_kv: int, head_dim: int,
+                         bias=None) -> torch.Tensor:
+        """Encodes q and k of the fused projection `qkv` ([tokens, (n_q + 2 n_kv) * d], or its
+        32-bit split-K partial products [splits, tokens, ...] with `bias` still to add), writes
+        k and v to the cache slots when the call may write, and returns the encoded q."""
         raise NotImplementedError
 
 

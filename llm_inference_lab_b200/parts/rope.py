@@ -20,10 +20,11 @@ class Rope(PositionEncoding):
         inv = np.power(float(spec["theta"]), -2.0 * i / self.rotary_dim).astype(np.float32)
         self.inv_freq = torch.from_numpy(inv).to(device)
 
-    def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim):
+    def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim, bias=None):
         write = cache is not None and cache.write
-        ops.rope_kv_write(qkv, positions, self.inv_freq, self.rotary_dim, slots if write else None,
-                          cache.k if write else None, cache.v if write else None, n_q, n_kv, head_dim)
+        return ops.rope_kv_write(qkv, positions, self.inv_freq, self.rotary_dim, slots if write else None,
+                                 cache.k if write else None, cache.v if write else None, n_q, n_kv, head_dim,
+                                 bias=bias)
 
 
 class NoPosition(PositionEncoding):
@@ -33,10 +34,11 @@ class NoPosition(PositionEncoding):
         super().__init__(spec, weights, dtype, device)
         self.inv_freq = torch.zeros((0,), dtype=torch.float32, device=device)
 
-    def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim):
+    def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim, bias=None):
         write = cache is not None and cache.write
-        if write:
-            ops.rope_kv_write(qkv, positions, self.inv_freq, 0, slots, cache.k, cache.v, n_q, n_kv, head_dim)
+        return ops.rope_kv_write(qkv, positions, self.inv_freq, 0, slots if write else None,
+                                 cache.k if write else None, cache.v if write else None, n_q, n_kv, head_dim,
+                                 bias=bias)
 
 
 register_part("position", "rope", Rope)

@@ -105,6 +105,29 @@ def test_rope_kv_write(dtype, n_q, n_kv, d, rot, theta):
     assert torch.equal(dq[:, (n_q + n_kv) * d:].cpu(), qkv[:, (n_q + n_kv) * d:])
 
 
+def test_rope_kv_write_from_split_k_partials():
+    """The fused projection may arrive as 32-bit split-K partial sums with the bias still to add:
+    the result equals summing, adding the bias, rounding once, and then the ordinary call."""
+    g = torch.Generator().manual_seed(31)
+    T, n_q, n_kv, d, ps, pages, theta = 9, 7, 1, 64, 8, 5, 1e6
+    width = (n_q + 2 * n_kv) * d
+    part = torch.randn(5, T, width, generator=g)
+    bias = torch.randn(width, generator=g).bfloat16()
+    pos = torch.arange(20, 20 + T, dtype=torch.int32)
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
+    inv = torch.from_numpy(np.power(theta, -2.0 * np.arange(d // 2) / d).astype(np.float32))
+    caches = [torch.zeros((pages, n_kv, ps, d), dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    q1 = ops().rope_kv_write(part.to(DEV), pos.to(DEV), inv.to(DEV), d, slots.to(DEV), caches[0], caches[1], n_q, n_kv,
+                             d, bias=bias.to(DEV))
+    summed = part[0]
+    for s in range(1, 5):
+        summed = summed + part[s]
+    qkv = (summed + bias.float()).bfloat16().to(DEV)
+    q2 = ops().rope_kv_write(qkv, pos.to(DEV), inv.to(DEV), d, slots.to(DEV), caches[2], caches[3], n_q, n_kv, d)
+    assert q1.shape == (T, n_q * d) and torch.equal(q1, q2)
+    assert torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(1, 5, 3), (7, 130, 65), (70, 33, 200), (129, 64, 48)])
 def test_gemm_plain_exact(dtype, M, N, K):
@@ -144,6 +167,9 @@ GEMM_TC_SHAPES = [
     (300, 504, 200, False, True, False, 128, 1),
     (513, 300, 320, False, False, False, 256, 1),
     (5, 200, 104, True, False, None, None, 1),
+    (1, 4864, 896, True, False, None, None, 1),
+    (100, 72, 64, True, False, True, 128, 1),
+    (200, 136, 200, True, False, True, 256, 1),
     (333, 200, 104, True, False, False, 64, 1),
     (260, 520, 72, True, False, False, 256, 1),
     (9, 136, 1000, False, False, None, None, 5),
