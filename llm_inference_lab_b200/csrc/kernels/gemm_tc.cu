@@ -19,9 +19,11 @@
 // accumulator row holds both; in swapped orientation a tile's M side is 64 gate rows over 64 up
 // rows of the same features, and the epilogue warps exchange them through shared memory.
 //
-// One CTA computes one output tile: warp 0 issues TMA loads into a ring of stages, warp 1
-// issues the MMAs (one elected lane) and owns the tensor-memory allocation, warps 2-5 read
-// the accumulator back (each its quarter of the 128 lanes) and apply the epilogue.  Every
+// CTAs are persistent (one per SM at most) and walk the output tiles: warp 0 issues TMA loads
+// into a ring of stages that runs on across tiles, warp 1 issues the MMAs (one elected lane)
+// into one of two accumulators in tensor memory and owns the allocation, warps 2-5 read an
+// accumulator back (each its quarter of the 128 lanes) and apply the epilogue while the MMAs
+// of the next tile fill the other accumulator.  Every
 // wait on an mbarrier is bounded: when it runs out the kernel records an error code, lets
 // the other roles drain and frees its tensor memory before it returns.
 //
@@ -144,11 +146,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive accumulator columns of this thread's lane; the registers are valid after tmem_wait().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// T(silu(T(g))) * T(u) with the roundings of the reference (kernels.rs:1469-1486); exp and the
+// division use the hardware approximations (relative error about 2^-21, far below bfloat16's 2^-9).
 __device__ __forceinline__ float silu_gate(float g, float u) {
   g = bf16_round(g);
   u = bf16_round(u);
-  return bf16_round(g / (1.f + expf(-g))) * u;
+  return bf16_round(__fdividef(g, 1.f + __expf(-g))) * u;
 }
 
 struct Params {
@@ -161,52 +178,57 @@ struct Params {
   int k_tiles;          // k-tiles in total
   int k_tiles_per_split;
   int up_offset;        // gated: row offset of the "up" half inside the weight matrix
+  int m_tiles, n_tiles, splits;  // tiles on the M side, on the N side, and split-K planes
 };
 
 template <int BN, bool GATED, bool SWAP>
 struct Shape {
-  static constexpr int A_TILES = 1;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int ACC_COLS = BN;
-  static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-  // gated + swapped: the epilogue exchanges gate and up values through the (by then idle) stages
-  static_assert(!(GATED && SWAP) || STAGES * STAGE_BYTES >= BM * (BN + 1) * 4, "exchange buffer must fit");
+  // gated + swapped: the epilogue warps exchange gate and up values through a buffer of their own
+  static constexpr int EXCHANGE_BYTES = (GATED && SWAP) ? ((BM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
+  static constexpr int STAGES_RAW = (SMEM_BUDGET - EXCHANGE_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+  static constexpr int ACC_COLS = BN < 32 ? 32 : BN;
+  static constexpr int ACC_BUFS = 2 * ACC_COLS <= 512 ? 2 : 1;  // accumulators in tensor memory
+  static constexpr int TMEM_COLS = ACC_BUFS * ACC_COLS;         // a power of two >= 32
+  static constexpr int SMEM = STAGES * STAGE_BYTES + EXCHANGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(STAGES >= 2, "the tile does not leave room for a pipeline");
 };
 
+// A persistent CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Tiles are numbered with
+// the M side fastest, so CTAs that run at the same time share the N-side operand in L2.
+// Two accumulators in tensor memory let the epilogue of one tile run beside the MMAs of the next.
 template <int BN, bool GATED, bool SWAP, typename OutT>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_b, Params p) {
   using S = Shape<BN, GATED, SWAP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES);
+  float* exchange = reinterpret_cast<float*>(tiles + S::STAGES * S::STAGE_BYTES);
+  uint64_t* full = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES + S::EXCHANGE_BYTES);
   uint64_t* empty = full + S::STAGES;
-  uint64_t* acc_full = empty + S::STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  uint64_t* acc_full = empty + S::STAGES;       // [ACC_BUFS]
+  uint64_t* acc_empty = acc_full + 2;           // [ACC_BUFS]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int M_ROWS = (GATED && SWAP) ? BM / 2 : BM;  // output rows (features) per tile on the M side
-  const int m0 = blockIdx.x * M_ROWS;
-  const int n_tile_rows = (GATED && !SWAP) ? BN / 2 : BN;  // rows of the N-side operand per tile
-  const int n0 = blockIdx.y * n_tile_rows;
-  const int kt0 = blockIdx.z * p.k_tiles_per_split;
-  int kt1 = kt0 + p.k_tiles_per_split;
-  if (kt1 > p.k_tiles) kt1 = p.k_tiles;
-  const int n_kt = kt1 - kt0;
+  constexpr int M_ROWS = (GATED && SWAP) ? BM / 2 : BM;    // output rows per tile on the M side
+  constexpr int N_ROWS = (GATED && !SWAP) ? BN / 2 : BN;   // rows of the N-side operand per tile
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_full, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -216,54 +238,73 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // tile index -> (row on the M side, row on the N side, first k-tile, number of k-tiles)
+  auto locate = [&](int tile, int& m0, int& n0, int& kt0, int& n_kt, int& split) {
+    const int mt = tile % p.m_tiles;
+    const int rest = tile / p.m_tiles;
+    const int nt = rest % p.n_tiles;
+    split = rest / p.n_tiles;
+    m0 = mt * M_ROWS;
+    n0 = nt * N_ROWS;
+    kt0 = split * p.k_tiles_per_split;
+    int kt1 = kt0 + p.k_tiles_per_split;
+    if (kt1 > p.k_tiles) kt1 = p.k_tiles;
+    n_kt = kt1 > kt0 ? kt1 - kt0 : 0;
+  };
+
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: TMA loads ----
       // Weights do not depend on earlier kernels of the step: the first stages' weight tiles are
       // requested before the wait on the predecessor, the activation tiles after it.
-      auto load_weights = [&](int s, int kx) {
+      auto load_weights = [&](int s, int kx, int m0, int n0) {
         uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
         uint8_t* b_dst = a_dst + S::A_BYTES;
         if (SWAP) {
-          if (GATED) {
-            tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
-            tma_load_2d(a_dst + (BM / 2) * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
-          } else {
-            tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
-          }
+          tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
+          if (GATED) tma_load_2d(a_dst + (BM / 2) * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
         } else {
           tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
           if (GATED) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kx, p.up_offset + n0);
         }
       };
-      auto load_activations = [&](int s, int kx) {
+      auto load_activations = [&](int s, int kx, int m0, int n0) {
         uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
         if (SWAP) tma_load_2d(a_dst + S::A_BYTES, &map_b, &full[s], kx, n0);
         else tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
       };
-      int issued = 0;
-      const int ahead = n_kt < S::STAGES ? n_kt : S::STAGES;
-      for (int i = 0; i < ahead; ++i) {  // the ring is empty: no wait
-        mbar_expect_tx(&full[i], S::STAGE_BYTES);
-        load_weights(i, (kt0 + i) * BK);
+      int it = 0;  // stages filled so far, over all tiles
+      bool first_tile = true, alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        int m0, n0, kt0, n_kt, split;
+        locate(tile, m0, n0, kt0, n_kt, split);
+        int i = 0;
+        if (first_tile) {
+          const int ahead = n_kt < S::STAGES ? n_kt : S::STAGES;
+          for (; i < ahead; ++i) {  // the ring is empty: no wait
+            mbar_expect_tx(&full[i], S::STAGE_BYTES);
+            load_weights(i, (kt0 + i) * BK, m0, n0);
+          }
+          pdl_wait();
+          for (int j = 0; j < ahead; ++j) load_activations(j, (kt0 + j) * BK, m0, n0);
+          it = ahead;
+          first_tile = false;
+        }
+        for (; i < n_kt; ++i, ++it) {
+          const int s = it % S::STAGES;
+          const uint32_t ph = (it / S::STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { alive = false; break; }
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          const int kx = (kt0 + i) * BK;
+          load_weights(s, kx, m0, n0);
+          load_activations(s, kx, m0, n0);
+        }
       }
-      pdl_wait();
-      for (int i = 0; i < ahead; ++i) load_activations(i, (kt0 + i) * BK);
-      issued = ahead;
-      for (int i = ahead; i < n_kt; ++i) {
-        const int s = i % S::STAGES;
-        const uint32_t ph = (i / S::STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        mbar_expect_tx(&full[s], S::STAGE_BYTES);
-        const int kx = (kt0 + i) * BK;
-        load_weights(s, kx);
-        load_activations(s, kx);
-        issued = i + 1;
-      }
+      if (first_tile) pdl_wait();
       if (*abort_flag) {
         // Let copies in flight land before the CTA's shared memory goes away.
-        const int first = issued > S::STAGES ? issued - S::STAGES : 0;
-        for (int i = first; i < issued; ++i) {
+        const int first = it > S::STAGES ? it - S::STAGES : 0;
+        for (int i = first; i < it; ++i) {
           const uint64_t t0 = global_timer_ns();
           while (!mbar_try_wait(&full[i % S::STAGES], (i / S::STAGES) & 1) && global_timer_ns() - t0 < 100000000ull) {
           }
@@ -274,137 +315,201 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     if (lane == 0) {
       // ---- MMA issuer ----
       constexpr uint32_t idesc = instr_desc(BN);
+      int it = 0, local = 0;
       bool ok = true;
-      for (int i = 0; i < n_kt && ok; ++i) {
-        const int s = i % S::STAGES;
-        const uint32_t ph = (i / S::STAGES) & 1;
-        ok = mbar_wait(&full[s], ph, abort_flag);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        int m0, n0, kt0, n_kt, split;
+        locate(tile, m0, n0, kt0, n_kt, split);
+        const int buf = local % S::ACC_BUFS;
+        const uint32_t use = (uint32_t)(local / S::ACC_BUFS);
+        // the epilogue must have drained this accumulator (passes at once on its first use)
+        ok = mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + S::A_BYTES;
+        const uint32_t acc_addr = tmem_base + buf * S::ACC_COLS;
+        for (int i = 0; i < n_kt; ++i, ++it) {
+          const int s = it % S::STAGES;
+          const uint32_t ph = (it / S::STAGES) & 1;
+          ok = mbar_wait(&full[s], ph, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint64_t db = smem_desc_sw128(b_addr + k * UMMA_K * 2);
-          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-          umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, acc);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(acc_addr, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
+                      idesc, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
-        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+        umma_commit(&acc_full[buf]);  // the accumulator is complete once every MMA has retired
       }
-      umma_commit(acc_full);     // the accumulator is complete once every MMA has retired
     }
   } else {
     // ---- epilogue: warps 2..5, each reads its quarter of the 128 accumulator lanes ----
     const int quarter = warp & 3;
     pdl_wait();  // the output may still be read by an earlier kernel until it has completed
-    const bool ok = n_kt > 0 ? mbar_wait(acc_full, 0, abort_flag) : true;
-    tc_fence_after();
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const int m = m0 + quarter * 32 + lane;  // this thread's row on the M side
-    const bool partial = p.split_stride != 0;
-    // Decided once per thread; the gated swapped epilogue meets at a named barrier, which every
-    // epilogue thread reaches whatever it decided.
-    const bool go = ok && !*abort_flag;
-    if (go || (SWAP && GATED)) {
-      if (!SWAP) {
-        // thread = token row m; columns = output features
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      int m0, n0, kt0, n_kt, split;
+      locate(tile, m0, n0, kt0, n_kt, split);
+      const int buf = local % S::ACC_BUFS;
+      const uint32_t use = (uint32_t)(local / S::ACC_BUFS);
+      const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag);
+      tc_fence_after();
+      const uint32_t lane_addr = tmem_base + buf * S::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      const int m = m0 + quarter * 32 + lane;  // this thread's row on the M side
+      const bool partial = p.split_stride != 0;
+      // Decided once per thread; the gated swapped epilogue meets at named barriers, which every
+      // epilogue thread reaches whatever it decided.
+      const bool go = __all_sync(0xffffffffu, ok && !*abort_flag);
+      bool released = false;
+      auto release = [&]() {  // the accumulator has been read: the MMA warp may overwrite it (once per tile)
+        if (released) return;
+        released = true;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+      };
+      if constexpr (!SWAP) {
+        // thread = token row m; columns = output features, 32 at a time
         constexpr int OUT_COLS = GATED ? BN / 2 : BN;
-        const int nbase = blockIdx.y * OUT_COLS;
+        static_assert(OUT_COLS % 32 == 0, "normal orientation works on 32 output columns at a time");
+        const int nbase = (n0 / N_ROWS) * OUT_COLS;
 #pragma unroll 1
-        for (int c = 0; c < OUT_COLS / 16; ++c) {
+        for (int c = 0; c < OUT_COLS / 32 && go; ++c) {
+          uint32_t r[32];
+          float v[32];
+          if (n_kt > 0) {
+            tmem_ld32_issue(lane_addr + c * 32, r);
+            if (GATED) {
+              uint32_t ru[32];
+              tmem_ld32_issue(lane_addr + BN / 2 + c * 32, ru);
+              tmem_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = silu_gate(__uint_as_float(r[j]), __uint_as_float(ru[j]));
+            } else {
+              tmem_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+          if (c == OUT_COLS / 32 - 1) release();
+          const int n = nbase + c * 32;
+          if (m >= p.m_rows || n >= p.n_rows) continue;
+          if (partial) {
+            float* dst = (float*)p.out + split * p.split_stride + (size_t)m * p.ld_out + n;
+            if (n + 32 <= p.n_rows && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n + j < p.n_rows) dst[j] = v[j];
+            }
+          } else {
+            if (p.bias) {
+              if (n + 32 <= p.n_rows && (((uintptr_t)(p.bias + n)) & 15) == 0) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                  const uint4 raw = reinterpret_cast<const uint4*>(p.bias + n)[q4];
+                  const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(hb[e]);
+                    v[q4 * 8 + 2 * e] += f.x;
+                    v[q4 * 8 + 2 * e + 1] += f.y;
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (n + j < p.n_rows) v[j] += __bfloat162float(p.bias[n + j]);
+              }
+            }
+            OutT* dst = (OutT*)p.out + (size_t)m * p.ld_out + n;
+            if (n + 32 <= p.n_rows && (((uintptr_t)dst) & 15) == 0) {
+              if (sizeof(OutT) == 2) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                  uint32_t w[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v[q4 * 8 + 2 * e], v[q4 * 8 + 2 * e + 1]);
+                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                  }
+                  reinterpret_cast<uint4*>(dst)[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n + j < p.n_rows) dst[j] = from_f32<OutT>(v[j]);
+            }
+          }
+        }
+        release();
+      } else if constexpr (GATED) {
+        // thread = output feature; columns = tokens.  Lanes 0..63 hold gate values, lanes 64..127
+        // the up values of the same 64 features: all go through the exchange buffer, then each of
+        // the 128 threads finishes one feature for half of the tokens.
+        const int lane_global = quarter * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < BN / 16 && go; ++c) {
+          if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
+          float v[16];
+          tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) exchange[lane_global * (BN + 1) + c * 16 + j] = v[j];
+        }
+        release();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int t = threadIdx.x - 64, f = t & 63, h = t >> 6;
+        if (go && m0 + f < p.m_rows) {
+          __nv_bfloat16* dst = (__nv_bfloat16*)p.out + m0 + f;
+          for (int col = h * (BN / 2); col < (h + 1) * (BN / 2); ++col) {
+            const int tok = n0 + col;
+            if (tok >= p.n_rows) break;
+            dst[(size_t)tok * p.ld_out] =
+                __float2bfloat16_rn(silu_gate(exchange[f * (BN + 1) + col], exchange[(64 + f) * (BN + 1) + col]));
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
+      } else {
+        // thread = output feature m; columns = tokens
+        const float b = (p.bias && !partial && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
+        int c = 0;
+#pragma unroll 1
+        for (; c < BN / 16 && go; ++c) {
+          const int t = n0 + c * 16;
+          if (t >= p.n_rows) break;  // same for the whole warp
           float v[16];
           if (n_kt > 0) tmem_ld16(lane_addr + c * 16, v);
           else
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          if (GATED) {
-            float u[16];
-            tmem_ld16(lane_addr + BN / 2 + c * 16, u);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_gate(v[j], u[j]);
-          }
-          const int n = nbase + c * 16;
-          if (m >= p.m_rows || n >= p.n_rows) continue;
+          if (c == BN / 16 - 1 || t + 16 >= p.n_rows) release();
+          if (m >= p.m_rows) continue;
           if (partial) {
-            float* dst = (float*)p.out + blockIdx.z * p.split_stride + (size_t)m * p.ld_out + n;
+            float* dst = (float*)p.out + split * p.split_stride + m;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (n + j < p.n_rows) dst[j] = v[j];
+              if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = v[j];
           } else {
-            if (p.bias)
+            OutT* dst = (OutT*)p.out + m;
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (n + j < p.n_rows) v[j] += __bfloat162float(p.bias[n + j]);
-            OutT* dst = (OutT*)p.out + (size_t)m * p.ld_out + n;
-            if (sizeof(OutT) == 2 && n + 16 <= p.n_rows && (((uintptr_t)dst) & 15) == 0) {
-              uint32_t w[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                w[j] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-              reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (n + j < p.n_rows) dst[j] = from_f32<OutT>(v[j]);
-            }
+            for (int j = 0; j < 16; ++j)
+              if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(v[j] + b);
           }
         }
-      } else {
-        // thread = output feature m; columns = tokens
-        if (GATED) {
-          // lanes 0..63 hold gate values, lanes 64..127 the up values of the same 64 features:
-          // all go through shared memory (the pipeline stages are idle by now), then each of the
-          // 128 threads finishes one feature for half of the tokens.
-          float* ex = reinterpret_cast<float*>(tiles);
-          const int lane_global = quarter * 32 + lane;
-          const bool go_warp = __all_sync(0xffffffffu, go);
-#pragma unroll 1
-          for (int c = 0; c < BN / 16 && go_warp; ++c) {
-            if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
-            float v[16];
-            tmem_ld16(lane_addr + c * 16, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) ex[lane_global * (BN + 1) + c * 16 + j] = v[j];
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          const int t = threadIdx.x - 64, f = t & 63, h = t >> 6;
-          if (go && m0 + f < p.m_rows) {
-            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + m0 + f;
-            for (int col = h * (BN / 2); col < (h + 1) * (BN / 2); ++col) {
-              const int tok = n0 + col;
-              if (tok >= p.n_rows) break;
-              dst[(size_t)tok * p.ld_out] =
-                  __float2bfloat16_rn(silu_gate(ex[f * (BN + 1) + col], ex[(64 + f) * (BN + 1) + col]));
-            }
-          }
-        } else {
-          const float b = (p.bias && !partial && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
-#pragma unroll 1
-          for (int c = 0; c < BN / 16; ++c) {
-            const int t = n0 + c * 16;
-            if (t >= p.n_rows) break;  // same for the whole warp
-            float v[16];
-            if (n_kt > 0) tmem_ld16(lane_addr + c * 16, v);
-            else
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = 0.f;
-            if (m >= p.m_rows) continue;
-            if (partial) {
-              float* dst = (float*)p.out + blockIdx.z * p.split_stride + m;
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = v[j];
-            } else {
-              OutT* dst = (OutT*)p.out + m;
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (t + j < p.n_rows) dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(v[j] + b);
-            }
-          }
-        }
+        release();
       }
     }
   }
@@ -504,14 +609,29 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
     if ((rc = make_map(&mb, w, w_rows, K, K, box_b))) return rc;
     p.m_rows = tokens;
     p.n_rows = n_out;
-    grid = dim3((tokens + BM - 1) / BM, (n_out + box_b - 1) / box_b, splits);
+    p.m_tiles = (tokens + BM - 1) / BM;
+    p.n_tiles = (n_out + box_b - 1) / box_b;
   } else {
     const int m_rows_tile = gated ? BM / 2 : BM;
     if ((rc = make_map(&ma, w, w_rows, K, K, m_rows_tile))) return rc;
     if ((rc = make_map(&mb, x, tokens, K, ldx, bn))) return rc;
+    if (gated && bn > 64) return (int)cudaErrorInvalidValue;  // the exchange buffer is sized for up to 64 tokens
     p.m_rows = n_out;
     p.n_rows = tokens;
-    grid = dim3((n_out + m_rows_tile - 1) / m_rows_tile, (tokens + bn - 1) / bn, splits);
+    p.m_tiles = (n_out + m_rows_tile - 1) / m_rows_tile;
+    p.n_tiles = (tokens + bn - 1) / bn;
+  }
+  p.splits = splits;
+  {
+    static int sm_count = 0;
+    if (sm_count == 0) {
+      int dev = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+        sm_count = 148;
+    }
+    const long long tiles = (long long)p.m_tiles * p.n_tiles * splits;
+    grid = dim3((unsigned)(tiles < sm_count ? tiles : sm_count));
   }
   // A gated tile whose "gate" rows run past n_out would read "up" rows as gate: tiles are cut so
   // that valid outputs never mix the halves (rows >= n_out are masked in the epilogue), but the
@@ -519,7 +639,12 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
   if (gated) {
     if (swap) {
       if (out_f32) return (int)cudaErrorInvalidValue;
-      return dispatch_bn<true, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+      switch (bn) {
+        case 16: return launch<16, true, true, __nv_bfloat16>(ma, mb, p, grid, stream);
+        case 32: return launch<32, true, true, __nv_bfloat16>(ma, mb, p, grid, stream);
+        case 64: return launch<64, true, true, __nv_bfloat16>(ma, mb, p, grid, stream);
+      }
+      return (int)cudaErrorInvalidValue;
     }
     if (out_f32) return (int)cudaErrorInvalidValue;
     return dispatch_bn<true, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);

@@ -284,11 +284,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
     if x.data_ptr() % 16 or w.data_ptr() % 16:
         raise KernelError("gemm_tc: operands must start on a 16-byte boundary")
     if swap is None:
-        swap = T <= 128
+        swap = T <= (64 if gated else 128)
     if bn is None:
         if swap:
             bn = 16
-            while bn < min(T, 256):
+            while bn < min(T, 64 if gated else 256):
                 bn *= 2
         else:
             bn = 256 if gated else 128

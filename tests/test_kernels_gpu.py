@@ -168,8 +168,11 @@ GEMM_TC_SHAPES = [
     (513, 300, 320, False, False, False, 256, 1),
     (5, 200, 104, True, False, None, None, 1),
     (1, 4864, 896, True, False, None, None, 1),
-    (100, 72, 64, True, False, True, 128, 1),
-    (200, 136, 200, True, False, True, 256, 1),
+    (100, 72, 64, True, False, True, 64, 1),
+    (40, 136, 200, True, False, True, 64, 1),
+    (3000, 1000, 136, False, True, False, 128, 1),
+    (700, 2600, 72, True, False, False, 256, 1),
+    (20, 20000, 64, False, False, True, 32, 1),
     (333, 200, 104, True, False, False, 64, 1),
     (260, 520, 72, True, False, False, 256, 1),
     (9, 136, 1000, False, False, None, None, 5),
