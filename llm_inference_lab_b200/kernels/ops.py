@@ -394,6 +394,66 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     return out
 
 
+# The fused decode attention (rotation + cache write + attention + merge in one kernel) is built and
+# tested, but off by default: with programmatic dependent launch hiding launch latency, the separate
+# rope, attention and merge kernels measured faster at the benchmark's sizes (1.05 ms against
+# 1.15 ms per decode step at batch 8), because every split repeats the rotation of q before its
+# first tile and the merge waits on an atomic counter.
+FUSE_DECODE_ATTENTION = False
+_decode_counters: dict = {}
+
+
+def _counters(device, n: int) -> torch.Tensor:
+    """Zeroed counters the fused decode attention leaves zero (kept per device)."""
+    key = str(device)
+    buf = _decode_counters.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros((max(n, 4096),), dtype=torch.int32, device=device)
+        _decode_counters[key] = buf
+    return buf
+
+
+def decode_fusable(dtype, head_dim: int, n_q: int, n_kv: int) -> bool:
+    return (dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim)
+            and n_q % n_kv == 0 and n_q // n_kv <= 16)
+
+
+def attention_decode_fused(qkv, bias, inv_freq, rotary_dim, slots, cache_k, cache_v, q_start, kv_len, block_table,
+                           n_requests, max_kv_len, n_q, n_kv, head_dim, window, scale, out=None, splits=None):
+    """A pure-decode step's attention with its prologue fused in: sum of the fused projection's
+    split-K partial products and bias (or the rounded projection), rotary encoding of q and of the
+    newest k, write of the newest k and v into their cache slots, attention, merge of the splits."""
+    _on_gpu(qkv, bias, inv_freq, slots, cache_k, cache_v, q_start, kv_len, block_table)
+    width = (n_q + 2 * n_kv) * head_dim
+    num_pages, kvh, page_size, d = cache_k.shape
+    assert kvh == n_kv and d == head_dim and cache_k.dtype == torch.bfloat16 and cache_k.is_contiguous()
+    partial = qkv.dim() == 3
+    tokens = qkv.shape[1] if partial else qkv.shape[0]
+    assert tokens == n_requests and qkv.shape[-1] == width and inv_freq.numel() == rotary_dim // 2
+    if out is None:
+        out = torch.empty((tokens, n_q * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    if splits is None:
+        span = min(max_kv_len, window) if window else max_kv_len
+        splits = decode_splits(n_requests, n_kv, n_q // n_kv, span)
+    scratch = counters = None
+    if splits > 1:
+        scratch = torch.empty((n_requests * n_q * splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
+        counters = _counters(qkv.device, n_requests * n_kv)
+    L = lib("attention_tc", {"LAB_HEAD_DIM": head_dim})
+    if partial:
+        assert qkv.dtype == torch.float32 and qkv.is_contiguous()
+        args = (None, width, _ptr(qkv), qkv.shape[0], ctypes.c_longlong(tokens * width), _ptr(bias))
+    else:
+        assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and bias is None
+        args = (_ptr(qkv), qkv.stride(0), None, 0, ctypes.c_longlong(0), None)
+    _check(L.lab_attention_decode_fused(
+        _ptr(out), out.stride(0), *args, _ptr(inv_freq), rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v),
+        _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1], n_requests, n_q, n_kv, page_size,
+        num_pages, window, ctypes.c_float(scale), splits, _ptr(scratch), _ptr(counters), _stream()),
+        "attention_decode_fused")
+    return out
+
+
 def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale):
     if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim):
         return attention_tc(q, cache_k, cache_v, ctx.q_start, ctx.kv_len, ctx.pos0, group.block_table,

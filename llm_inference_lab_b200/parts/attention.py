@@ -62,6 +62,15 @@ class GQAttention(Mixer):
         # With few tokens the product may come back as split-K partial sums (bias not yet added);
         # the position encoding then sums them, adds the bias and rounds once.
         qkv = ops.linear(x, self.w_qkv, self.b_qkv, allow_partial=True)
+        rotary = getattr(self.position, "rotary", None)
+        if (ops.FUSE_DECODE_ATTENTION and ctx.max_q_len == 1 and cache.write and rotary is not None
+                and ops.decode_fusable(qkv.dtype if qkv.dim() == 2 else cache.k.dtype, self.d, self.n_q, self.n_kv)):
+            # Every request brings one token: rotation, cache write and attention run as one kernel.
+            attn = ops.attention_decode_fused(
+                qkv, self.b_qkv if qkv.dim() == 3 else None, rotary[0], rotary[1], group.row_slot, cache.k, cache.v,
+                ctx.q_start, ctx.kv_len, group.block_table, ctx.n_requests, ctx.max_kv_len, self.n_q, self.n_kv,
+                self.d, self.window, self.scale)
+            return ops.linear(attn, self.w_o, self.b_o, allow_partial=self.b_o is None)
         q = self.position.rotate_and_store(qkv, ctx.row_pos, group.row_slot, cache, self.n_q, self.n_kv, self.d,
                                            bias=self.b_qkv if qkv.dim() == 3 else None)
         attn = ops.attention(q, cache.k, cache.v, ctx, group, self.n_q, self.n_kv, self.d, self.window, self.scale)

@@ -19,6 +19,8 @@ class Rope(PositionEncoding):
         i = np.arange(self.rotary_dim // 2, dtype=np.float64)
         inv = np.power(float(spec["theta"]), -2.0 * i / self.rotary_dim).astype(np.float32)
         self.inv_freq = torch.from_numpy(inv).to(device)
+        # (inverse frequencies, rotary width): lets a mixer hand the rotation to a fused kernel
+        self.rotary = (self.inv_freq, self.rotary_dim)
 
     def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim, bias=None):
         write = cache is not None and cache.write
@@ -33,6 +35,7 @@ class NoPosition(PositionEncoding):
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)
         self.inv_freq = torch.zeros((0,), dtype=torch.float32, device=device)
+        self.rotary = (self.inv_freq, 0)
 
     def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim, bias=None):
         write = cache is not None and cache.write

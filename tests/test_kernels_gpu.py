@@ -335,6 +335,52 @@ def test_attention_decode_splits(splits):
         assert rel_err(g, w) < 2e-2
 
 
+@pytest.mark.parametrize("partial", [False, True])
+@pytest.mark.parametrize("n_q,n_kv,d,ps,window,rot,kvs,splits", [
+    (14, 2, 64, 16, 0, 64, [640, 33, 1, 257], None), (6, 1, 32, 8, 0, 32, [100, 7], 3),
+    (3, 3, 48, 8, 20, 48, [100, 19, 20, 21], None), (8, 2, 128, 32, 0, 64, [1000, 96], 4),
+    (4, 2, 16, 4, 0, 0, [9, 30], 2)])
+def test_attention_decode_fused(partial, n_q, n_kv, d, ps, window, rot, kvs, splits):
+    """The fused decode kernel (partial sums + bias + rotation + cache write + attention + merge)
+    gives what the separate kernels give, and leaves the same cache behind."""
+    rng = np.random.default_rng(5)
+    B = len(kvs)
+    requests = [(kv, 1) for kv in kvs]
+    ck, cv, bt, ks, vs = build_paged(rng, requests, n_kv, d, ps, torch.bfloat16)
+    width = (n_q + 2 * n_kv) * d
+    part = torch.from_numpy(rng.standard_normal((4, B, width)).astype(np.float32))
+    bias = torch.from_numpy(rng.standard_normal(width).astype(np.float32)).bfloat16()
+    qkv_sum = part[0]
+    for s in range(1, 4):
+        qkv_sum = qkv_sum + part[s]
+    qkv = (qkv_sum + bias.float()).bfloat16()
+    inv = torch.from_numpy(np.power(1e4, -2.0 * np.arange(rot // 2) / max(rot, 1)).astype(np.float32))
+    kv_len = torch.tensor(kvs, dtype=torch.int32)
+    pos = kv_len - 1
+    blocks = torch.from_numpy(bt)
+    slots = torch.tensor([int(bt[b, (kv - 1) // ps]) * ps + (kv - 1) % ps for b, kv in enumerate(kvs)],
+                         dtype=torch.int32)
+    q_start = torch.arange(B + 1, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    dev = lambda a: a.to(DEV)  # noqa: E731
+    # separate kernels
+    ck1, cv1 = ck.clone().to(DEV), cv.clone().to(DEV)
+    q1 = ops().rope_kv_write(dev(qkv.clone()), dev(pos), dev(inv), rot, dev(slots), ck1, cv1, n_q, n_kv, d)
+    want = ops().attention_tc(q1, ck1, cv1, dev(q_start), dev(kv_len), dev(pos), dev(blocks), B, [1] * B, max(kvs),
+                              n_q, n_kv, d, window, scale, splits=splits)
+    # fused, twice in a row (the counters must come back to zero)
+    for _ in range(2):
+        ck2, cv2 = ck.clone().to(DEV), cv.clone().to(DEV)
+        src = dev(part) if partial else dev(qkv)
+        got = ops().attention_decode_fused(src, dev(bias) if partial else None, dev(inv), rot, dev(slots), ck2, cv2,
+                                           dev(q_start), dev(kv_len), dev(blocks), B, max(kvs), n_q, n_kv, d, window,
+                                           scale, splits=splits)
+        ops().take_device_errors()
+        held = torch.isfinite(ck1.float()) | torch.isfinite(ck2.float())
+        assert torch.equal(ck1[held], ck2[held]) and torch.equal(cv1[held], cv2[held]), "same cache contents"
+        assert rel_err(got, want.double()) < 2e-2
+
+
 @pytest.mark.parametrize("kind,dtype", [("plain", torch.float32), ("plain", torch.bfloat16), ("tc", torch.bfloat16)])
 @pytest.mark.parametrize("needle", ["first", "page_end", "page_start", "last", "window_first", "window_out"])
 def test_attention_needle(kind, dtype, needle):
