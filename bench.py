@@ -223,6 +223,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the prefill")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through LLM.generate")
+    ap.add_argument("--only-prefill", type=int, default=0, metavar="TOKENS",
+                    help="run only a prefill of TOKENS tokens a few times and print its time (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -248,6 +250,14 @@ def main() -> int:
     engine = Engine(folder, "bf16", max_tokens=64 * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + 4096, page_size=PAGE_SIZE,
                     max_requests=64, max_batch_tokens=8192, max_seq_len=4096)
     graphs = DecodeGraphs(engine)
+
+    if args.only_prefill:
+        global PREFILL_TOKENS
+        PREFILL_TOKENS = args.only_prefill
+        pms = run_prefill(engine, rng, repeats=2)
+        print(json.dumps({"prefill_tokens": PREFILL_TOKENS, "ms": round(pms, 4), "layers": args.layers,
+                          "tokens_per_s": round(PREFILL_TOKENS / (pms / 1e3), 1)}))
+        return 0
 
     clocks = ClockSampler()
     ms, launches, mean_ctx = run_decode(engine, graphs, args.batch, steps, warmup, rng, clocks)

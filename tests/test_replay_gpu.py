@@ -152,3 +152,28 @@ def test_windowed_group_gives_pages_back(tmp_path_factory):
     assert engine.cache.held_pages(0, 0) == 19
     engine.close(0)
     engine.cache.check_consistency()
+
+
+def test_qwen25_05b_layer_sizes_in_32_bit(tmp_path):
+    """The benchmark's layer sizes (hidden 896, 14/2 heads of 64, intermediate 4864, vocabulary
+    151,936, theta 1e6, tied head) with two of the 24 layers and N(0, 0.02) weights: the 32-bit
+    engine against the plain implementation, whole and in portions beside decoded tokens."""
+    from llm_inference_lab_b200.engine import Engine
+
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=151936, hidden_size=896,
+               intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2,
+               rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=4096, hidden_act="silu",
+               tie_word_embeddings=True)
+    folder = make_model_folder(str(tmp_path / "m"), cfg, seed=0, dtype="float32", std=0.02, scales={})
+    rng = np.random.default_rng(2)
+    seqs = {"a": random_tokens(rng, 40, cfg["vocab_size"]), "b": random_tokens(rng, 23, cfg["vocab_size"])}
+    ref = plain_logits(folder, seqs)
+    engine = Engine(folder, "float32", max_tokens=256, page_size=16, max_requests=4)
+    for steps in (trace_whole(seqs), trace_mixed(seqs, np.random.default_rng(1), max_portion=7)):
+        for st in steps:   # logits of 151,936 columns: ask for the last place of each portion only
+            for e in st["entries"]:
+                e["want"] = [len(e["tokens"]) - 1]
+        got = run_trace_inprocess(engine, steps)
+        err, scale, where = worst_error(got, ref)
+        assert err <= F32_ABS, f"max abs error {err:.3e} at {where} (largest logit {scale:.2f})"
+    assert engine.cache.live_requests == 0
