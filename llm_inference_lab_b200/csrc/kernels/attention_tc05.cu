@@ -1,0 +1,513 @@
+// Causal prefill attention over the paged cache on the 5th-generation tensor cores, for heads
+// of 64 (-DLAB_HEAD_DIM=64) and page sizes of 8, 16, 32, 64 or 128 tokens.
+//
+// One CTA serves 128 query rows of one head of one request and walks the keys in tiles of 128:
+//   S = Q K^T        tcgen05.mma, Q and K tiles in 128-byte-swizzled shared memory (TMA; K is
+//                    gathered page by page through the block table), S in tensor memory
+//   P = softmax(S)   four warps, one query row per thread: tcgen05.ld of the row, scale and
+//                    causal/window mask, running max and sum in 32-bit, exp2, P rounded to
+//                    bfloat16 and stored to shared memory in the swizzled layout the MMA reads
+//   O_j = P V        tcgen05.mma with V as the N-major operand (V rows lie [key][d] as cached)
+//   acc = acc * exp2(m_old - m_new) + O_j     in registers of the row's thread, 32-bit
+// Two S buffers, two P buffers and two O buffers let the MMAs of tile j+1 run beside the
+// softmax of tile j.  Formulas and rounding as the reference's tensor-core prefill attention
+// (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124, 1295-1452): scores scaled by
+// 1/sqrt(d) (folded into the exp2 argument), key <= query, p rounded to T before PV, o = acc / sum.
+//
+// Warp 0 loads (TMA; the page that holds a request's last keys is copied by hand with rows
+// beyond the length set to zero, because a masked NaN would still poison P V), warp 1 issues
+// the MMAs and owns tensor memory, warps 2-5 do the softmax.  Every wait is bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef LAB_HEAD_DIM
+#error "build with -DLAB_HEAD_DIM=64"
+#endif
+
+namespace {
+
+constexpr int D = LAB_HEAD_DIM;
+static_assert(D == 64, "the tcgen05 attention kernel is built for heads of 64");
+constexpr int BM = 128;        // query rows per CTA
+constexpr int BN = 128;        // keys per tile
+constexpr int THREADS = 192;
+constexpr int KV_STAGES = 3;
+constexpr int ROW = 128;       // bytes of a swizzled row: 64 bf16
+constexpr int Q_BYTES = BM * ROW;
+constexpr int KV_TILE = BN * ROW;         // one K or V tile
+constexpr int P_HALF = BM * ROW;          // P for 64 keys
+constexpr int P_BYTES = 2 * P_HALF;       // P for 128 keys
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + Q_BYTES;
+constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE;
+constexpr int OFF_P = OFF_V + KV_STAGES * KV_TILE;
+constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+constexpr int SMEM = OFF_BAR + 256 + 1024;
+constexpr int TM_S = 0, TM_O = 2 * BN, TMEM_COLS = 512;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after about two seconds, records it, and lets every role drain.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > 2000000000ull) {
+      *abort_flag = 1;
+      lab_set_error(LAB_ERR_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_dst),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// 128-byte-swizzled tile whose rows are 128 bytes; 8-row groups lie 1024 bytes apart.  The same
+// descriptor serves a K-major operand (rows = M or N, 16 elements of K are 32 bytes along the row)
+// and an N-major operand (rows = K, a row holds 64 elements of N).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset: one 16-byte unit (a single atom wide)
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;            // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;            // 128-byte swizzle
+  return d;
+}
+// bf16 x bf16 -> f32, M = 128, N = n; b_n_major: the B operand is N-major (V as cached) instead of K-major.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_n_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_n_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct Barriers {
+  uint64_t q_full;
+  uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
+  uint64_t s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int out_stride,
+    const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
+    const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ pos0_arr,
+    const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
+    float scale_log2, int min_q_len) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + OFF_BAR);
+  volatile int* abort_flag = &bar->abort_flag;
+  pdl_trigger();
+  pdl_wait();
+  // Blocks are numbered with the head fastest and the tiles of the latest rows first: the CTAs
+  // that walk the most keys all start in the first wave.
+  const int b = blockIdx.z, h = blockIdx.x;
+  const int qs = q_start[b], ql = q_start[b + 1] - qs;
+  const int r0 = (gridDim.y - 1 - blockIdx.y) * BM;
+  if (ql < min_q_len || r0 >= ql) return;
+  const int kvh = h / (n_q / n_kv);
+  const int p0 = pos0_arr[b], kvl = kv_len_arr[b];
+  const int* bt = block_table + (size_t)b * max_blocks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int last_row = min(r0 + BM, ql) - 1;
+  const int hi_all = p0 + last_row;                                    // last key any row sees
+  const int lo_all = window > 0 ? max(0, p0 + r0 - window + 1) : 0;    // first key any row sees
+  const int t_first = lo_all / BN, t_last = hi_all / BN;
+  const int n_tiles = t_last - t_first + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&bar->kv_full[s], 2);  // the expect_tx arrival and the arrival after hand copies
+      mbar_init(&bar->kv_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar->s_full[i], 1);
+      mbar_init(&bar->s_empty[i], 4);
+      mbar_init(&bar->p_full[i], 4);
+      mbar_init(&bar->o_full[i], 1);
+      mbar_init(&bar->o_empty[i], 4);
+    }
+    bar->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp >= 2) {
+    // K and V stages start as zeros: rows no copy ever fills stay finite (they are always masked).
+    uint4* z = reinterpret_cast<uint4*>(smem + OFF_K);
+    for (int i = threadIdx.x - 64; i < 2 * KV_STAGES * KV_TILE / 16; i += 128) z[i] = make_uint4(0, 0, 0, 0);
+    proxy_fence();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bar->tmem_slot;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    // ---------------- loader ----------------
+    if (lane == 0) {
+      mbar_expect_tx(&bar->q_full, Q_BYTES);
+      tma_load_2d(smem_base + OFF_Q, &map_q, &bar->q_full, h * D, qs + r0);
+    }
+    const int pages_per_tile = BN / page_size;  // at most 16: one lane looks up each page of a tile
+    const int page_bytes = page_size * ROW;
+    bool alive = true;
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      const int s = j % KV_STAGES;
+      const uint32_t ph = (j / KV_STAGES) & 1;
+      const int key0 = (t_first + j) * BN;
+      // Lane pg classifies page pg of the tile and reads its number from the block table, before the
+      // wait for the stage, so that the lookups' latency is hidden behind it:
+      // 0 nothing to fetch (beyond the length, or wholly before the window), 1 whole page (TMA),
+      // 2 the page that holds the request's last keys (copied by hand, rows past the length zeroed).
+      int kind = 0, page = -1;
+      if (lane < pages_per_tile) {
+        const int k_lo = key0 + lane * page_size;
+        if (k_lo < kvl && k_lo + page_size > lo_all) {
+          kind = k_lo + page_size > kvl ? 2 : 1;
+          page = bt[k_lo / page_size];
+          if (page < 0 || page >= num_pages) {  // a page inside the length and the window must exist
+            lab_set_error(LAB_ERR_PAGE_RANGE);
+            kind = 0;
+          }
+        }
+      }
+      const uint32_t tma_lanes = __ballot_sync(0xffffffffu, kind == 1);
+      const uint32_t tail_lanes = __ballot_sync(0xffffffffu, kind == 2);
+      if (lane == 0) alive = mbar_wait(&bar->kv_empty[s], ph ^ 1, abort_flag);
+      alive = __shfl_sync(0xffffffffu, alive, 0);
+      if (!alive) break;
+      const uint32_t k_dst = smem_base + OFF_K + s * KV_TILE, v_dst = smem_base + OFF_V + s * KV_TILE;
+      // Lane 0 announces the bytes (one of the barrier's two arrivals); then every lane fetches its
+      // own page, so the copies of a tile are issued side by side.  The phase cannot end before the
+      // second arrival below, whatever the order in which bytes are announced and land.
+      if (lane == 0) mbar_expect_tx(&bar->kv_full[s], 2 * __popc(tma_lanes) * page_bytes);
+      __syncwarp();
+      if (kind == 1) {
+        const int row = (page * n_kv + kvh) * page_size;
+        tma_load_2d(k_dst + lane * page_bytes, &map_k, &bar->kv_full[s], 0, row);
+        tma_load_2d(v_dst + lane * page_bytes, &map_v, &bar->kv_full[s], 0, row);
+      }
+      if (tail_lanes) {
+        // The page with the request's last keys: rows below the length are copied, the rest set to
+        // zero, in the swizzled layout (16-byte chunk c of row r lies at chunk c ^ (r % 8)).
+        const int tail_slot = __ffs(tail_lanes) - 1;
+        const int tail_page = __shfl_sync(0xffffffffu, page, tail_slot);
+        const int k_lo = key0 + tail_slot * page_size;
+        const size_t src0 = ((size_t)tail_page * n_kv + kvh) * page_size * D;
+        for (int c = lane; c < page_size * 8; c += 32) {
+          const int r = c >> 3, q8 = c & 7;
+          const int tile_row = tail_slot * page_size + r;
+          uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+          if (k_lo + r < kvl) {
+            kk = *reinterpret_cast<const uint4*>(cache_k + src0 + (size_t)r * D + q8 * 8);
+            vv = *reinterpret_cast<const uint4*>(cache_v + src0 + (size_t)r * D + q8 * 8);
+          }
+          const int off = tile_row * ROW + ((q8 ^ (tile_row & 7)) << 4);
+          *reinterpret_cast<uint4*>(smem + OFF_K + s * KV_TILE + off) = kk;
+          *reinterpret_cast<uint4*>(smem + OFF_V + s * KV_TILE + off) = vv;
+        }
+        proxy_fence();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->kv_full[s]);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(BN, false);
+      constexpr uint32_t idesc_o = instr_desc(D, true);
+      bool ok = mbar_wait(&bar->q_full, 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % KV_STAGES, sb = j & 1;
+        if (!mbar_wait(&bar->kv_full[s], (j / KV_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(&bar->s_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_base + OFF_Q, ka = smem_base + OFF_K + s * KV_TILE;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem_base + TM_S + sb * BN, smem_desc_sw128(qa + k * 32), smem_desc_sw128(ka + k * 32), idesc_s,
+                    k > 0 ? 1u : 0u);
+        umma_commit(&bar->s_full[sb]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);  // the next tile's scores run beside this tile's softmax
+        if (!ok) break;
+        const int s = j % KV_STAGES, sb = j & 1;
+        ok = mbar_wait(&bar->p_full[sb], (j >> 1) & 1, abort_flag) &&
+             mbar_wait(&bar->o_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t pa = smem_base + OFF_P + sb * P_BYTES, va = smem_base + OFF_V + s * KV_TILE;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_bf16(tmem_base + TM_O + sb * D, smem_desc_sw128(pa + (kk >> 2) * P_HALF + (kk & 3) * 32),
+                    smem_desc_sw128(va + kk * 16 * ROW), idesc_o, kk > 0 ? 1u : 0u);
+        umma_commit(&bar->o_full[sb]);
+        umma_commit(&bar->kv_empty[s]);  // both products of this stage have been issued
+      }
+    }
+  } else {
+    // ---------------- softmax: one query row per thread ----------------
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;            // row of the tile = lane of tensor memory
+    const int pos = p0 + r0 + row;                  // absolute position of this row's query
+    const bool row_valid = r0 + row < ql;
+    const int hi = row_valid ? pos : -1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    // m: running maximum (log2 units) after the last tile seen; l: running sum relative to m;
+    // acc: sum of P V relative to m_acc, which lags one tile behind m.
+    float m = -INFINITY, l = 0.f, m_acc = -INFINITY, m_of_prev_tile = -INFINITY;
+    bool ok = true;
+    // acc = acc * 2^(m_acc - m_j) + O_j, where O_j was formed with P relative to m_j.
+    auto accumulate = [&](int j, float m_j) {
+      const int sb = j & 1;
+      ok = ok && mbar_wait(&bar->o_full[sb], (j >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return;
+      tc_fence_after();
+      const float corr = (m_acc == -INFINITY) ? 0.f : fast_exp2(m_acc - m_j);
+#pragma unroll
+      for (int half = 0; half < D / 32; ++half) {
+        uint32_t r[32];
+        tmem_ld32_issue(lane_addr + TM_O + sb * D + half * 32, r);
+        tmem_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[half * 32 + i] = acc[half * 32 + i] * corr + __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->o_empty[sb]);  // the O buffer may be overwritten
+      m_acc = m_j;
+    };
+    for (int j = 0; j < n_tiles; ++j) {
+      const int sb = j & 1;
+      ok = ok && mbar_wait(&bar->s_full[sb], (j >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(lane_addr + TM_S + sb * BN + c * 32, sr + c * 32);
+      tmem_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->s_empty[sb]);  // the scores are in registers: the buffer is free
+      const int key0 = (t_first + j) * BN;
+      const bool all_visible = key0 >= lo && key0 + BN - 1 <= hi;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maxima do not wait on each other
+#pragma unroll
+      for (int c = 0; c < BN; ++c) {
+        float sv = __uint_as_float(sr[c]) * scale_log2;
+        if (!all_visible && (key0 + c < lo || key0 + c > hi)) sv = -INFINITY;
+        sr[c] = __float_as_uint(sv);
+        mx4[c & 3] = fmaxf(mx4[c & 3], sv);
+      }
+      const float m_new = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+      const float base = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen no key yet
+      l *= (m == -INFINITY) ? 0.f : fast_exp2(m - base);
+      m = m_new;
+      // P, rounded to bfloat16, into the swizzled A-operand layout: row `row`, 16 chunks of 8 keys
+      uint8_t* p_row = smem + OFF_P + sb * P_BYTES + row * ROW;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q8 = 0; q8 < BN / 8; ++q8) {
+        float p[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          p[e] = fast_exp2(__uint_as_float(sr[q8 * 8 + e]) - base);  // 2^(-inf) = 0 for masked keys
+          sum4[e & 3] += p[e];
+        }
+        const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
+                                        pack_bf16(p[6], p[7]));
+        *reinterpret_cast<uint4*>(p_row + (q8 >> 3) * P_HALF + (((q8 & 7) ^ (row & 7)) << 4)) = packed;
+      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      proxy_fence();  // the generic-proxy stores of P become visible to the tensor cores
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->p_full[sb]);
+      // While the tensor cores form O_j, fold in O_{j-1}.
+      if (j > 0) {
+        accumulate(j - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
+        if (!ok) break;
+      }
+      m_of_prev_tile = m_new;
+    }
+    if (ok && n_tiles > 0) accumulate(n_tiles - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
+    if (ok && row_valid) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = out + (size_t)(qs + r0 + row) * out_stride + (size_t)h * D;
+#pragma unroll
+      for (int q8 = 0; q8 < D / 8; ++q8) {
+        const uint4 packed = make_uint4(pack_bf16(acc[q8 * 8] * inv, acc[q8 * 8 + 1] * inv),
+                                        pack_bf16(acc[q8 * 8 + 2] * inv, acc[q8 * 8 + 3] * inv),
+                                        pack_bf16(acc[q8 * 8 + 4] * inv, acc[q8 * 8 + 5] * inv),
+                                        pack_bf16(acc[q8 * 8 + 6] * inv, acc[q8 * 8 + 7] * inv));
+        if ((((uintptr_t)dst) & 15) == 0) {
+          reinterpret_cast<uint4*>(dst)[q8] = packed;
+        } else {
+          const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&packed);
+          for (int e = 0; e < 8; ++e) dst[q8 * 8 + e] = hp[e];
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+// bf16 matrix [rows, cols] with row stride ld (elements); box = [64 columns, box_rows], 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+LAB_EXPORT int lab_attention_tc05_head_dim() { return D; }
+
+// 1 if the kernel takes this page size (pages are fetched as TMA boxes and must tile 128 keys
+// with swizzle groups of 8 rows).
+LAB_EXPORT int lab_attention_tc05_supports(int page_size) {
+  return page_size >= 8 && page_size <= 128 && (page_size & (page_size - 1)) == 0;
+}
+
+// Arguments as lab_attention_prefill; total_rows is the number of rows of q (for the TMA bounds).
+LAB_EXPORT int lab_attention_prefill_tc05(void* out, int out_stride, const void* q, int q_stride, int total_rows,
+                                          const void* cache_k, const void* cache_v, const int* q_start,
+                                          const int* kv_len, const int* pos0, const int* block_table, int max_blocks,
+                                          int requests, int max_q_len, int n_q, int n_kv, int page_size, int num_pages,
+                                          int window, float scale, int min_q_len, cudaStream_t stream) {
+  if (requests <= 0 || max_q_len <= 0) return 0;
+  if (!lab_attention_tc05_supports(page_size) || n_q % n_kv || q_stride % 8 || (((uintptr_t)q) & 15) ||
+      (((uintptr_t)cache_k) & 15) || (((uintptr_t)cache_v) & 15))
+    return (int)cudaErrorInvalidValue;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_map(&mq, q, total_rows, n_q * D, q_stride, BM))) return rc;
+  const long long cache_rows = (long long)num_pages * n_kv * page_size;
+  if ((rc = make_map(&mk, cache_k, cache_rows, D, D, page_size))) return rc;
+  if ((rc = make_map(&mv, cache_v, cache_rows, D, D, page_size))) return rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(attention_prefill_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_q, (max_q_len + BM - 1) / BM, requests);
+  return (int)lab_launch(attention_prefill_tc05_kernel, grid, dim3(THREADS), (size_t)SMEM, stream, mq, mk, mv,
+                         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v,
+                         q_start, kv_len, pos0, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
+                         scale * LOG2E, min_q_len);
+}

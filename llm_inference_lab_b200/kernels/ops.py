@@ -342,6 +342,11 @@ def linear_gated(x, w_gate_up):
     return gemm_tc(x, w_gate_up, None, gated=True)
 
 
+# Which kernel serves requests that bring several tokens: "auto" (tcgen05 for heads of 64 once a
+# request brings more than 64 tokens, else mma.sync), "mma" or "tc05".
+PREFILL_KERNEL = "auto"
+
+
 def attention_tc_supported(head_dim: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 128
 
@@ -373,7 +378,16 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     L = lib("attention_tc", {"LAB_HEAD_DIM": head_dim})
     max_q = max(q_lens)
     n_decode = sum(1 for n in q_lens if n == 1)
-    if max_q > 1:
+    use_tc05 = PREFILL_KERNEL == "tc05" or (PREFILL_KERNEL == "auto" and max_q > 64)
+    if max_q > 1 and use_tc05 and head_dim == 64 and page_size >= 8 and page_size <= 128 and \
+            page_size & (page_size - 1) == 0:
+        # tcgen05 kernel: tiles of 128 query rows, scores and P V on the 5th-generation tensor cores
+        L5 = lib("attention_tc05", {"LAB_HEAD_DIM": head_dim})
+        _check(L5.lab_attention_prefill_tc05(
+            _ptr(out), out.stride(0), _ptr(q), q.stride(0), tokens, _ptr(cache_k), _ptr(cache_v), _ptr(q_start),
+            _ptr(kv_len), _ptr(pos0), _ptr(block_table), block_table.shape[1], n_requests, max_q, n_q, n_kv,
+            page_size, num_pages, window, ctypes.c_float(scale), 2, _stream()), "attention_prefill_tc05")
+    elif max_q > 1:
         _check(L.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                        _ptr(q_start), _ptr(kv_len), _ptr(pos0), _ptr(block_table),
                                        block_table.shape[1], n_requests, max_q, n_q, n_kv, page_size, num_pages,

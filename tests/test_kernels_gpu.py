@@ -326,6 +326,33 @@ def test_attention_tc(n_q, n_kv, d, ps, window, requests):
         assert rel_err(g, w) < 2e-2
 
 
+TC05_CASES = [
+    # n_q, n_kv, page, window, requests [(kv_len, q_len)]
+    (2, 1, 16, 0, [(128, 128)]),
+    (2, 2, 16, 0, [(256, 256)]),
+    (14, 2, 16, 0, [(300, 300), (129, 129), (1000, 130), (77, 77), (640, 1)]),
+    (4, 2, 8, 0, [(515, 200), (2100, 2100)]),
+    (3, 1, 64, 0, [(333, 333), (130, 2)]),
+    (6, 3, 32, 50, [(400, 400), (700, 150)]),
+    (2, 1, 128, 0, [(260, 260)]),
+]
+
+
+@pytest.mark.parametrize("n_q,n_kv,ps,window,requests", TC05_CASES)
+def test_attention_prefill_tcgen05(n_q, n_kv, ps, window, requests):
+    """The tcgen05 prefill kernel (heads of 64) against the 64-bit reference: whole prompts, portions
+    on top of a long history, ragged batches beside decode rows, windows, every supported page size.
+    Unused cache slots hold NaN: nothing beyond a request's length may leak into P V."""
+    old = ops().PREFILL_KERNEL
+    ops().PREFILL_KERNEL = "tc05"
+    try:
+        got, want = run_attention("tc", requests, n_q, n_kv, 64, ps, window, torch.bfloat16, seed=3)
+    finally:
+        ops().PREFILL_KERNEL = old
+    for g, w in zip(got, want):
+        assert rel_err(g, w) < 2e-2
+
+
 @pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
 def test_attention_decode_splits(splits):
     """Every way of splitting the keys gives the same result, also with splits that get no keys."""
