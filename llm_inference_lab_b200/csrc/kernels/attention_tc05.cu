@@ -378,15 +378,20 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       if (lane == 0) mbar_arrive(&bar->s_empty[sb]);  // the scores are in registers: the buffer is free
       const int key0 = (t_first + j) * BN;
       const bool all_visible = key0 >= lo && key0 + BN - 1 <= hi;
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maxima do not wait on each other
+      // Maxima are taken over the raw scores (the scale is positive), four chains side by side;
+      // the scale is applied inside the exponent: p = 2^(s * scale - m * scale), one FMA per score.
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (all_visible) {
 #pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        float sv = __uint_as_float(sr[c]) * scale_log2;
-        if (!all_visible && (key0 + c < lo || key0 + c > hi)) sv = -INFINITY;
-        sr[c] = __float_as_uint(sv);
-        mx4[c & 3] = fmaxf(mx4[c & 3], sv);
+        for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          if (key0 + c < lo || key0 + c > hi) sr[c] = __float_as_uint(-INFINITY);
+          mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+        }
       }
-      const float m_new = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+      const float m_new = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
       const float base = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen no key yet
       l *= (m == -INFINITY) ? 0.f : fast_exp2(m - base);
       m = m_new;
@@ -398,7 +403,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         float p[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          p[e] = fast_exp2(__uint_as_float(sr[q8 * 8 + e]) - base);  // 2^(-inf) = 0 for masked keys
+          p[e] = fast_exp2(fmaf(__uint_as_float(sr[q8 * 8 + e]), scale_log2, -base));  // 2^(-inf) = 0 for masked keys
           sum4[e & 3] += p[e];
         }
         const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
