@@ -250,6 +250,7 @@ def main() -> int:
     engine = Engine(folder, "bf16", max_tokens=64 * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + 4096, page_size=PAGE_SIZE,
                     max_requests=64, max_batch_tokens=8192, max_seq_len=4096)
     graphs = DecodeGraphs(engine)
+    engine.enable_step_graphs()   # a prefill of a repeating shape is replayed from a CUDA graph
 
     if args.only_prefill:
         global PREFILL_TOKENS

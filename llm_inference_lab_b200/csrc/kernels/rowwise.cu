@@ -311,6 +311,111 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
   }
 }
 
+// cos and sin of pos * inv_freq[i] for every row of a step, formed once per step in 32-bit and
+// read by the rotary kernels of all layers: table[t][i] = (cos, sin).
+__global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int half, int total) {
+  pdl_trigger();
+  pdl_wait();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int t = e / half, i = e - t * half;
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+  table[e] = make_float2(cs, sn);
+}
+
+LAB_EXPORT int lab_rope_table(void* table, const int* positions, const float* inv_freq, int tokens, int half,
+                              cudaStream_t stream) {
+  const int total = tokens * half;
+  if (total <= 0) return 0;
+  return (int)lab_launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, (float2*)table, positions,
+                         inv_freq, half, total);
+}
+
+// bfloat16, many rows: a thread rotates 8 pairs (or copies 8 values) with 16-byte loads and stores;
+// cos and sin come from the step's table.  Needs rotary_dim / 2 and the head size to be multiples
+// of 8 and 16-byte aligned rows.
+__global__ void __launch_bounds__(256) rope_kv_write_vec_kernel(
+    __nv_bfloat16* __restrict__ qkv, int row_stride, const float2* __restrict__ table, int rotary_dim,
+    const int* __restrict__ slots, __nv_bfloat16* __restrict__ cache_k, __nv_bfloat16* __restrict__ cache_v, int n_q,
+    int n_kv, int d, int page_size, int num_pages, int tokens) {
+  pdl_trigger();
+  pdl_wait();
+  const int half = rotary_dim / 2;
+  const int rot_items = half / 8, copy_items = (d - rotary_dim) / 8;
+  const int per_head = rot_items + copy_items;          // q and k heads: pairs of chunks, then plain chunks
+  const int per_v = d / 8;
+  const int per_token = (n_q + n_kv) * per_head + n_kv * per_v;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= (long long)tokens * per_token) return;
+  const int t = (int)(e / per_token);
+  int w = (int)(e - (long long)t * per_token);
+  int head, item;
+  bool is_v = false;
+  if (w < (n_q + n_kv) * per_head) {
+    head = w / per_head;
+    item = w - head * per_head;
+  } else {
+    w -= (n_q + n_kv) * per_head;
+    head = n_q + n_kv + w / per_v;
+    item = w % per_v;
+    is_v = true;
+  }
+  __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)head * d;
+  __nv_bfloat16* dst = src;
+  if (head >= n_q) {
+    if (cache_k == nullptr) return;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int page = slot / page_size, off = slot - page * page_size;
+    if (page >= num_pages) {
+      lab_set_error(LAB_ERR_PAGE_RANGE);
+      return;
+    }
+    const int kvh = is_v ? head - n_q - n_kv : head - n_q;
+    dst = (is_v ? cache_v : cache_k) + (((size_t)page * n_kv + kvh) * page_size + off) * d;
+  }
+  if (is_v || item >= rot_items) {
+    const int i0 = is_v ? item * 8 : rotary_dim + (item - rot_items) * 8;
+    if (dst != src) *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(src + i0);
+    return;
+  }
+  const int i0 = item * 8;
+  const uint4 rlo = *reinterpret_cast<const uint4*>(src + i0), rhi = *reinterpret_cast<const uint4*>(src + i0 + half);
+  const __nv_bfloat16* lo = reinterpret_cast<const __nv_bfloat16*>(&rlo);
+  const __nv_bfloat16* hi = reinterpret_cast<const __nv_bfloat16*>(&rhi);
+  const float2* cs = table + (size_t)t * half + i0;
+  uint4 olo, ohi;
+  __nv_bfloat16* pl = reinterpret_cast<__nv_bfloat16*>(&olo);
+  __nv_bfloat16* ph = reinterpret_cast<__nv_bfloat16*>(&ohi);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float2 f = cs[j];
+    const float c = round_to<__nv_bfloat16>(f.x), sv = round_to<__nv_bfloat16>(f.y);
+    const float l = __bfloat162float(lo[j]), h = __bfloat162float(hi[j]);
+    pl[j] = __float2bfloat16_rn(round_to<__nv_bfloat16>(l * c) - round_to<__nv_bfloat16>(h * sv));
+    ph[j] = __float2bfloat16_rn(round_to<__nv_bfloat16>(h * c) + round_to<__nv_bfloat16>(l * sv));
+  }
+  *reinterpret_cast<uint4*>(dst + i0) = olo;
+  *reinterpret_cast<uint4*>(dst + i0 + half) = ohi;
+}
+
+// table: optional [tokens, rotary_dim / 2] (cos, sin) pairs from lab_rope_table.
+LAB_EXPORT int lab_rope_kv_write_table(void* qkv, int row_stride, const void* table, int rotary_dim, const int* slots,
+                                       void* cache_k, void* cache_v, int tokens, int n_q, int n_kv, int d,
+                                       int page_size, int num_pages, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rotary_dim % 16 || rotary_dim > d || d % 8 || row_stride % 8 || table == nullptr ||
+      ((((uintptr_t)qkv) | ((uintptr_t)cache_k) | ((uintptr_t)cache_v)) & 15))
+    return (int)cudaErrorInvalidValue;
+  const int per_head = rotary_dim / 16 + (d - rotary_dim) / 8;
+  const long long total = (long long)tokens * ((n_q + n_kv) * per_head + n_kv * (d / 8));
+  return (int)lab_launch(rope_kv_write_vec_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                         (__nv_bfloat16*)qkv, row_stride, (const float2*)table, rotary_dim, slots,
+                         (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, n_q, n_kv, d, page_size, num_pages, tokens);
+}
+
 LAB_EXPORT int lab_rope_kv_write(void* qkv, int row_stride, const float* partial, int splits, long long split_stride,
                                  const void* bias, void* q_out, const int* positions, const float* inv_freq,
                                  int rotary_dim, const int* slots, void* cache_k, void* cache_v, int tokens, int n_q,

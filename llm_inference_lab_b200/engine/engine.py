@@ -113,6 +113,13 @@ class Engine:
         self.stats = EngineStats()
         self._staging = [self._new_staging() for _ in range(3)]
         self._staging_at = 0
+        # Steps whose shape repeats (same token counts per request, same wanted counts) can be
+        # replayed from CUDA graphs; off until `enable_step_graphs` is called.
+        self._graphs_on = False
+        self._graphs: dict = {}
+        self._seen: dict = {}
+        self._graphs_max = 8
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------------------------
     def _new_staging(self):
@@ -128,6 +135,14 @@ class Engine:
         if st["event"] is not None:
             st["event"].synchronize()
         return st
+
+    def enable_step_graphs(self, max_cached: int = 8) -> None:
+        """Replay steps of a repeating shape from CUDA graphs (captured when a shape comes a second
+        time).  The logits a replayed step returns live in the graph's buffer: read them before the
+        next step of the same shape.  Models with fixed-size per-request state keep running eagerly
+        (their mixers may index the state on the host)."""
+        self._graphs_on = all(v.state is None for v in self.views)
+        self._graphs_max = max_cached
 
     # ------------------------------------------------------------------------------------
     def open(self, request: int) -> None:
@@ -198,8 +213,7 @@ class Engine:
                 for e in entries:
                     self.cache.reserve(e.request, len(e.tokens))
                     taken.append(e.request)
-            ctx, logit_rows = self._pack(entries)
-            logits = self.model.forward(ctx, self.views, logit_rows)
+            logits = self._run(entries)
         except Exception:
             for r in taken:
                 self.cache.rollback(r)
@@ -218,20 +232,69 @@ class Engine:
         return logits
 
     # ------------------------------------------------------------------------------------
-    def _pack(self, entries: Sequence[Entry]):
+    def _run(self, entries: Sequence[Entry]):
+        """Packs the step and runs the model, eagerly or from a CUDA graph of the same shape."""
+        if self._graphs_on:
+            max_kv = max(self.cache.reserved(e.request) for e in entries)
+            bucket = 256
+            while bucket < max_kv:
+                bucket *= 2
+            sig = (tuple(len(e.tokens) for e in entries), tuple(len(e.want) for e in entries), bucket)
+            cap = self._graphs.get(sig)
+            if cap is not None:
+                self._fill(entries, cap["layout"], cap["widths"], cap["dev"], cap["tok_at"], cap["want_at"])
+                cap["graph"].replay()
+                ops.COUNTER.launches += cap["launches"]
+                self.graph_replays += 1
+                return cap["logits"]
+            self._seen[sig] = self._seen.get(sig, 0) + 1
+            if self._seen[sig] >= 2:
+                return self._capture(sig, entries, bucket)
+        ctx, logit_rows = self._pack(entries)
+        return self.model.forward(ctx, self.views, logit_rows)
+
+    def _capture(self, sig, entries, bucket):
+        if len(self._graphs) >= self._graphs_max:
+            self._graphs.pop(next(iter(self._graphs)))
         pairs = [(int(e.request), len(e.tokens)) for e in entries]
-        T = sum(n for _, n in pairs)
-        B = len(pairs)
-        n_groups = len(self.group_windows)
-        widths = []
-        for g in range(n_groups):
-            ps = self.page_size
-            width = max(-(-self.cache.reserved(r) // ps) for r, _ in pairs)
-            widths.append((width + 7) & ~7)
-        layout = self.cache.layout(T, B, widths)
+        T, B = sum(n for _, n in pairs), len(pairs)
         n_want = sum(len(e.want) for e in entries)
+        widths = [self.max_blocks] * len(self.group_windows)
+        layout = self.cache.layout(T, B, widths)
         tok_at = layout.total
         want_at = tok_at + ((T + 3) & ~3)
+        total = want_at + ((n_want + 3) & ~3)
+        dev = torch.zeros((total,), dtype=torch.int32, device=self.device)
+        self._fill(entries, layout, widths, dev, tok_at, want_at)
+        q_lens = [n for _, n in pairs]
+        ctx = self._context(dev, layout, widths, T, B, q_lens, [bucket] * B, [], tok_at)
+        rows = dev[want_at: want_at + n_want] if n_want else None
+        # One eager run (it also configures kernels and warms the allocator), then the capture.
+        # Running the step more than once is harmless: it writes the same cache entries again.
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.model.forward(ctx, self.views, rows)
+        torch.cuda.current_stream().wait_stream(side)
+        ctx.scratch.clear()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.COUNTER.launches
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.views, rows)
+        launches = ops.COUNTER.launches - before
+        ops.COUNTER.launches = before
+        cap = {"graph": graph, "layout": layout, "widths": widths, "dev": dev, "tok_at": tok_at, "want_at": want_at,
+               "logits": logits, "launches": launches}
+        self._graphs[sig] = cap
+        graph.replay()
+        ops.COUNTER.launches += launches
+        self.graph_replays += 1
+        return logits
+
+    def _fill(self, entries, layout, widths, dev, tok_at, want_at) -> None:
+        """Writes a step's metadata, token ids and wanted rows into `dev` through pinned memory."""
+        pairs = [(int(e.request), len(e.tokens)) for e in entries]
+        n_want = sum(len(e.want) for e in entries)
         total = want_at + ((n_want + 3) & ~3)
         st = self._next_staging()
         if total > st["np"].shape[0]:
@@ -247,25 +310,42 @@ class Engine:
                 host[wi] = row + w
                 wi += 1
             row += n
-        dev = torch.empty((total,), dtype=torch.int32, device=self.device)
         dev.copy_(st["host"][:total], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         st["event"] = ev
 
+    def _context(self, dev, layout, widths, T, B, q_lens, kv_lens, state_slots, tok_at) -> StepContext:
         def view(at, n):
             return dev[at: at + n]
 
-        q_lens = [n for _, n in pairs]
-        kv_lens = [self.cache.reserved(r) for r, _ in pairs]
+        n_groups = len(self.group_windows)
         groups = [GroupView(self.page_size, self.group_windows[g], view(layout.row_slot[g], T),
                             view(layout.block_table[g], B * widths[g]).view(B, widths[g])) for g in range(n_groups)]
-        ctx = StepContext(
+        return StepContext(
             dtype=self.dtype, device=self.device, n_tokens=T, n_requests=B,
             token_ids=view(tok_at, T), row_req=view(layout.row_req, T), row_pos=view(layout.row_pos, T),
             q_start=view(layout.q_start, B + 1), kv_len=view(layout.kv_len, B), pos0=view(layout.pos0, B),
             state_slot=view(layout.state_slot, B), groups=groups, q_lens=q_lens, kv_lens=kv_lens,
-            state_slots=[self.cache.state_slot(r) for r, _ in pairs],
-            max_q_len=max(q_lens), max_kv_len=max(kv_lens))
-        logit_rows = view(want_at, n_want) if n_want else None
+            state_slots=state_slots, max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+
+    def _pack(self, entries: Sequence[Entry]):
+        pairs = [(int(e.request), len(e.tokens)) for e in entries]
+        T = sum(n for _, n in pairs)
+        B = len(pairs)
+        widths = []
+        for g in range(len(self.group_windows)):
+            width = max(-(-self.cache.reserved(r) // self.page_size) for r, _ in pairs)
+            widths.append((width + 7) & ~7)
+        layout = self.cache.layout(T, B, widths)
+        n_want = sum(len(e.want) for e in entries)
+        tok_at = layout.total
+        want_at = tok_at + ((T + 3) & ~3)
+        total = want_at + ((n_want + 3) & ~3)
+        dev = torch.empty((total,), dtype=torch.int32, device=self.device)
+        self._fill(entries, layout, widths, dev, tok_at, want_at)
+        ctx = self._context(dev, layout, widths, T, B, [n for _, n in pairs],
+                            [self.cache.reserved(r) for r, _ in pairs],
+                            [self.cache.state_slot(r) for r, _ in pairs], tok_at)
+        logit_rows = dev[want_at: want_at + n_want] if n_want else None
         return ctx, logit_rows

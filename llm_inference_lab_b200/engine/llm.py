@@ -43,6 +43,8 @@ class LLM:
         self.model_eos = list(self.engine.model.blueprint.eos_token_ids)
         self.cuda_graph = bool(cuda_graph)
         self.graphs = DecodeGraphs(self.engine) if self.cuda_graph else None
+        if self.cuda_graph:
+            self.engine.enable_step_graphs()      # prompt portions of a repeating shape as well
         self.step_log: list[tuple[float, int, bool]] = []   # (time the step's tokens reached the host, tokens, decode?)
         self._next_id = 0
         self.steps = 0

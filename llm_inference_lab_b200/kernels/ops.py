@@ -27,15 +27,24 @@ DEVICE_ERRORS = {1: "a page or slot index outside the pool", 2: "a bounded wait 
                  3: "a gathered row index outside the batch"}
 
 
+_fast: dict = {}    # (name, head size or None) -> library handle; read without the lock on the hot path
+
+
 def lib(name: str, defines: dict[str, int] | None = None) -> ctypes.CDLL:
+    fast_key = (name, defines["LAB_HEAD_DIM"] if defines else None)
+    handle = _fast.get(fast_key)
+    if handle is not None:
+        return handle
     key = name + repr(sorted((defines or {}).items()))
     with _lock:
         if key in _libs:
+            _fast[fast_key] = _libs[key]
             return _libs[key]
     path = build.kernel_library(name, defines)
     handle = ctypes.CDLL(path)
     with _lock:
         _libs[key] = handle
+        _fast[fast_key] = handle
     return handle
 
 
@@ -52,7 +61,13 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"unsupported storage type {dtype}: the kernels take float32 or bfloat16")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current CUDA stream's handle (also the capturing stream while a graph is recorded)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -162,6 +177,27 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Te
         _ptr(qkv), qkv.stride(0), None, 0, ctypes.c_longlong(0), None, None, _ptr(positions), _ptr(inv_freq),
         rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v), tokens, n_q, n_kv, head_dim, page_size, num_pages,
         dtype_code(qkv.dtype), _stream()), "rope_kv_write")
+    return qkv[:, : n_q * head_dim]
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of pos * inv_freq for every row of a step: [tokens, rotary_dim / 2, 2] float32."""
+    tokens, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((tokens, half, 2), dtype=torch.float32, device=positions.device)
+    _check(lib("rowwise").lab_rope_table(_ptr(table), _ptr(positions), _ptr(inv_freq), tokens, half, _stream()),
+           "rope_table")
+    return table
+
+
+def rope_kv_write_table(qkv, table, rotary_dim, slots, cache_k, cache_v, n_q, n_kv, head_dim) -> torch.Tensor:
+    """The rotation and cache write for bfloat16 steps with many rows, with cos/sin from `rope_table`."""
+    tokens = qkv.shape[0]
+    page_size = num_pages = 0
+    if cache_k is not None:
+        num_pages, _, page_size, _ = cache_k.shape
+    _check(lib("rowwise").lab_rope_kv_write_table(
+        _ptr(qkv), qkv.stride(0), _ptr(table), rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v), tokens, n_q,
+        n_kv, head_dim, page_size, num_pages, _stream()), "rope_kv_write_table")
     return qkv[:, : n_q * head_dim]
 
 

@@ -72,7 +72,7 @@ class GQAttention(Mixer):
                 self.d, self.window, self.scale)
             return ops.linear(attn, self.w_o, self.b_o, allow_partial=self.b_o is None)
         q = self.position.rotate_and_store(qkv, ctx.row_pos, group.row_slot, cache, self.n_q, self.n_kv, self.d,
-                                           bias=self.b_qkv if qkv.dim() == 3 else None)
+                                           bias=self.b_qkv if qkv.dim() == 3 else None, scratch=ctx.scratch)
         attn = ops.attention(q, cache.k, cache.v, ctx, group, self.n_q, self.n_kv, self.d, self.window, self.scale)
         return ops.linear(attn, self.w_o, self.b_o, allow_partial=self.b_o is None)
 

@@ -117,10 +117,11 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     def rotate_and_store(self, qkv, positions, slots, cache: CacheView, n_q: int, n_kv: int, head_dim: int,
-                         bias=None) -> torch.Tensor:
+                         bias=None, scratch=None) -> torch.Tensor:
         """Encodes q and k of the fused projection `qkv` ([tokens, (n_q + 2 n_kv) * d], or its
         32-bit split-K partial products [splits, tokens, ...] with `bias` still to add), writes
-        k and v to the cache slots when the call may write, and returns the encoded q."""
+        k and v to the cache slots when the call may write, and returns the encoded q.  `scratch` is
+        the step's dictionary for buffers that layers may share (e.g. a table of angles)."""
         raise NotImplementedError
 
 

@@ -105,6 +105,24 @@ def test_rope_kv_write(dtype, n_q, n_kv, d, rot, theta):
     assert torch.equal(dq[:, (n_q + n_kv) * d:].cpu(), qkv[:, (n_q + n_kv) * d:])
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,rot", [(14, 2, 64, 64), (3, 1, 32, 16), (5, 5, 48, 48), (2, 2, 128, 128)])
+def test_rope_table_path_equals_scalar_path(n_q, n_kv, d, rot):
+    """The vectorised rotation with a per-step cos/sin table gives the scalar kernel's bits."""
+    g = torch.Generator().manual_seed(32)
+    T, ps, pages = 300, 16, 40
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * d, generator=g).bfloat16()
+    pos = torch.randint(0, 4096, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
+    inv = torch.from_numpy(np.power(1e6, -2.0 * np.arange(rot // 2) / rot).astype(np.float32)).to(DEV)
+    caches = [torch.zeros((pages, n_kv, ps, d), dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    a, b = qkv.clone().to(DEV), qkv.clone().to(DEV)
+    q1 = ops().rope_kv_write(a, pos.to(DEV), inv, rot, slots.to(DEV), caches[0], caches[1], n_q, n_kv, d)
+    table = ops().rope_table(pos.to(DEV), inv)
+    q2 = ops().rope_kv_write_table(b, table, rot, slots.to(DEV), caches[2], caches[3], n_q, n_kv, d)
+    assert torch.equal(q1, q2) and torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])
+    assert torch.equal(a, b)
+
+
 def test_rope_kv_write_from_split_k_partials():
     """The fused projection may arrive as 32-bit split-K partial sums with the bias still to add:
     the result equals summing, adding the bias, rounding once, and then the ordinary call."""

@@ -177,3 +177,29 @@ def test_qwen25_05b_layer_sizes_in_32_bit(tmp_path):
         err, scale, where = worst_error(got, ref)
         assert err <= F32_ABS, f"max abs error {err:.3e} at {where} (largest logit {scale:.2f})"
     assert engine.cache.live_requests == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_replayed_from_cuda_graphs(tmp_path_factory, dtype):
+    """Steps of a repeating shape are captured the second time they come and replayed after that;
+    the logits stay those of the plain implementation, for other requests, pages and positions."""
+    from llm_inference_lab_b200.engine import Engine, Entry
+
+    folder, cfg, opt, _, _, _ = model_case(tmp_path_factory, "B", dtype)
+    rng = np.random.default_rng(21)
+    seqs = {f"g{i}": random_tokens(rng, 150, cfg["vocab_size"]) for i in range(5)}
+    ref = plain_logits(folder, seqs)
+    engine = Engine(folder, dtype, max_tokens=512, page_size=opt["page_size"], max_requests=4)
+    engine.enable_step_graphs()
+    got = {}
+    for i, (name, ids) in enumerate(seqs.items()):
+        # every request: a portion of 130 tokens (the same shape each time), then single tokens
+        logits = engine.step([Entry(i, ids[:130], list(range(130)))])
+        for p in range(130):
+            got[(name, p)] = logits[p].float().cpu().numpy()
+        for p in range(130, 150):
+            got[(name, p)] = engine.step([Entry(i, [ids[p]], [0])])[0].float().cpu().numpy()
+        engine.close(i)
+    assert engine.graph_replays >= 4 * 1 + 5 * 18, "the repeated shapes ran from graphs"
+    check(got, ref, dtype, seqs)
+    assert engine.cache.live_requests == 0
