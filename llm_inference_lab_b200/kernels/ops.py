@@ -359,13 +359,37 @@ def _pick_splits(T: int, n_out: int, K: int) -> int:
     return max(1, min(k_tiles // 4, SM_COUNT // tiles, 16))
 
 
+def _pick_prefill_tiles(T: int, n_out: int, K: int, allow_partial: bool) -> tuple[int, int]:
+    """(N tile, K splits) of a product with many tokens (tokens on the 128-row side).  A CTA fills
+    shared memory from L2 at a fixed rate, so wide tiles (256) do more arithmetic per byte; they
+    are taken when they still give every SM work, if need be by splitting K (measured at
+    [2048 x 4864] x [4864 x 896]: 28 us with 128-wide tiles, 23 us with 256-wide tiles and two
+    K splits; at 8,192 tokens 95 against 71 us)."""
+    m_tiles = -(-T // 128)
+    t256 = m_tiles * (-(-n_out // 256))
+    if t256 >= 1.4 * SM_COUNT:
+        return 256, 1
+    if allow_partial:
+        k_tiles = -(-K // 64)
+        splits = min(SM_COUNT // max(t256, 1), k_tiles // 16)
+        if splits >= 2:
+            return 256, splits
+    return 128, 1
+
+
 def linear(x, w, bias=None, out_f32=False, allow_partial=False):
     """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
     products [splits, tokens, out], without the bias, that the consumer sums (`add_rmsnorm`,
     `rope_kv_write`)."""
     if x.dtype == torch.float32 or _force_plain:
         return gemm_plain(x, w, bias, out_f32=out_f32)
-    splits = _pick_splits(x.shape[0], w.shape[0], x.shape[1]) if allow_partial else 1
+    T = x.shape[0]
+    if T > 128:
+        bn, splits = _pick_prefill_tiles(T, w.shape[0], x.shape[1], allow_partial and bias is None and not out_f32)
+        if splits > 1:
+            return gemm_tc(x, w, None, swap=False, bn=bn, splits=splits)
+        return gemm_tc(x, w, bias, out_f32=out_f32, swap=False, bn=bn)
+    splits = _pick_splits(T, w.shape[0], x.shape[1]) if allow_partial else 1
     if splits > 1:
         return gemm_tc(x, w, None, splits=splits)     # the consumer adds the bias
     return gemm_tc(x, w, bias, out_f32=out_f32)
