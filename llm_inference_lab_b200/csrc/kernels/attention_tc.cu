@@ -315,12 +315,30 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
 // through a private ring of shared-memory stages; the warps' softmax states are merged at
 // the end.  With several splits the CTA leaves (acc, max, sum) in scratch for the merge kernel.
 // ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the cluster's shared window, of `addr` (shared, this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 constexpr int DC_BN = 32, DC_THREADS = 128, DC_WARPS = 4;
 constexpr int DC_STAGES = D <= 64 ? 3 : 2;
 constexpr int DC_TILE_BYTES = DC_BN * ROW_BYTES;
 constexpr int DC_WARP_BYTES = DC_STAGES * 2 * DC_TILE_BYTES;
 constexpr int DC_MERGE_BYTES = DC_WARPS * 16 * (D + 2) * 4;
-constexpr int DC_SMEM = DC_WARPS * DC_WARP_BYTES > DC_MERGE_BYTES ? DC_WARPS * DC_WARP_BYTES : DC_MERGE_BYTES;
+constexpr int DC_CLUSTER_BYTES = 16 * (D + 2) * 4;  // a CTA's merged state, read by its cluster
+constexpr int DC_SMEM = DC_WARPS * DC_WARP_BYTES > DC_MERGE_BYTES + DC_CLUSTER_BYTES ? DC_WARPS * DC_WARP_BYTES
+                                                                                    : DC_MERGE_BYTES + DC_CLUSTER_BYTES;
+constexpr int DC_MAX_CLUSTER = 8;  // the portable cluster size
 constexpr int DC_SMEM_FUSED = DC_SMEM + 18 * ROW_BYTES;  // + the rotated q rows, the newest key and value
 
 // What the fused variant needs besides the plain one's arguments: it takes the fused projection
@@ -341,7 +359,11 @@ struct FusedDecodeArgs {
   int* counters;              // [requests * n_kv] zeros
 };
 
-template <bool FUSED>
+// CLUSTER: the splits of one (request, kv head, tile of heads) are the CTAs of one thread-block
+// cluster (grid x = cluster x = splits, at most 8).  Each leaves its (acc, max, sum) in its own
+// shared memory, and after a cluster barrier every CTA merges its share of the output elements
+// from all of them through distributed shared memory: no scratch and no merge kernel.
+template <bool FUSED, bool CLUSTER = false>
 __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, int out_stride, const __nv_bfloat16* __restrict__ q, int q_stride,
     __nv_bfloat16* __restrict__ cache_k, __nv_bfloat16* __restrict__ cache_v,
@@ -350,10 +372,15 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     float* __restrict__ part_acc, float* __restrict__ part_ml, FusedDecodeArgs fa) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_trigger();
-  pdl_wait();
+  // Until pdl_wait() below only what no kernel of this step writes is read: the step's metadata
+  // (row offsets, lengths, block tables) and keys and values of earlier steps.  The rows of this
+  // step (q, and the tile that holds the newest key) come after the wait.
   const int b = blockIdx.z;
   const int qs = q_start[b];
-  if (q_start[b + 1] - qs != 1) return;
+  if (q_start[b + 1] - qs != 1) {
+    pdl_wait();  // this kernel ends only after the one before it: what follows may count on both
+    return;
+  }
   const int group = n_q / n_kv, m_tiles = (group + 15) / 16;
   const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y - kvh * m_tiles;
   const int split = blockIdx.x;
@@ -386,9 +413,17 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   };
   // this warp's tiles: tile_lo + warp, + DC_WARPS, ...; the first copies start before anything else
   int t_issue = tile_lo + warp;
-#pragma unroll
-  for (int s = 0; s < DC_STAGES - 1; ++s) {
-    if (t_issue < tile_hi) issue(t_issue, s);
+  int staged = 0;
+  for (; staged < DC_STAGES - 1; ++staged) {
+    // a tile that reaches the newest key waits for the kernel that writes it
+    if (t_issue < tile_hi && start + (t_issue + 1) * DC_BN >= kvl_load) break;
+    if (t_issue < tile_hi) issue(t_issue, staged);
+    cp_async_commit();
+    t_issue += DC_WARPS;
+  }
+  pdl_wait();
+  for (; staged < DC_STAGES - 1; ++staged) {
+    if (t_issue < tile_hi) issue(t_issue, staged);
     cp_async_commit();
     t_issue += DC_WARPS;
   }
@@ -556,6 +591,13 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     const int head = head0 + row;
     if (splits == 1) {
       out[(size_t)qs * out_stride + (size_t)head * D + dim] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else if constexpr (CLUSTER) {
+      float* mine = reinterpret_cast<float*>(smem + DC_MERGE_BYTES);  // [16][D + 2], beside the warps' states
+      mine[row * (D + 2) + dim] = num;
+      if (dim == 0) {
+        mine[row * (D + 2) + D] = big;
+        mine[row * (D + 2) + D + 1] = den;
+      }
     } else {
       const size_t slot = ((size_t)b * n_q + head) * splits + split;
       part_acc[slot * D + dim] = num;
@@ -563,6 +605,31 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
         part_ml[slot * 2] = big;
         part_ml[slot * 2 + 1] = den;
       }
+    }
+  }
+  if constexpr (CLUSTER) {
+    if (splits > 1) {
+      cluster_sync();  // every split's state is in its shared memory
+      const uint32_t mine = smem_u32(smem) + DC_MERGE_BYTES;
+      const int items = n_heads * D, share = (items + splits - 1) / splits;
+      const int hi_item = min(items, (split + 1) * share);
+      for (int i = split * share + tid; i < hi_item; i += DC_THREADS) {
+        const int row = i / D, dim = i - row * D;
+        float big = -INFINITY;
+        for (int sp = 0; sp < splits; ++sp)
+          big = fmaxf(big, ld_cluster_f32(map_to_rank(mine + (row * (D + 2) + D) * 4, sp)));
+        float num = 0.f, den = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {  // ascending split order, as the merge kernel
+          const uint32_t base = map_to_rank(mine + row * (D + 2) * 4, sp);
+          const float ms = ld_cluster_f32(base + D * 4);
+          const float wt = (ms == -INFINITY) ? 0.f : exp2f(ms - big);
+          num += wt * ld_cluster_f32(base + dim * 4);
+          den += wt * ld_cluster_f32(base + (D + 1) * 4);
+        }
+        out[(size_t)qs * out_stride + (size_t)(head0 + row) * D + dim] =
+            __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      }
+      cluster_sync();  // no CTA leaves while another still reads its shared memory
     }
   }
   if constexpr (FUSED) {
@@ -647,24 +714,45 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
                          block_table, max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, min_q_len);
 }
 
-// scratch: lab_attention_decode_scratch_floats(...) floats when splits > 1 (may be null otherwise).
-LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
-                                    const void* cache_v, const int* q_start, const int* kv_len,
-                                    const int* block_table, int max_blocks, int requests, int n_q, int n_kv,
-                                    int page_size, int num_pages, int window, float scale, int splits, float* scratch,
-                                    cudaStream_t stream) {
+static int decode_launch(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
+                         const void* cache_v, const int* q_start, const int* kv_len, const int* block_table,
+                         int max_blocks, int requests, int n_q, int n_kv, int page_size, int num_pages, int window,
+                         float scale, int splits, float* scratch, bool may_cluster, cudaStream_t stream) {
   if (requests <= 0) return 0;
-  if (n_q % n_kv || splits < 1 || (splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
+  const bool cluster = may_cluster && splits >= 2 && splits <= DC_MAX_CLUSTER;
+  if (n_q % n_kv || splits < 1 || (splits > 1 && !cluster && scratch == nullptr)) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DC_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DC_SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int group = n_q / n_kv, m_tiles = (group + 15) / 16;
+  dim3 grid(splits, n_kv * m_tiles, requests);
+  if (cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DC_THREADS);
+    cfg.dynamicSmemBytes = DC_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_lab_pdl ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel<false, true>, (__nv_bfloat16*)out, out_stride,
+                                   (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v,
+                                   q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
+                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr, FusedDecodeArgs{});
+  }
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
-  dim3 grid(splits, n_kv * m_tiles, requests);
   cudaError_t e = lab_launch(attention_decode_kernel<false>, grid, dim3(DC_THREADS), (size_t)DC_SMEM, stream,
                              (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                              (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, q_start, kv_len, block_table,
@@ -675,6 +763,19 @@ LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, in
     e = lab_launch(attention_merge_kernel, dim3(requests, n_q), dim3(D), 0, stream, (__nv_bfloat16*)out, out_stride,
                    q_start, n_q, splits, (const float*)part_acc, (const float*)part_ml);
   return (int)e;
+}
+
+// cluster_merge != 0 and 2 <= splits <= 8: the splits merge inside the kernel, through their cluster's
+// shared memory (worth it while all CTAs of the launch are resident at once); else the merge kernel
+// does it, from scratch: lab_attention_decode_scratch_floats(...) floats (may be null when unused).
+LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
+                                    const void* cache_v, const int* q_start, const int* kv_len,
+                                    const int* block_table, int max_blocks, int requests, int n_q, int n_kv,
+                                    int page_size, int num_pages, int window, float scale, int splits, float* scratch,
+                                    int cluster_merge, cudaStream_t stream) {
+  return decode_launch(out, out_stride, q, q_stride, cache_k, cache_v, q_start, kv_len, block_table, max_blocks,
+                       requests, n_q, n_kv, page_size, num_pages, window, scale, splits, scratch, cluster_merge != 0,
+                       stream);
 }
 
 // Decode attention fused with what precedes it in a pure-decode step: the sum of the fused
@@ -773,7 +874,7 @@ LAB_EXPORT int lab_attention_decode_noalloc(void* out, int out_stride, const voi
   }
   // Every split writes its (acc, max, sum) before the merge reads it, splits without keys
   // included, so nothing in the array has to start at zero and nothing is cleared.
-  return lab_attention_decode(out, out_stride, q, q_stride, cache_k, cache_v, q_start, kv_len, block_table, max_blocks,
-                              requests, n_q, n_kv, page_size, num_pages, window, scale, splits,
-                              g_noalloc_address[device], stream);
+  return decode_launch(out, out_stride, q, q_stride, cache_k, cache_v, q_start, kv_len, block_table, max_blocks,
+                       requests, n_q, n_kv, page_size, num_pages, window, scale, splits, g_noalloc_address[device],
+                       false, stream);
 }

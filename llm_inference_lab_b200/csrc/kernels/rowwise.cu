@@ -77,6 +77,9 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, T* __restrict__ x, const T
   __shared__ float scratch[32];
   extern __shared__ float rowbuf[];  // hidden floats
   pdl_trigger();
+  // The norm weight depends on nothing that runs before this kernel: its first element per thread
+  // is fetched while the kernel before this one is still finishing.
+  const float w_first = threadIdx.x < hidden ? to_f32<T>(w[threadIdx.x]) : 0.f;
   pdl_wait();
   int in_row = blockIdx.x;
   if (rows) {
@@ -87,9 +90,6 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, T* __restrict__ x, const T
     }
   }
   T* xr = x + (size_t)in_row * hidden;
-  // The norm weight does not depend on the row's sum: its first element per thread is fetched now,
-  // so that its latency runs beside the loads and the reduction below.
-  const float w_first = threadIdx.x < hidden ? to_f32<T>(w[threadIdx.x]) : 0.f;
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = to_f32<T>(xr[i]);
@@ -254,7 +254,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      const int* __restrict__ slots, T* __restrict__ cache_k, T* __restrict__ cache_v,
                                      int n_q, int n_kv, int d, int page_size, int num_pages, int heads_per_block) {
   pdl_trigger();
-  pdl_wait();
+  // Before pdl_wait() only what no kernel of this step writes is read (positions, slots, the
+  // frequencies): the angle of this thread's first pair is ready when the projection arrives.
   const int t = blockIdx.x;
   const int n_heads = n_q + 2 * n_kv;  // [0, n_q) q heads, then n_kv k heads, then n_kv v heads
   const int head_lo = blockIdx.y * heads_per_block;
@@ -281,6 +282,12 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     }
   }
   const int items = (head_hi - head_lo) * d;
+  float sn0 = 0.f, cs0 = 1.f;
+  {
+    const int i = threadIdx.x % d;
+    if ((int)threadIdx.x < items && i < rotary_dim / 2) sincosf(pos * inv_freq[i], &sn0, &cs0);
+  }
+  pdl_wait();
   for (int e = threadIdx.x; e < items; e += blockDim.x) {
     const int head = head_lo + e / d, i = e % d;
     const size_t col0 = (size_t)head * d;
@@ -295,9 +302,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     }
     const int half = (head < n_q + n_kv) ? rotary_dim / 2 : 0;  // v is not rotated
     if (i < half) {
-      const float ang = pos * inv_freq[i];
-      float sn, cs;
-      sincosf(ang, &sn, &cs);
+      float sn = sn0, cs = cs0;
+      if (e != (int)threadIdx.x) sincosf(pos * inv_freq[i], &sn, &cs);
       const float c = round_to<T>(cs), sv = round_to<T>(sn);
       // Both halves are read before either is written: a thread owns the pair (i, i + half).
       const float lo = value(col0 + i), hi = value(col0 + i + half);

@@ -407,6 +407,13 @@ def linear_gated(x, w_gate_up):
 PREFILL_KERNEL = "auto"
 
 
+# With 2 to 8 splits, and all CTAs of the launch resident at once, the decode kernel merges the splits
+# itself: the splits of a (request, kv head) form a thread-block cluster and read one another's shared
+# memory.  (With more CTAs than SMs the cluster launch measured slower than the merge kernel.)
+# False: always the merge kernel.
+CLUSTER_MERGE = True
+
+
 def attention_tc_supported(head_dim: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 128
 
@@ -414,10 +421,15 @@ def attention_tc_supported(head_dim: int) -> bool:
 def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int) -> int:
     """How many ways the keys of a decoding request are split across CTAs.  A warp needs about
     two microseconds per 32-key tile (its instructions depend on one another), so for latency a
-    CTA's four warps should get two tiles each at most: 256 keys per CTA, as far as the GPU has
-    room for the CTAs (the reference splits 1..16 ways,
+    CTA's four warps should get one tile each: 128 keys per CTA while all CTAs of the launch find
+    room at once and the splits (8 at most) can merge inside their cluster; else two tiles each,
+    256 keys per CTA, as far as the GPU has room for the CTAs (the reference splits 1..16 ways,
     rust/engine/src/runner/model/qwen2/engine.rs:1597-1617)."""
     ctas = max(1, n_decode * n_kv * (-(-group // 16)))
+    if CLUSTER_MERGE:
+        fine = min(8, -(-max_kv_len // 128), SM_COUNT // ctas)
+        if fine >= 2:
+            return int(fine)
     room = max(1, (4 * SM_COUNT) // ctas)
     return int(max(1, min(room, -(-max_kv_len // 256), 32)))
 
@@ -456,15 +468,19 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
         if splits is None:
             span = min(max_kv_len, window) if window else max_kv_len
             splits = decode_splits(n_decode, n_kv, n_q // n_kv, span)
-        if splits > 1:
+        ctas = n_decode * n_kv * (-(-(n_q // n_kv) // 16)) * splits
+        in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and ctas <= SM_COUNT
+        if splits > 1 and not in_cluster:
             need = n_requests * n_q * splits * (head_dim + 2)
             if scratch is None or scratch.numel() < need:
                 scratch = torch.empty((need,), dtype=torch.float32, device=q.device)
+        else:
+            scratch = None
         _check(L.lab_attention_decode(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                       _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1],
                                       n_requests, n_q, n_kv, page_size, num_pages, window, ctypes.c_float(scale),
-                                      splits, _ptr(scratch if splits > 1 else None), _stream()), "attention_decode",
-               2 if splits > 1 else 1)
+                                      splits, _ptr(scratch), 1 if in_cluster else 0, _stream()), "attention_decode",
+               2 if splits > 1 and not in_cluster else 1)
     return out
 
 

@@ -380,6 +380,28 @@ def test_attention_decode_splits(splits):
         assert rel_err(g, w) < 2e-2
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,window,splits", [
+    (14, 2, 64, 0, 2), (14, 2, 64, 0, 8), (6, 1, 32, 0, 3), (4, 4, 16, 0, 5), (8, 2, 128, 100, 4),
+    (40, 2, 48, 0, 7),   # groups of 20 heads: two tiles of heads per kv head
+])
+def test_attention_decode_cluster_merge(n_q, n_kv, d, window, splits):
+    """The merge of the splits inside the decode kernel (through the cluster's shared memory) gives the
+    same bits as the merge kernel, and both are right; decode rows stand beside a prompt's portion."""
+    requests = [(777, 1), (64, 5), (33, 1), (1, 1), (500, 1), (257, 1)]
+    old = ops().CLUSTER_MERGE
+    outs = {}
+    try:
+        for on in (True, False):
+            ops().CLUSTER_MERGE = on
+            outs[on], want = run_attention("tc", requests, n_q, n_kv, d, 16, window, torch.bfloat16, seed=11,
+                                           splits=splits)
+    finally:
+        ops().CLUSTER_MERGE = old
+    for a, b, w in zip(outs[True], outs[False], want):
+        assert torch.equal(a, b)
+        assert rel_err(a, w) < 2e-2
+
+
 @pytest.mark.parametrize("partial", [False, True])
 @pytest.mark.parametrize("n_q,n_kv,d,ps,window,rot,kvs,splits", [
     (14, 2, 64, 16, 0, 64, [640, 33, 1, 257], None), (6, 1, 32, 8, 0, 32, [100, 7], 3),
