@@ -58,9 +58,6 @@ class Qwen2Config(ModelConfig):
             raise ConfigError(f"'head_dim' must be a multiple of 16 up to 256, got {self.head_dim}")
         if self.num_attention_heads % self.num_key_value_heads:
             raise ConfigError("'num_attention_heads' must be a multiple of 'num_key_value_heads'")
-        if self.hidden_size % 8 or self.intermediate_size % 8:
-            raise ConfigError("'hidden_size' and 'intermediate_size' must be multiples of 8 "
-                              "(16-byte rows for bfloat16 copies)")
         if self.use_sliding_window:
             if not self.sliding_window or self.sliding_window <= 0:
                 raise ConfigError("'use_sliding_window' is true but 'sliding_window' is not a positive integer")

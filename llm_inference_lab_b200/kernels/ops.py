@@ -377,11 +377,18 @@ def _pick_prefill_tiles(T: int, n_out: int, K: int, allow_partial: bool) -> tupl
     return 128, 1
 
 
+def _tc_operands(x, w) -> bool:
+    """Whether TMA can describe the operands: rows of 16-byte multiples that start on 16-byte
+    boundaries.  Widths that are no multiple of 8 go to the plain kernel instead."""
+    return (x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1 and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def linear(x, w, bias=None, out_f32=False, allow_partial=False):
     """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
     products [splits, tokens, out], without the bias, that the consumer sums (`add_rmsnorm`,
     `rope_kv_write`)."""
-    if x.dtype == torch.float32 or _force_plain:
+    if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w):
         return gemm_plain(x, w, bias, out_f32=out_f32)
     T = x.shape[0]
     if T > 128:
@@ -397,7 +404,7 @@ def linear(x, w, bias=None, out_f32=False, allow_partial=False):
 
 def linear_gated(x, w_gate_up):
     """silu(x @ wg.T) * (x @ wu.T) with w_gate_up = [wg; wu]."""
-    if x.dtype == torch.float32 or _force_plain:
+    if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w_gate_up):
         return gemm_plain(x, w_gate_up, None, gated=True)
     return gemm_tc(x, w_gate_up, None, gated=True)
 

@@ -32,8 +32,23 @@ TINY_C = dict(
     rope_theta=50000.0, max_position_embeddings=192, hidden_act="silu", tie_word_embeddings=False,
     use_sliding_window=True, sliding_window=20, max_window_layers=2, eos_token_id=None)
 
+# Two with sizes the tensor-core kernels cannot take as they are: a width and an intermediate size
+# that are no multiples of 8 (rows of no 16-byte multiple), a head of 80, and a head of 160 (beyond
+# the tensor-core attention); heads * head size differs from the width.
+TINY_D = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=257, hidden_size=100, intermediate_size=90,
+    num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=80, rms_norm_eps=1e-5,
+    rope_theta=10000.0, max_position_embeddings=160, hidden_act="silu", tie_word_embeddings=True,
+    use_sliding_window=False, eos_token_id=3)
+TINY_E = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=129, hidden_size=72, intermediate_size=136,
+    num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5, head_dim=160, rms_norm_eps=1e-6,
+    rope_theta=500000.0, max_position_embeddings=128, hidden_act="silu", tie_word_embeddings=False,
+    use_sliding_window=False, eos_token_id=None)
+
 TINY = {"A": (TINY_A, dict(seed=0, page_size=4)), "B": (TINY_B, dict(seed=1, page_size=16)),
-        "C": (TINY_C, dict(seed=2, page_size=8))}
+        "C": (TINY_C, dict(seed=2, page_size=8)), "D": (TINY_D, dict(seed=3, page_size=32)),
+        "E": (TINY_E, dict(seed=4, page_size=64))}
 
 # Random weights N(0, 0.02) make attention nearly uniform and would hide a misplaced key;
 # the q and k projections are scaled up so that scores spread over several units (more would only amplify rounding).

@@ -93,6 +93,15 @@ def test_replay(tmp_path_factory, name, dtype, kind):
         assert worst <= BF16_CUT * scale, f"cut changed bfloat16 logits by {worst / scale:.3e} of their size"
 
 
+@pytest.mark.parametrize("kind", ["whole", "mixed"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_replay_sizes_beyond_the_tensor_core_kernels(tmp_path_factory, name, dtype, kind):
+    """Widths that are no multiple of 8 and heads of 80 and 160: the engine serves them (through the
+    plain kernels where the tensor-core ones cannot), never with a wrong result."""
+    test_replay(tmp_path_factory, name, dtype, kind)
+
+
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16")])
 def test_trace_run_program(tmp_path_factory, tmp_path, name, dtype):
     """bin/trace_run as a user starts it: mixed trace, pool sized by --max-tokens."""
