@@ -53,10 +53,17 @@ LAB_EXPORT int lab_embed(void* out, const void* table, const int* ids, int token
 // of the preceding matrix product, summed here in a fixed order.
 // ----------------------------------------------------------------------------------------
 // Sum of the split-K partial products of one element, in ascending split order; the loads of
-// four splits are issued together so that their latencies overlap.
+// eight (then four) splits are issued together so that their latencies overlap.
 __device__ __forceinline__ float sum_partials(const float* __restrict__ p, int splits, size_t stride) {
   float acc = 0.f;
   int s = 0;
+  for (; s + 8 <= splits; s += 8) {
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = p[(size_t)(s + j) * stride];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += a[j];
+  }
   for (; s + 4 <= splits; s += 4) {
     const float a0 = p[(size_t)s * stride], a1 = p[(size_t)(s + 1) * stride], a2 = p[(size_t)(s + 2) * stride],
                 a3 = p[(size_t)(s + 3) * stride];
