@@ -128,9 +128,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;                  // layout: 128-byte swizzle
   return d;
 }
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = m (64 or 128), N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
@@ -181,29 +181,37 @@ struct Params {
   int m_tiles, n_tiles, splits;  // tiles on the M side, on the N side, and split-K planes
 };
 
-template <int BN, bool GATED, bool SWAP>
+// TM: rows of the M-side tile, 128 or (swapped orientation only) 64.  With 64 rows an output has twice
+// the tiles, so a decode step's products spread over more SMs and a CTA's share of the weights fits
+// its shared memory whole: all of it is requested before the wait on the preceding kernel.  The
+// accumulator of an M = 64 MMA lies in lanes 0..15 of each quarter of tensor memory (row r in lane
+// 32 * (r / 16) + r % 16), so each epilogue warp still reads its own quarter.
+template <int TM, int BN, bool GATED, bool SWAP>
 struct Shape {
-  static constexpr int A_BYTES = BM * BK * 2;
+  static_assert(TM == 128 || (TM == 64 && SWAP), "64-row tiles exist in swapped orientation only");
+  static constexpr int A_BYTES = TM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // gated + swapped: the epilogue warps exchange gate and up values through a buffer of their own
-  static constexpr int EXCHANGE_BYTES = (GATED && SWAP) ? ((BM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
+  static constexpr int EXCHANGE_BYTES = (GATED && SWAP) ? ((TM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
   static constexpr int STAGES_RAW = (SMEM_BUDGET - EXCHANGE_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+  static constexpr int STAGES_CAP = TM == 64 ? 16 : 10;
+  static constexpr int STAGES = STAGES_RAW > STAGES_CAP ? STAGES_CAP : STAGES_RAW;
   static constexpr int ACC_COLS = BN < 32 ? 32 : BN;
   static constexpr int ACC_BUFS = 2 * ACC_COLS <= 512 ? 2 : 1;  // accumulators in tensor memory
   static constexpr int TMEM_COLS = ACC_BUFS * ACC_COLS;         // a power of two >= 32
-  static constexpr int SMEM = STAGES * STAGE_BYTES + EXCHANGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + EXCHANGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static_assert(STAGES >= 2, "the tile does not leave room for a pipeline");
+  static_assert((2 * STAGES + 4) * 8 + 8 <= 512, "the barriers outgrow their 512 bytes");
 };
 
 // A persistent CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Tiles are numbered with
 // the M side fastest, so CTAs that run at the same time share the N-side operand in L2.
 // Two accumulators in tensor memory let the epilogue of one tile run beside the MMAs of the next.
-template <int BN, bool GATED, bool SWAP, typename OutT>
+template <int TM, int BN, bool GATED, bool SWAP, typename OutT>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_b, Params p) {
-  using S = Shape<BN, GATED, SWAP>;
+  using S = Shape<TM, BN, GATED, SWAP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* exchange = reinterpret_cast<float*>(tiles + S::STAGES * S::STAGE_BYTES);
@@ -216,7 +224,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int M_ROWS = (GATED && SWAP) ? BM / 2 : BM;    // output rows per tile on the M side
+  constexpr int M_ROWS = (GATED && SWAP) ? TM / 2 : TM;    // output rows per tile on the M side
   constexpr int N_ROWS = (GATED && !SWAP) ? BN / 2 : BN;   // rows of the N-side operand per tile
   const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
 
@@ -262,7 +270,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         uint8_t* b_dst = a_dst + S::A_BYTES;
         if (SWAP) {
           tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
-          if (GATED) tma_load_2d(a_dst + (BM / 2) * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
+          if (GATED) tma_load_2d(a_dst + (TM / 2) * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
         } else {
           tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
           if (GATED) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kx, p.up_offset + n0);
@@ -314,7 +322,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
-      constexpr uint32_t idesc = instr_desc(BN);
+      constexpr uint32_t idesc = instr_desc(TM, BN);
       int it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
@@ -347,6 +355,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   } else {
     // ---- epilogue: warps 2..5, each reads its quarter of the 128 accumulator lanes ----
     const int quarter = warp & 3;
+    constexpr int QROWS = TM / 4;            // tile rows in a quarter: its first QROWS lanes
+    const bool has_row = lane < QROWS;
     pdl_wait();  // the output may still be read by an earlier kernel until it has completed
     int local = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
@@ -357,7 +367,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag);
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * S::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      const int m = m0 + quarter * 32 + lane;  // this thread's row on the M side
+      const int m = m0 + quarter * QROWS + lane;  // this thread's row on the M side (if has_row)
       const bool partial = p.split_stride != 0;
       // Decided once per thread; the gated swapped epilogue meets at named barriers, which every
       // epilogue thread reaches whatever it decided.
@@ -460,31 +470,35 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         // thread = output feature; columns = tokens.  Lanes 0..63 hold gate values, lanes 64..127
         // the up values of the same 64 features: all go through the exchange buffer, then each of
         // the 128 threads finishes one feature for half of the tokens.
-        const int lane_global = quarter * 32 + lane;
+        const int tile_row = quarter * QROWS + lane;
 #pragma unroll 1
         for (int c = 0; c < BN / 16 && go; ++c) {
           if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
           float v[16];
           tmem_ld16(lane_addr + c * 16, v);
+          if (has_row) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) exchange[lane_global * (BN + 1) + c * 16 + j] = v[j];
+            for (int j = 0; j < 16; ++j) exchange[tile_row * (BN + 1) + c * 16 + j] = v[j];
+          }
         }
         release();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int t = threadIdx.x - 64, f = t & 63, h = t >> 6;
+        // the 128 threads share the tile's TM / 2 features: PARTS threads per feature, each a part of the tokens
+        constexpr int HALF = TM / 2, PARTS = 128 / HALF;
+        const int t = threadIdx.x - 64, f = t % HALF, h = t / HALF;
         if (go && m0 + f < p.m_rows) {
           __nv_bfloat16* dst = (__nv_bfloat16*)p.out + m0 + f;
-          for (int col = h * (BN / 2); col < (h + 1) * (BN / 2); ++col) {
+          for (int col = h * (BN / PARTS); col < (h + 1) * (BN / PARTS); ++col) {
             const int tok = n0 + col;
             if (tok >= p.n_rows) break;
             dst[(size_t)tok * p.ld_out] =
-                __float2bfloat16_rn(silu_gate(exchange[f * (BN + 1) + col], exchange[(64 + f) * (BN + 1) + col]));
+                __float2bfloat16_rn(silu_gate(exchange[f * (BN + 1) + col], exchange[(HALF + f) * (BN + 1) + col]));
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
       } else {
         // thread = output feature m; columns = tokens
-        const float b = (p.bias && !partial && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
+        const float b = (p.bias && !partial && has_row && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
         int c = 0;
 #pragma unroll 1
         for (; c < BN / 16 && go; ++c) {
@@ -496,7 +510,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
           if (c == BN / 16 - 1 || t + 16 >= p.n_rows) release();
-          if (m >= p.m_rows) continue;
+          if (!has_row || m >= p.m_rows) continue;
           if (partial) {
             float* dst = (float*)p.out + split * p.split_stride + m;
 #pragma unroll
@@ -553,11 +567,11 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int bo
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int BN, bool GATED, bool SWAP, typename OutT>
+template <int TM, int BN, bool GATED, bool SWAP, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
-  using S = Shape<BN, GATED, SWAP>;
+  using S = Shape<TM, BN, GATED, SWAP>;
   static bool configured = false;
-  auto kern = gemm_tc_kernel<BN, GATED, SWAP, OutT>;
+  auto kern = gemm_tc_kernel<TM, BN, GATED, SWAP, OutT>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -567,13 +581,24 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
 }
 
 template <bool GATED, bool SWAP, typename OutT>
-int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t s) {
+int dispatch_bn(int bm, int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid,
+                cudaStream_t s) {
+  if constexpr (SWAP) {
+    if (bm == 64) {
+      switch (bn) {
+        case 16: return launch<64, 16, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+        case 32: return launch<64, 32, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+        case 64: return launch<64, 64, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+      }
+      return (int)cudaErrorInvalidValue;
+    }
+  }
   switch (bn) {
-    case 16: if constexpr (SWAP) return launch<16, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 32: if constexpr (SWAP) return launch<32, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 64: return launch<64, GATED, SWAP, OutT>(ma, mb, p, grid, s);
-    case 128: return launch<128, GATED, SWAP, OutT>(ma, mb, p, grid, s);
-    case 256: return launch<256, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+    case 16: if constexpr (SWAP) return launch<128, 16, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 32: if constexpr (SWAP) return launch<128, 32, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 64: return launch<128, 64, GATED, SWAP, OutT>(ma, mb, p, grid, s);
+    case 128: if constexpr (!(GATED && SWAP)) return launch<128, 128, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 256: if constexpr (!(GATED && SWAP)) return launch<128, 256, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
   }
   return (int)cudaErrorInvalidValue;
 }
@@ -583,11 +608,13 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Para
 // x: [tokens, K] bf16 (row stride ldx), w: [n_out (x2 when gated), K] bf16 contiguous.
 // out: bf16 or f32 [tokens, ld_out]; with splits > 1, `out` is the partial buffer
 // [splits, tokens, ld_out] of floats (no bias, not gated).
-// swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256).
+// swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256); bm: rows of the
+// M-side tile, 128, or 64 (swapped orientation with bn <= 64 only).
 LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
-                           int ldx, int ld_out, int gated, int out_f32, int swap, int bn, int splits,
+                           int ldx, int ld_out, int gated, int out_f32, int swap, int bm, int bn, int splits,
                            cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
+  if (bm != 128 && !(bm == 64 && swap && bn <= 64)) return (int)cudaErrorInvalidValue;
   if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA
   if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return (int)cudaErrorInvalidValue;  // 16-byte bases for TMA
   if (splits < 1 || (splits > 1 && (gated || !out_f32))) return (int)cudaErrorInvalidValue;
@@ -612,7 +639,7 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
     p.m_tiles = (tokens + BM - 1) / BM;
     p.n_tiles = (n_out + box_b - 1) / box_b;
   } else {
-    const int m_rows_tile = gated ? BM / 2 : BM;
+    const int m_rows_tile = gated ? bm / 2 : bm;
     if ((rc = make_map(&ma, w, w_rows, K, K, m_rows_tile))) return rc;
     if ((rc = make_map(&mb, x, tokens, K, ldx, bn))) return rc;
     if (gated && bn > 64) return (int)cudaErrorInvalidValue;  // the exchange buffer is sized for up to 64 tokens
@@ -637,22 +664,14 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
   // that valid outputs never mix the halves (rows >= n_out are masked in the epilogue), but the
   // up half must start at a row the map can address with the same box.
   if (gated) {
-    if (swap) {
-      if (out_f32) return (int)cudaErrorInvalidValue;
-      switch (bn) {
-        case 16: return launch<16, true, true, __nv_bfloat16>(ma, mb, p, grid, stream);
-        case 32: return launch<32, true, true, __nv_bfloat16>(ma, mb, p, grid, stream);
-        case 64: return launch<64, true, true, __nv_bfloat16>(ma, mb, p, grid, stream);
-      }
-      return (int)cudaErrorInvalidValue;
-    }
     if (out_f32) return (int)cudaErrorInvalidValue;
-    return dispatch_bn<true, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+    if (swap) return dispatch_bn<true, true, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
+    return dispatch_bn<true, false, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
   }
   if (swap) {
-    if (out_f32) return dispatch_bn<false, true, float>(bn, ma, mb, p, grid, stream);
-    return dispatch_bn<false, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+    if (out_f32) return dispatch_bn<false, true, float>(bm, bn, ma, mb, p, grid, stream);
+    return dispatch_bn<false, true, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
   }
-  if (out_f32) return dispatch_bn<false, false, float>(bn, ma, mb, p, grid, stream);
-  return dispatch_bn<false, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+  if (out_f32) return dispatch_bn<false, false, float>(bm, bn, ma, mb, p, grid, stream);
+  return dispatch_bn<false, false, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
 }

@@ -304,11 +304,13 @@ def force_plain(flag: bool) -> bool:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
             out_f32: bool = False, swap: bool | None = None, bn: int | None = None, splits: int = 1,
-            out: torch.Tensor | None = None) -> torch.Tensor:
+            out: torch.Tensor | None = None, bm: int | None = None) -> torch.Tensor:
     """out = x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulate).
 
-    `swap` puts output features on the 128-row side of the MMA (few tokens); `bn` is the
-    tile on the other side; `splits` > 1 returns 32-bit partial products [splits, tokens, out].
+    `swap` puts output features on the M side of the MMA (few tokens); `bn` is the tile on the
+    other side; `bm` the rows of the M-side tile (128, or 64 when swapped with bn <= 64: chosen
+    when 128-row tiles would leave SMs without work); `splits` > 1 returns 32-bit partial
+    products [splits, tokens, out].
     """
     _on_gpu(x, w, bias, out)
     T, K = x.shape
@@ -328,6 +330,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
                 bn *= 2
         else:
             bn = 256 if gated else 128
+    if bm is None:
+        bm = _pick_bm(T, n_out, gated, swap, bn)
     if splits > 1:
         if gated or bias is not None:
             raise KernelError("split-K takes no bias and no gate")
@@ -344,8 +348,16 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
         assert out.dtype == odt and out.stride(1) == 1
         ld_out, f32 = out.stride(0), out_f32
     _check(lib("gemm_tc").lab_gemm_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                      int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
+                                      int(gated), int(f32), int(swap), bm, bn, splits, _stream()), "gemm_tc")
     return out
+
+
+def _pick_bm(T: int, n_out: int, gated: bool, swap: bool, bn: int) -> int:
+    """Rows of the M-side tile.  Tiles of 64 rows (swapped orientation, bn <= 64) double the CTAs of
+    a decode step's products, but measured slower at the benchmark's sizes (a step of 0.85 ms
+    against 0.82 ms): a step's kernels overlap under programmatic dependent launch, and more,
+    smaller CTAs get in one another's way.  So 128 unless the caller asks."""
+    return 128
 
 
 def _pick_splits(T: int, n_out: int, K: int) -> int:

@@ -223,6 +223,33 @@ def test_gemm_tc_exact(T, N, K, gated, bias, swap, bn, splits):
     assert torch.equal(out.double().cpu(), ref)
 
 
+@pytest.mark.parametrize("bm", [64, 128])
+@pytest.mark.parametrize("T,N,K,gated,bias,bn,splits", [
+    (8, 1152, 896, False, True, 16, 1), (8, 896, 4864, False, False, 16, 10), (5, 200, 104, True, False, 16, 1),
+    (1, 4864, 896, True, False, 16, 1), (33, 1000, 200, False, True, 64, 1), (20, 20000, 64, False, False, 32, 1),
+    (64, 4864, 896, True, False, 64, 1), (40, 136, 1000, True, False, 64, 1), (17, 72, 2000, False, False, 32, 7),
+])
+def test_gemm_tc_swapped_tile_rows(bm, T, N, K, gated, bias, bn, splits):
+    """Swapped orientation with M-side tiles of 64 and of 128 rows: both exact, outputs with several
+    tiles per CTA, features that fill no whole tile, split K, the gated epilogue."""
+    g = torch.Generator().manual_seed(16)
+    x = (torch.randint(-4, 5, (T, K), generator=g).float() / 4).bfloat16()
+    w = (torch.randint(-4, 5, (N * (2 if gated else 1), K), generator=g).float() / 8).bfloat16()
+    b = (torch.randint(-8, 9, (N,), generator=g).float() / 2).bfloat16() if bias else None
+    out = ops().gemm_tc(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), gated=gated,
+                        out_f32=not gated, swap=True, bn=bn, splits=splits, bm=bm)
+    ops().take_device_errors()
+    ref = x.double() @ w.double().T
+    if splits > 1:
+        assert torch.equal(out.double().sum(0).cpu(), ref)
+    elif gated:
+        gq, uq = ref[:, :N].bfloat16().double(), ref[:, N:].bfloat16().double()
+        want = torch.from_numpy(plain_silu(gq.numpy())).bfloat16().double() * uq
+        assert rel_err(out, want) < 1e-2
+    else:
+        assert torch.equal(out.double().cpu(), ref + (b.double() if bias else 0))
+
+
 def test_gemm_tc_guards():
     """Outputs beyond the valid rows and columns are not touched (NaN-prefilled buffer)."""
     g = torch.Generator().manual_seed(7)
