@@ -449,7 +449,7 @@ def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int) -> int:
         fine = min(8, -(-max_kv_len // 128), SM_COUNT // ctas)
         if fine >= 2:
             return int(fine)
-    room = max(1, (4 * SM_COUNT) // ctas)
+    room = max(1, (2 * SM_COUNT) // ctas)      # two CTAs fit an SM: no second round of CTAs
     return int(max(1, min(room, -(-max_kv_len // 256), 32)))
 
 
