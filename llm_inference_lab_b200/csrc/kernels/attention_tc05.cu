@@ -6,17 +6,20 @@
 //                    gathered page by page through the block table), S in tensor memory
 //   P = softmax(S)   four warps, one query row per thread: tcgen05.ld of the row, scale and
 //                    causal/window mask, running max and sum in 32-bit, exp2, P rounded to
-//                    bfloat16 and stored to shared memory in the swizzled layout the MMA reads
-//   O_j = P V        tcgen05.mma with V as the N-major operand (V rows lie [key][d] as cached)
+//                    bfloat16 and written back to tensor memory (tcgen05.st, two keys per column)
+//   O_j = P V        tcgen05.mma with P as the A operand from tensor memory and V as the N-major
+//                    B operand from shared memory (V rows lie [key][d] as cached)
 //   acc = acc * exp2(m_old - m_new) + O_j     in registers of the row's thread, 32-bit
-// Two S buffers, two P buffers and two O buffers let the MMAs of tile j+1 run beside the
-// softmax of tile j.  Formulas and rounding as the reference's tensor-core prefill attention
-// (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124, 1295-1452): scores scaled by
-// 1/sqrt(d) (folded into the exp2 argument), key <= query, p rounded to T before PV, o = acc / sum.
+// Two S buffers, two P buffers and two O buffers (all 512 columns of tensor memory) let the MMAs
+// of tile j+1 run beside the softmax of tile j.  Formulas and rounding as the reference's
+// tensor-core prefill attention (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124,
+// 1295-1452): scores scaled by 1/sqrt(d) (folded into the exp2 argument), key <= query, p rounded
+// to T before PV, o = acc / sum.
 //
 // Warp 0 loads (TMA; the page that holds a request's last keys is copied by hand with rows
 // beyond the length set to zero, because a masked NaN would still poison P V), warp 1 issues
-// the MMAs and owns tensor memory, warps 2-5 do the softmax.  Every wait is bounded.
+// the MMAs (the whole warp walks the loop, one elected lane issues) and owns tensor memory, warps
+// 2-5 do the softmax.  Every wait is bounded.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -32,19 +35,19 @@ static_assert(D == 64, "the tcgen05 attention kernel is built for heads of 64");
 constexpr int BM = 128;        // query rows per CTA
 constexpr int BN = 128;        // keys per tile
 constexpr int THREADS = 192;
-constexpr int KV_STAGES = 3;
+constexpr int KV_STAGES = 4;
 constexpr int ROW = 128;       // bytes of a swizzled row: 64 bf16
 constexpr int Q_BYTES = BM * ROW;
 constexpr int KV_TILE = BN * ROW;         // one K or V tile
-constexpr int P_HALF = BM * ROW;          // P for 64 keys
-constexpr int P_BYTES = 2 * P_HALF;       // P for 128 keys
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + Q_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE;
-constexpr int OFF_P = OFF_V + KV_STAGES * KV_TILE;
-constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_TILE;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
-constexpr int TM_S = 0, TM_O = 2 * BN, TMEM_COLS = 512;
+// tensor memory columns: two S buffers (32-bit scores), two O buffers, two P buffers (bfloat16
+// pairs: 128 keys in 64 columns)
+constexpr int TM_S = 0, TM_O = 2 * BN, TM_P = TM_O + 2 * D, P_COLS = BN / 2, TMEM_COLS = 512;
+static_assert(TM_P + 2 * P_COLS <= TMEM_COLS, "tensor memory holds S, O and P twice");
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,17 +101,35 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// The MMA and commit wrappers are called by every lane of a converged warp with the same
+// arguments; one elected lane issues the instruction.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
+      : "memory");
 }
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// The same with the A operand in tensor memory: lane = row, a 32-bit column holds two consecutive
+// bfloat16 elements of K (16 elements of K = 8 columns from a_tmem on).
+__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t a_tmem, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_tmem), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
 // 128-byte-swizzled tile whose rows are 128 bytes; 8-row groups lie 1024 bytes apart.  The same
@@ -138,6 +159,18 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+// 32 consecutive columns of this thread's lane are written from r[0..31].
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -229,25 +262,32 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     const int pages_per_tile = BN / page_size;  // at most 16: one lane looks up each page of a tile
     const int page_bytes = page_size * ROW;
     bool alive = true;
+    // Lane pg classifies page pg of a tile and reads its number from the block table:
+    // 0 nothing to fetch (beyond the length, or wholly before the window), 1 whole page (TMA),
+    // 2 the page that holds the request's last keys (copied by hand, rows past the length zeroed).
+    // The lookup for tile j + 1 is issued before tile j's copies, so its latency hides behind them.
+    auto classify = [&](int j, int& kind, int& page) {
+      kind = 0;
+      page = -1;
+      if (j < n_tiles && lane < pages_per_tile) {
+        const int k_lo = (t_first + j) * BN + lane * page_size;
+        if (k_lo < kvl && k_lo + page_size > lo_all) {
+          kind = k_lo + page_size > kvl ? 2 : 1;
+          page = bt[k_lo / page_size];
+        }
+      }
+    };
+    int next_kind, next_page;
+    classify(0, next_kind, next_page);
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int s = j % KV_STAGES;
       const uint32_t ph = (j / KV_STAGES) & 1;
       const int key0 = (t_first + j) * BN;
-      // Lane pg classifies page pg of the tile and reads its number from the block table, before the
-      // wait for the stage, so that the lookups' latency is hidden behind it:
-      // 0 nothing to fetch (beyond the length, or wholly before the window), 1 whole page (TMA),
-      // 2 the page that holds the request's last keys (copied by hand, rows past the length zeroed).
-      int kind = 0, page = -1;
-      if (lane < pages_per_tile) {
-        const int k_lo = key0 + lane * page_size;
-        if (k_lo < kvl && k_lo + page_size > lo_all) {
-          kind = k_lo + page_size > kvl ? 2 : 1;
-          page = bt[k_lo / page_size];
-          if (page < 0 || page >= num_pages) {  // a page inside the length and the window must exist
-            lab_set_error(LAB_ERR_PAGE_RANGE);
-            kind = 0;
-          }
-        }
+      int kind = next_kind, page = next_page;
+      classify(j + 1, next_kind, next_page);
+      if (kind != 0 && (page < 0 || page >= num_pages)) {  // a page inside the length and the window must exist
+        lab_set_error(LAB_ERR_PAGE_RANGE);
+        kind = 0;
       }
       const uint32_t tma_lanes = __ballot_sync(0xffffffffu, kind == 1);
       const uint32_t tail_lanes = __ballot_sync(0xffffffffu, kind == 2);
@@ -291,20 +331,25 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop with the same values, and one elected lane issues each MMA and
+    // commit: the operands are uniform across the warp, as the instructions want them.
+    {
       constexpr uint32_t idesc_s = instr_desc(BN, false);
       constexpr uint32_t idesc_o = instr_desc(D, true);
-      bool ok = mbar_wait(&bar->q_full, 0, abort_flag);
+      auto wait_all = [&](uint64_t* b, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(b, parity, abort_flag));
+      };
+      bool ok = wait_all(&bar->q_full, 0);
       auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES, sb = j & 1;
-        if (!mbar_wait(&bar->kv_full[s], (j / KV_STAGES) & 1, abort_flag)) return false;
-        if (!mbar_wait(&bar->s_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag)) return false;
+        if (!wait_all(&bar->kv_full[s], (j / KV_STAGES) & 1)) return false;
+        if (!wait_all(&bar->s_empty[sb], ((j >> 1) & 1) ^ 1)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_base + OFF_Q, ka = smem_base + OFF_K + s * KV_TILE;
+        // descriptors of the first 16 dimensions; each further 16 lie 32 bytes (two address units) on
+        const uint64_t qd = smem_desc_sw128(smem_base + OFF_Q), kd = smem_desc_sw128(smem_base + OFF_K + s * KV_TILE);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_bf16(tmem_base + TM_S + sb * BN, smem_desc_sw128(qa + k * 32), smem_desc_sw128(ka + k * 32), idesc_s,
-                    k > 0 ? 1u : 0u);
+          umma_bf16(tmem_base + TM_S + sb * BN, qd + 2 * k, kd + 2 * k, idesc_s, k > 0 ? 1u : 0u);
         umma_commit(&bar->s_full[sb]);
         return true;
       };
@@ -313,15 +358,16 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         if (j + 1 < n_tiles) ok = issue_s(j + 1);  // the next tile's scores run beside this tile's softmax
         if (!ok) break;
         const int s = j % KV_STAGES, sb = j & 1;
-        ok = mbar_wait(&bar->p_full[sb], (j >> 1) & 1, abort_flag) &&
-             mbar_wait(&bar->o_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag);
+        ok = wait_all(&bar->p_full[sb], (j >> 1) & 1);
+        ok = ok && wait_all(&bar->o_empty[sb], ((j >> 1) & 1) ^ 1);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t pa = smem_base + OFF_P + sb * P_BYTES, va = smem_base + OFF_V + s * KV_TILE;
+        // V rows are keys: 16 keys lie 16 * 128 bytes (128 address units) on
+        const uint64_t vd = smem_desc_sw128(smem_base + OFF_V + s * KV_TILE);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          umma_bf16(tmem_base + TM_O + sb * D, smem_desc_sw128(pa + (kk >> 2) * P_HALF + (kk & 3) * 32),
-                    smem_desc_sw128(va + kk * 16 * ROW), idesc_o, kk > 0 ? 1u : 0u);
+          umma_bf16_tmem_a(tmem_base + TM_O + sb * D, tmem_base + TM_P + sb * P_COLS + kk * 8,
+                           vd + (uint64_t)(kk * 16 * ROW / 16), idesc_o, kk > 0 ? 1u : 0u);
         umma_commit(&bar->o_full[sb]);
         umma_commit(&bar->kv_empty[s]);  // both products of this stage have been issued
       }
@@ -395,23 +441,26 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       const float base = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen no key yet
       l *= (m == -INFINITY) ? 0.f : fast_exp2(m - base);
       m = m_new;
-      // P, rounded to bfloat16, into the swizzled A-operand layout: row `row`, 16 chunks of 8 keys
-      uint8_t* p_row = smem + OFF_P + sb * P_BYTES + row * ROW;
+      // P, rounded to bfloat16, into tensor memory as the A operand of P V: this row's lane, two
+      // keys per 32-bit column
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int q8 = 0; q8 < BN / 8; ++q8) {
-        float p[8];
+      for (int c32 = 0; c32 < BN / 64; ++c32) {
+        uint32_t pk[32];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          p[e] = fast_exp2(fmaf(__uint_as_float(sr[q8 * 8 + e]), scale_log2, -base));  // 2^(-inf) = 0 for masked keys
-          sum4[e & 3] += p[e];
+        for (int i = 0; i < 32; ++i) {
+          const int c = c32 * 64 + 2 * i;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale_log2, -base));  // 2^(-inf) = 0 for masked keys
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale_log2, -base));
+          sum4[i & 1] += p0;
+          sum4[2 + (i & 1)] += p1;
+          pk[i] = pack_bf16(p0, p1);
         }
-        const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
-                                        pack_bf16(p[6], p[7]));
-        *reinterpret_cast<uint4*>(p_row + (q8 >> 3) * P_HALF + (((q8 & 7) ^ (row & 7)) << 4)) = packed;
+        tmem_st32(lane_addr + TM_P + sb * P_COLS + c32 * 32, pk);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      proxy_fence();  // the generic-proxy stores of P become visible to the tensor cores
+      tmem_st_wait();
+      tc_fence_before();  // the stores of P are ordered before the MMAs that the arrival releases
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->p_full[sb]);
       // While the tensor cores form O_j, fold in O_{j-1}.
@@ -484,7 +533,7 @@ LAB_EXPORT int lab_attention_tc05_head_dim() { return D; }
 // 1 if the kernel takes this page size (pages are fetched as TMA boxes and must tile 128 keys
 // with swizzle groups of 8 rows).
 LAB_EXPORT int lab_attention_tc05_supports(int page_size) {
-  return page_size >= 8 && page_size <= 128 && (page_size & (page_size - 1)) == 0;
+  return page_size >= 8 && page_size <= BN && (page_size & (page_size - 1)) == 0;
 }
 
 // Arguments as lab_attention_prefill; total_rows is the number of rows of q (for the TMA bounds).

@@ -103,17 +103,24 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// The MMA and commit wrappers are called by every lane of a converged warp with the same
+// arguments; one elected lane issues the instruction (measured: about half the issue time of a
+// loop that a single lane walks alone).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
+      : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]^T, bf16 inputs, 32-bit accumulate.
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
@@ -320,9 +327,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer ----
+    {
+      // ---- MMA issuer: the whole warp walks the loop, one elected lane issues ----
       constexpr uint32_t idesc = instr_desc(TM, BN);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+      };
       int it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
@@ -331,22 +341,23 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         const int buf = local % S::ACC_BUFS;
         const uint32_t use = (uint32_t)(local / S::ACC_BUFS);
         // the epilogue must have drained this accumulator (passes at once on its first use)
-        ok = mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag);
+        ok = wait_all(&acc_empty[buf], (use & 1) ^ 1);
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc_addr = tmem_base + buf * S::ACC_COLS;
         for (int i = 0; i < n_kt; ++i, ++it) {
           const int s = it % S::STAGES;
           const uint32_t ph = (it / S::STAGES) & 1;
-          ok = mbar_wait(&full[s], ph, abort_flag);
+          ok = wait_all(&full[s], ph);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + s * S::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + S::A_BYTES;
+          // descriptors of the stage's first 16 elements of K; each further 16 lie 32 bytes on
+          // (two 16-byte units of the address field)
+          const uint64_t desc_a = smem_desc_sw128(a_addr), desc_b = smem_desc_sw128(a_addr + S::A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(acc_addr, smem_desc_sw128(a_addr + k * UMMA_K * 2), smem_desc_sw128(b_addr + k * UMMA_K * 2),
-                      idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(acc_addr, desc_a + 2 * k, desc_b + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
         umma_commit(&acc_full[buf]);  // the accumulator is complete once every MMA has retired

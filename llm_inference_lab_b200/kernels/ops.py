@@ -27,11 +27,11 @@ DEVICE_ERRORS = {1: "a page or slot index outside the pool", 2: "a bounded wait 
                  3: "a gathered row index outside the batch"}
 
 
-_fast: dict = {}    # (name, head size or None) -> library handle; read without the lock on the hot path
+_fast: dict = {}    # (name, values of the defines) -> library handle; read without the lock on the hot path
 
 
 def lib(name: str, defines: dict[str, int] | None = None) -> ctypes.CDLL:
-    fast_key = (name, defines["LAB_HEAD_DIM"] if defines else None)
+    fast_key = (name, tuple(defines.values()) if defines else None)
     handle = _fast.get(fast_key)
     if handle is not None:
         return handle
