@@ -352,6 +352,41 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
     return out
 
 
+def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
+             out_f32: bool = False, splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x @ w.T (+ bias) on pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 tokens by 256
+    accumulator columns, each CTA of a pair loading half of the weight tile.  For steps with many
+    tokens; `splits` > 1 returns 32-bit partial products [splits, tokens, out]."""
+    _on_gpu(x, w, bias, out)
+    T, K = x.shape
+    n_out = w.shape[0] // 2 if gated else w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc2 takes bfloat16 operands")
+    if not _tc_operands(x, w) or w.shape[1] != K:
+        raise KernelError(f"gemm_tc2: K={K} and the row stride must be multiples of 8 (16-byte rows for TMA)")
+    if splits > 1:
+        if gated or bias is not None:
+            raise KernelError("split-K takes no bias and no gate")
+        k_tiles = -(-K // 64)
+        per = -(-k_tiles // splits)
+        splits = -(-k_tiles // per)       # no empty split
+    if splits > 1:
+        out = torch.empty((splits, T, n_out), dtype=torch.float32, device=x.device) if out is None else out
+        ld_out, f32 = n_out, True
+    else:
+        odt = torch.float32 if out_f32 else torch.bfloat16
+        if out is None:
+            out = torch.empty((T, n_out), dtype=odt, device=x.device)
+        assert out.dtype == odt and out.stride(1) == 1
+        ld_out, f32 = out.stride(0), out_f32
+    _check(lib("gemm_tc2").lab_gemm_tc2(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
+                                        int(gated), int(f32), splits, _stream()), "gemm_tc2")
+    return out
+
+
+PAIR_GEMM_TOKENS = 4096     # from this many tokens on, products with K >= 2048 run on pairs of SMs
+
+
 def _pick_bm(T: int, n_out: int, gated: bool, swap: bool, bn: int) -> int:
     """Rows of the M-side tile.  Tiles of 64 rows (swapped orientation, bn <= 64) double the CTAs of
     a decode step's products, but measured slower at the benchmark's sizes (a step of 0.85 ms
@@ -403,6 +438,12 @@ def linear(x, w, bias=None, out_f32=False, allow_partial=False):
     if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w):
         return gemm_plain(x, w, bias, out_f32=out_f32)
     T = x.shape[0]
+    if T >= PAIR_GEMM_TOKENS and x.shape[1] >= 2048:
+        # long reductions over many tokens: pairs of SMs, each CTA loading half of the weight tile
+        # (measured at [T x 4864] x [4864 x 896]: 33 against 39 us at 4,096 tokens, 63 against 71 us
+        # at 8,192; at 2,048 tokens and for the other products of a layer the single-CTA kernel is
+        # as fast or faster)
+        return gemm_tc2(x, w, bias, out_f32=out_f32)
     if T > 128:
         bn, splits = _pick_prefill_tiles(T, w.shape[0], x.shape[1], allow_partial and bias is None and not out_f32)
         if splits > 1:

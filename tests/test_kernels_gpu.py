@@ -250,6 +250,34 @@ def test_gemm_tc_swapped_tile_rows(bm, T, N, K, gated, bias, bn, splits):
         assert torch.equal(out.double().cpu(), ref + (b.double() if bias else 0))
 
 
+@pytest.mark.parametrize("T,N,K,gated,bias,splits", [
+    (256, 256, 64, False, False, 1), (2048, 896, 896, False, True, 1), (300, 1000, 200, False, True, 1),
+    (2048, 4864, 896, True, False, 1), (515, 200, 104, True, False, 1), (2048, 896, 4864, False, False, 2),
+    (700, 130, 1000, False, False, 5), (3000, 1152, 72, False, True, 1), (1, 8, 8, False, False, 1),
+    (4500, 896, 4864, False, False, 1),
+])
+def test_gemm_tc2_exact(T, N, K, gated, bias, splits):
+    """The product on pairs of SMs (tcgen05.mma.cta_group::2) with exactly representable inputs: equal
+    to the 64-bit product; ragged token counts and feature counts, several tiles per pair, split K,
+    the gated epilogue (gate rows in one CTA of the pair, up rows in the other)."""
+    g = torch.Generator().manual_seed(26)
+    x = (torch.randint(-4, 5, (T, K), generator=g).float() / 4).bfloat16()
+    w = (torch.randint(-4, 5, (N * (2 if gated else 1), K), generator=g).float() / 8).bfloat16()
+    b = (torch.randint(-8, 9, (N,), generator=g).float() / 2).bfloat16() if bias else None
+    out = ops().gemm_tc2(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), gated=gated,
+                         out_f32=not gated, splits=splits)
+    ops().take_device_errors()
+    ref = x.double() @ w.double().T
+    if splits > 1:
+        assert torch.equal(out.double().sum(0).cpu(), ref)
+    elif gated:
+        gq, uq = ref[:, :N].bfloat16().double(), ref[:, N:].bfloat16().double()
+        want = torch.from_numpy(plain_silu(gq.numpy())).bfloat16().double() * uq
+        assert rel_err(out, want) < 1e-2
+    else:
+        assert torch.equal(out.double().cpu(), ref + (b.double() if bias else 0))
+
+
 def test_gemm_tc_guards():
     """Outputs beyond the valid rows and columns are not touched (NaN-prefilled buffer)."""
     g = torch.Generator().manual_seed(7)
