@@ -17,7 +17,8 @@
 // to T before PV, o = acc / sum.
 //
 // Warp 0 loads (TMA; the page that holds a request's last keys is copied by hand with rows
-// beyond the length set to zero, because a masked NaN would still poison P V), warp 1 issues
+// beyond the length set to zero, and the rows of V of pages that are not fetched at all are set to
+// zero, because a masked NaN would still poison P V), warp 1 issues
 // the MMAs (the whole warp walks the loop, one elected lane issues) and owns tensor memory, warps
 // 2-5 do the softmax.  Every wait is bounded.
 #include <cuda.h>
@@ -202,13 +203,17 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
   Barriers* bar = reinterpret_cast<Barriers*>(smem + OFF_BAR);
   volatile int* abort_flag = &bar->abort_flag;
   pdl_trigger();
-  pdl_wait();
+  // Until pdl_wait() below only the step's metadata is read (no kernel of the step writes it): the
+  // set-up of the CTA runs while the kernel before this one finishes.
   // Blocks are numbered with the head fastest and the tiles of the latest rows first: the CTAs
   // that walk the most keys all start in the first wave.
   const int b = blockIdx.z, h = blockIdx.x;
   const int qs = q_start[b], ql = q_start[b + 1] - qs;
   const int r0 = (gridDim.y - 1 - blockIdx.y) * BM;
-  if (ql < min_q_len || r0 >= ql) return;
+  if (ql < min_q_len || r0 >= ql) {
+    pdl_wait();  // this kernel ends only after the one before it: what follows may count on both
+    return;
+  }
   const int kvh = h / (n_q / n_kv);
   const int p0 = pos0_arr[b], kvl = kv_len_arr[b];
   const int* bt = block_table + (size_t)b * max_blocks;
@@ -241,15 +246,10 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (warp >= 2) {
-    // K and V stages start as zeros: rows no copy ever fills stay finite (they are always masked).
-    uint4* z = reinterpret_cast<uint4*>(smem + OFF_K);
-    for (int i = threadIdx.x - 64; i < 2 * KV_STAGES * KV_TILE / 16; i += 128) z[i] = make_uint4(0, 0, 0, 0);
-    proxy_fence();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
   const uint32_t tmem_base = bar->tmem_slot;
   const uint32_t smem_base = smem_u32(smem);
 
@@ -291,6 +291,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       }
       const uint32_t tma_lanes = __ballot_sync(0xffffffffu, kind == 1);
       const uint32_t tail_lanes = __ballot_sync(0xffffffffu, kind == 2);
+      uint32_t skip_lanes = __ballot_sync(0xffffffffu, kind == 0 && lane < pages_per_tile);
       if (lane == 0) alive = mbar_wait(&bar->kv_empty[s], ph ^ 1, abort_flag);
       alive = __shfl_sync(0xffffffffu, alive, 0);
       if (!alive) break;
@@ -324,8 +325,17 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
           *reinterpret_cast<uint4*>(smem + OFF_K + s * KV_TILE + off) = kk;
           *reinterpret_cast<uint4*>(smem + OFF_V + s * KV_TILE + off) = vv;
         }
-        proxy_fence();
       }
+      // Pages that are not fetched (beyond the length, before the window) leave stale rows in the
+      // stage.  Their keys are masked, but p = 0 times a stale NaN would still poison P V: their
+      // rows of V are set to zero.
+      while (skip_lanes) {
+        const int slot = __ffs(skip_lanes) - 1;
+        skip_lanes &= skip_lanes - 1;
+        uint4* vz = reinterpret_cast<uint4*>(smem + OFF_V + s * KV_TILE + slot * page_bytes);
+        for (int c = lane; c < page_bytes / 16; c += 32) vz[c] = make_uint4(0, 0, 0, 0);
+      }
+      proxy_fence();  // the hand-written rows become visible to the tensor cores
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->kv_full[s]);
     }
