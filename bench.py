@@ -209,7 +209,7 @@ def run_e2e(folder, batch, steps, warmup):
     seconds = timed[-1][0] - timed[0][0]
     meta_words = llm.graphs.cached[next(iter(llm.graphs.cached))].layout.total
     return {"value": batch * k / seconds, "unit": "tokens/s", "steps": k,
-            "h2d_bytes_per_step": 4 * (meta_words + 3 * batch), "d2h_bytes_per_step": 4 * batch}
+            "h2d_bytes_per_step": 4 * (meta_words + batch), "d2h_bytes_per_step": 4 * batch}
 
 
 def main() -> int:

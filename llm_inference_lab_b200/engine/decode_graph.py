@@ -29,11 +29,13 @@ from ..parts.base import GroupView, StepContext
 class _Captured:
     graph: torch.cuda.CUDAGraph
     layout: object
-    dev: torch.Tensor           # int32 metadata on the device
-    tokens: torch.Tensor        # [B] int32: input ids of the step, overwritten with the sampled ids
-    temps: torch.Tensor         # [B] float32
-    seeds: torch.Tensor         # [B] int32
+    buf: torch.Tensor           # one int32 device buffer: [temps B | seeds B | metadata | tokens B]
+    dev: torch.Tensor           # view: the int32 metadata
+    tokens: torch.Tensor        # view [B] int32: input ids of the step, overwritten with the sampled ids
+    temps: torch.Tensor         # view [B] float32
+    seeds: torch.Tensor         # view [B] int32
     rows: torch.Tensor          # [B] int32: 0..B-1, the rows whose logits are computed
+    host_tokens: torch.Tensor   # [B] int32 in pinned memory: the sampled ids, copied by the graph itself
     logits: Optional[torch.Tensor] = None   # [B, vocab] float32 of the last replay (lives in the graph's pool)
     launches: int = 0           # kernels the graph holds
 
@@ -46,6 +48,8 @@ class DecodeGraphs:
         self.cached: dict[tuple, _Captured] = {}
         self.replays = 0
         self.captures = 0
+        self._last = None
+        self._done = torch.cuda.Event()     # recorded after every replay
 
     # ------------------------------------------------------------------------------------
     def _key(self, n_requests: int, max_kv_len: int):
@@ -74,6 +78,7 @@ class DecodeGraphs:
         logits = self.engine.model.forward(ctx, self.engine.views, cap.rows)
         # position of the token being drawn = tokens held after this step
         ops.sample(logits, cap.temps, cap.seeds, ctx.kv_len, out=cap.tokens)
+        cap.host_tokens.copy_(cap.tokens, non_blocking=True)   # part of the graph: no launch of its own later
         return logits
 
     def _new_capture(self, key):
@@ -81,12 +86,14 @@ class DecodeGraphs:
         B, kv_bucket = key
         n_groups = len(eng.group_windows)
         layout = eng.cache.layout(B, B, [eng.max_blocks] * n_groups)
-        dev = torch.zeros((layout.total,), dtype=torch.int32, device=eng.device)
-        cap = _Captured(graph=torch.cuda.CUDAGraph(), layout=layout, dev=dev,
-                        tokens=torch.zeros((B,), dtype=torch.int32, device=eng.device),
-                        temps=torch.zeros((B,), dtype=torch.float32, device=eng.device),
-                        seeds=torch.zeros((B,), dtype=torch.int32, device=eng.device),
-                        rows=torch.arange(B, dtype=torch.int32, device=eng.device))
+        # Temperatures and seeds before the metadata, tokens after it: whatever a step brings from
+        # the host is one contiguous piece, and one copy.
+        buf = torch.zeros((3 * B + layout.total,), dtype=torch.int32, device=eng.device)
+        at = 2 * B
+        cap = _Captured(graph=torch.cuda.CUDAGraph(), layout=layout, buf=buf, dev=buf[at: at + layout.total],
+                        tokens=buf[at + layout.total: at + layout.total + B], temps=buf[0: B].view(torch.float32),
+                        seeds=buf[B: 2 * B], rows=torch.arange(B, dtype=torch.int32, device=eng.device),
+                        host_tokens=torch.zeros((B,), dtype=torch.int32, pin_memory=True))
         return cap, self._context(cap, B, kv_bucket)
 
     # ------------------------------------------------------------------------------------
@@ -122,20 +129,25 @@ class DecodeGraphs:
         else:
             cap = self.cached[key]
         st = eng._next_staging()
-        eng.cache.pack(pairs, cap.layout, st["np"], 0, 0)
         n_meta = cap.layout.total
-        cap.dev.copy_(st["host"][:n_meta], non_blocking=True)
+        host = st["np"]
+        eng.cache.pack(pairs, cap.layout, host[2 * B:], 0, 0)
+        lo, hi = 2 * B, 2 * B + n_meta
         if tokens is not None:
-            st["np"][n_meta: n_meta + B] = np.asarray(tokens, dtype=np.int32)
-            cap.tokens.copy_(st["host"][n_meta: n_meta + B], non_blocking=True)
+            host[hi: hi + B] = np.asarray(tokens, dtype=np.int32)
+            hi += B
+        elif self._last is not None and self._last is not cap and self._last.tokens.numel() == B:
+            # the previous step of this batch ran from another graph (its context outgrew a bucket):
+            # the ids it sampled move over on the device
+            cap.tokens.copy_(self._last.tokens, non_blocking=True)
         if temps is not None:
-            host_f = st["host"][n_meta + B: n_meta + 2 * B].view(torch.float32)
-            host_f.copy_(torch.tensor(list(temps), dtype=torch.float32))
-            cap.temps.copy_(host_f, non_blocking=True)
-            st["np"][n_meta + 2 * B: n_meta + 3 * B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
-            cap.seeds.copy_(st["host"][n_meta + 2 * B: n_meta + 3 * B], non_blocking=True)
+            host[0: B].view(np.float32)[:] = np.asarray(list(temps), dtype=np.float32)
+            host[B: 2 * B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
+            lo = 0
+        cap.buf[lo: hi].copy_(st["host"][lo: hi], non_blocking=True)
+        stream = torch.cuda.current_stream()
         ev = torch.cuda.Event()
-        ev.record()
+        ev.record(stream)
         st["event"] = ev
         if fresh:
             # One eager run configures the kernels and fills the allocator, then the capture.
@@ -154,6 +166,7 @@ class DecodeGraphs:
             self.cached[key] = cap
             self.captures += 1
         cap.graph.replay()
+        self._done.record(stream)
         ops.COUNTER.launches += cap.launches
         self.replays += 1
         if not reserved:
@@ -161,7 +174,14 @@ class DecodeGraphs:
                 eng.cache.commit(r, 1)
         eng.stats.steps += 1
         eng.stats.decode_tokens += B
+        self._last = cap
         return cap.tokens
+
+    def host_tokens(self) -> list[int]:
+        """The ids the last step sampled, on the host: waits for the step (its graph ends with the
+        copy into pinned memory)."""
+        self._done.synchronize()
+        return self._last.host_tokens.tolist()
 
     def last_logits(self, n_requests: int, max_kv_len: int) -> torch.Tensor:
         return self.cached[self._key(n_requests, max_kv_len)].logits

@@ -84,6 +84,7 @@ class LLM:
 
     def _run(self, by_id) -> None:
         sched = self.scheduler
+        last_decode_ids = None     # requests of the previous step, if it was a decode step from a graph
         while True:
             plan = sched.plan()
             self._collect(by_id)
@@ -92,18 +93,28 @@ class LLM:
                     return
                 raise RuntimeError("the scheduler has requests left but plans no step")
             rows = [e for e in plan if e.sample]
-            cfgs = [by_id[e.id]["cfg"] for e in rows]
-            temps = [c.effective_temperature() for c in cfgs]
-            seeds = [c.seed for c in cfgs]
             pure_decode = all(e.n == 1 and e.sample for e in plan)
             sampled = []
             try:
                 if self.graphs is not None and pure_decode:
                     # every request brings one token: replay the step from a CUDA graph
+                    ids = [e.id for e in plan]
                     tokens = [sched.portion(e.id, e.start, 1)[0] for e in plan]
-                    out = self.graphs.step([e.id for e in plan], tokens, temps, seeds, reserved=True)
-                    sampled = self.sampler.check(out.cpu().tolist(), self.engine.vocab)
+                    if ids == last_decode_ids:
+                        # the same requests as in the step before: their temperatures and seeds are on
+                        # the device already
+                        self.graphs.step(ids, tokens, None, None, reserved=True)
+                    else:
+                        cfgs = [by_id[i]["cfg"] for i in ids]
+                        self.graphs.step(ids, tokens, [c.effective_temperature() for c in cfgs],
+                                         [c.seed for c in cfgs], reserved=True)
+                    last_decode_ids = ids
+                    sampled = self.sampler.check(self.graphs.host_tokens(), self.engine.vocab)
                 else:
+                    last_decode_ids = None
+                    cfgs = [by_id[e.id]["cfg"] for e in rows]
+                    temps = [c.effective_temperature() for c in cfgs]
+                    seeds = [c.seed for c in cfgs]
                     entries = [Entry(e.id, sched.portion(e.id, e.start, e.n), [e.n - 1] if e.sample else [])
                                for e in plan]
                     logits = self.engine.step(entries, reserved=True)
