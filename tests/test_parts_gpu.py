@@ -1,6 +1,7 @@
 """Each part of a layer alone against the plain function of the same part, and the proof that
-the framework takes a new kind of part without a change to its files: a toy mixer with a
-state of its own, a toy architecture that uses it beside attention, both defined here."""
+the framework takes new kinds of parts without a change to its files: a toy mixer with a state
+of its own, a toy feed-forward with routing, a toy position encoding, and the toy architectures
+that use them beside the framework's parts, all defined here."""
 import dataclasses
 import math
 
@@ -254,3 +255,182 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         assert err < 1e-4, (k, err)
     engine.close(1), engine.close(2)
     assert engine.cache.free_state_slots == 3
+
+
+# ----------------------------------------------------------------------------------------
+# A toy feed-forward with routing and a toy position encoding, again defined here only.
+# ----------------------------------------------------------------------------------------
+
+def define_toy_routed():
+    from llm_inference_lab_b200 import register_architecture
+    from llm_inference_lab_b200.config.base import ModelConfig, optional, positive, required
+    from llm_inference_lab_b200.kernels import ops
+    from llm_inference_lab_b200.parts import (FeedForward, LayerCall, LayerSpec, ModelBlueprint, PartSpec,
+                                              PositionEncoding, TensorSpec, register_part)
+
+    class Top1Experts(FeedForward):
+        """Each token goes to the expert with the largest router logit (32-bit); the expert is a gated
+        MLP and its output is weighted with the softmax probability of that logit."""
+
+        @classmethod
+        def tensors(cls, spec):
+            h, i, p = spec["hidden"], spec["intermediate"], spec.prefix
+            out = [TensorSpec(p + "router.weight", (spec["experts"], h))]
+            for e in range(spec["experts"]):
+                out += [TensorSpec(p + f"experts.{e}.gate_up.weight", (2 * i, h)),
+                        TensorSpec(p + f"experts.{e}.down.weight", (h, i))]
+            return out
+
+        def __init__(self, spec, weights, dtype, device):
+            super().__init__(spec, weights, dtype, device)
+            self.router = self._weight(weights, "router.weight").contiguous()
+            self.experts = [(self._weight(weights, f"experts.{e}.gate_up.weight").contiguous(),
+                             self._weight(weights, f"experts.{e}.down.weight").contiguous())
+                            for e in range(spec["experts"])]
+
+        def forward(self, x, ctx):
+            logits = ops.linear(x, self.router, None, out_f32=True)
+            prob, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+            out = torch.zeros_like(x)
+            for e, (w_gate_up, w_down) in enumerate(self.experts):
+                rows = torch.nonzero(choice == e).flatten()
+                if rows.numel():
+                    y = ops.linear(ops.linear_gated(x[rows].contiguous(), w_gate_up), w_down)
+                    out[rows] = (y.float() * prob[rows, None]).to(x.dtype)
+            return out
+
+    class StridedRope(PositionEncoding):
+        """Rotary encoding whose angle grows `stride` times as fast: position p is encoded as
+        p * stride.  Built on the framework's rotation kernel, with positions of its own."""
+
+        def __init__(self, spec, weights, dtype, device):
+            super().__init__(spec, weights, dtype, device)
+            d = int(spec["rotary_dim"])
+            inv = np.power(float(spec["theta"]), -2.0 * np.arange(d // 2, dtype=np.float64) / d).astype(np.float32)
+            self.inv_freq, self.rotary_dim, self.stride = torch.from_numpy(inv).to(device), d, int(spec["stride"])
+            self.rotary = None      # no fused kernel may take this rotation over
+
+        def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim, bias=None, scratch=None):
+            write = cache is not None and cache.write
+            return ops.rope_kv_write(qkv, positions * self.stride, self.inv_freq, self.rotary_dim,
+                                     slots if write else None, cache.k if write else None,
+                                     cache.v if write else None, n_q, n_kv, head_dim, bias=bias)
+
+    register_part("feed_forward", "top1_experts", Top1Experts)
+    register_part("position", "strided_rope", StridedRope)
+
+    @dataclasses.dataclass
+    class ToyRoutedConfig(ModelConfig):
+        architecture = "ToyRoutedLM"
+        vocab_size: int = required(int, positive)
+        hidden_size: int = required(int, positive)
+        num_layers: int = required(int, positive)
+        inner_size: int = required(int, positive)
+        experts: int = optional(int, 3)
+        heads: int = optional(int, 2)
+        stride: int = optional(int, 3)
+        theta: float = optional(float, 100.0)
+        eps: float = optional(float, 1e-5)
+        max_positions: int = optional(int, 256)
+
+    def blueprint(cfg):
+        layers = []
+        d = cfg.hidden_size // cfg.heads
+        for i in range(cfg.num_layers):
+            p = f"blocks.{i}."
+            mixer = PartSpec("gqa_attention", {
+                "hidden": cfg.hidden_size, "n_heads": cfg.heads, "n_kv_heads": 1, "head_dim": d, "qkv_bias": False,
+                "out_bias": False, "window": 0,
+                "position": PartSpec("strided_rope", {"rotary_dim": d, "theta": cfg.theta, "stride": cfg.stride})},
+                prefix=p + "attn.")
+            if i % 2 == 0:
+                ffn = PartSpec("top1_experts", {"hidden": cfg.hidden_size, "intermediate": cfg.inner_size,
+                                                "experts": cfg.experts}, prefix=p + "moe.")
+            else:
+                ffn = PartSpec("gated_mlp", {"hidden": cfg.hidden_size, "intermediate": cfg.inner_size,
+                                             "act": "silu"}, prefix=p + "ff.")
+            norms = tuple(PartSpec("rmsnorm", {"hidden": cfg.hidden_size, "eps": cfg.eps}, prefix=p + f"n{j}.")
+                          for j in range(2))
+            layers.append(LayerSpec("prenorm", mixer, ffn, norms, hidden=cfg.hidden_size))
+        return ModelBlueprint(
+            hidden=cfg.hidden_size, vocab=cfg.vocab_size,
+            embedding=PartSpec("token_embedding", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size}, prefix="emb."),
+            layers=tuple(layers), order=tuple(LayerCall(i, i) for i in range(cfg.num_layers)),
+            final_norm=PartSpec("rmsnorm", {"hidden": cfg.hidden_size, "eps": cfg.eps}, prefix="out_norm."),
+            head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size, "tied_to": None},
+                          prefix="head."),
+            max_positions=cfg.max_positions)
+
+    register_architecture("ToyRoutedLM", ToyRoutedConfig, blueprint)
+    return ToyRoutedConfig
+
+
+def toy_routed_reference(folder, ids):
+    """The routed toy model on one whole sequence, in plain NumPy."""
+    import json
+    from plain_qwen2 import plain_attention, plain_rope, plain_silu
+    cfg = json.load(open(f"{folder}/config.json"))
+    _, w = read_model_folder(folder)
+    H, heads, T = cfg["hidden_size"], cfg["heads"], len(ids)
+    d = H // heads
+    x = w["emb.weight"][np.asarray(ids)].astype(np.float64)
+    pos = np.arange(T)
+    for i in range(cfg["num_layers"]):
+        p = f"blocks.{i}."
+        h = plain_rms_norm(x, w[p + "n0.weight"], cfg["eps"])
+        q = plain_rope(plain_linear(h, w[p + "attn.q_proj.weight"]).reshape(T, heads, d), pos * cfg["stride"], cfg["theta"])
+        k = plain_rope(plain_linear(h, w[p + "attn.k_proj.weight"]).reshape(T, 1, d), pos * cfg["stride"], cfg["theta"])
+        v = plain_linear(h, w[p + "attn.v_proj.weight"]).reshape(T, 1, d)
+        x = x + plain_linear(plain_attention(q, k, v, pos).reshape(T, H), w[p + "attn.o_proj.weight"])
+        h = plain_rms_norm(x, w[p + "n1.weight"], cfg["eps"])
+        if i % 2 == 0:
+            logits = plain_linear(h, w[p + "moe.router.weight"])
+            prob = np.exp(logits - logits.max(-1, keepdims=True))
+            prob /= prob.sum(-1, keepdims=True)
+            y = np.zeros_like(h)
+            for t in range(T):
+                e = int(np.argmax(logits[t]))
+                gu = plain_linear(h[t: t + 1], w[p + f"moe.experts.{e}.gate_up.weight"])
+                inner = gu.shape[1] // 2
+                y[t] = plain_linear(plain_silu(gu[:, :inner]) * gu[:, inner:], w[p + f"moe.experts.{e}.down.weight"])[0] \
+                    * prob[t, e]
+            x = x + y
+        else:
+            x = x + plain_gated_mlp(h, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"],
+                                    w[p + "ff.down_proj.weight"])
+    return plain_linear(plain_rms_norm(x, w["out_norm.weight"], cfg["eps"]), w["head.weight"])
+
+
+def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
+    """A feed-forward with routing and another position encoding register, build and step, whole and in
+    portions beside a decoding request, without a change to the framework's files."""
+    from llm_inference_lab_b200.engine import Engine, Entry
+    from llm_inference_lab_b200.weights import write_random_model
+
+    Config = define_toy_routed()
+    cfg = Config.from_dict(dict(vocab_size=61, hidden_size=32, num_layers=3, inner_size=40, experts=3, heads=2))
+    folder = write_random_model(cfg, str(tmp_path / "routed"), seed=5, dtype=torch.float32, std=0.2)
+    engine = Engine(folder, "float32", max_tokens=256, page_size=8, max_requests=3)
+    rng = np.random.default_rng(1)
+    seqs = {0: random_tokens(rng, 33, 61), 1: random_tokens(rng, 9, 61)}
+    want = {k: toy_routed_reference(folder, ids) for k, ids in seqs.items()}
+    whole = engine.step([Entry(7, seqs[0], list(range(33)))]).cpu().numpy()
+    engine.close(7)
+    assert np.abs(whole - want[0]).max() < 1e-4
+    got = {0: [], 1: []}
+    at0 = at1 = 0
+    for n0 in [4, 9, 2, 1, 8, 3, 6]:
+        entries = [Entry(0, seqs[0][at0: at0 + n0], list(range(n0)))]
+        if at1 < len(seqs[1]):
+            entries.append(Entry(1, seqs[1][at1: at1 + 1], [0]))
+        logits = engine.step(entries).cpu().numpy()
+        got[0].append(logits[:n0])
+        if len(entries) == 2:
+            got[1].append(logits[n0:])
+            at1 += 1
+        at0 += n0
+    assert at0 == 33
+    for k in (0, 1):
+        have = np.concatenate(got[k])
+        assert np.abs(have - want[k][: len(have)]).max() < 1e-4, k
+    engine.close(0), engine.close(1)
