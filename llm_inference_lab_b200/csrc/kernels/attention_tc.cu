@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
       cluster_sync();  // no CTA leaves while another still reads its shared memory
     }
   }
-  if constexpr (FUSED) {
+  if constexpr (FUSED && !CLUSTER) {
     if (splits > 1) {
       // The split that finishes last for this (request, kv head, tile of heads) merges them all.
       __shared__ int is_last;
@@ -790,15 +790,19 @@ LAB_EXPORT int lab_attention_decode_fused(void* out, int out_stride, const void*
                                           void* cache_k, void* cache_v, const int* q_start, const int* kv_len,
                                           const int* block_table, int max_blocks, int requests, int n_q, int n_kv,
                                           int page_size, int num_pages, int window, float scale, int splits,
-                                          float* scratch, int* counters, cudaStream_t stream) {
+                                          float* scratch, int* counters, int cluster_merge, cudaStream_t stream) {
   if (requests <= 0) return 0;
   if (n_q % n_kv || n_q / n_kv > 16 || splits < 1 || rotary_dim % 2 || rotary_dim > D) return (int)cudaErrorInvalidValue;
-  if (splits > 1 && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
+  const bool cluster = cluster_merge != 0 && splits >= 2 && splits <= DC_MAX_CLUSTER;
+  if (splits > 1 && !cluster && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
   if ((qkv == nullptr) == (partial == nullptr)) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          DC_SMEM_FUSED);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               DC_SMEM_FUSED);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -816,6 +820,26 @@ LAB_EXPORT int lab_attention_decode_fused(void* out, int out_stride, const void*
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
   dim3 grid(splits, n_kv, requests);
+  if (cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DC_THREADS);
+    cfg.dynamicSmemBytes = DC_SMEM_FUSED;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_lab_pdl ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel<true, true>, (__nv_bfloat16*)out, out_stride,
+                                   (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v,
+                                   q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
+                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr, fa);
+  }
   return (int)lab_launch(attention_decode_kernel<true>, grid, dim3(DC_THREADS), (size_t)DC_SMEM_FUSED, stream,
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)cache_k,
                          (__nv_bfloat16*)cache_v, q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size,

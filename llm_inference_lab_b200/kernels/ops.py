@@ -545,10 +545,10 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
 
 
 # The fused decode attention (rotation + cache write + attention + merge in one kernel) is built and
-# tested, but off by default: with programmatic dependent launch hiding launch latency, the separate
-# rope, attention and merge kernels measured faster at the benchmark's sizes (1.05 ms against
-# 1.15 ms per decode step at batch 8), because every split repeats the rotation of q before its
-# first tile and the merge waits on an atomic counter.
+# tested, but off by default: with programmatic dependent launch the separate rotation kernel runs
+# beside the attention kernel's reads of metadata and old keys, and fusing them puts the rotation
+# back in front of the first tile (measured with the merge inside the cluster: 0.875 ms against
+# 0.823 ms per decode step at batch 8, 1.24 against 1.17 ms at batch 64).
 FUSE_DECODE_ATTENTION = False
 _decode_counters: dict = {}
 
@@ -586,7 +586,8 @@ def attention_decode_fused(qkv, bias, inv_freq, rotary_dim, slots, cache_k, cach
         span = min(max_kv_len, window) if window else max_kv_len
         splits = decode_splits(n_requests, n_kv, n_q // n_kv, span)
     scratch = counters = None
-    if splits > 1:
+    in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and n_requests * n_kv * splits <= SM_COUNT
+    if splits > 1 and not in_cluster:
         scratch = torch.empty((n_requests * n_q * splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
         counters = _counters(qkv.device, n_requests * n_kv)
     L = lib("attention_tc", {"LAB_HEAD_DIM": head_dim})
@@ -599,8 +600,8 @@ def attention_decode_fused(qkv, bias, inv_freq, rotary_dim, slots, cache_k, cach
     _check(L.lab_attention_decode_fused(
         _ptr(out), out.stride(0), *args, _ptr(inv_freq), rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v),
         _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1], n_requests, n_q, n_kv, page_size,
-        num_pages, window, ctypes.c_float(scale), splits, _ptr(scratch), _ptr(counters), _stream()),
-        "attention_decode_fused")
+        num_pages, window, ctypes.c_float(scale), splits, _ptr(scratch), _ptr(counters), 1 if in_cluster else 0,
+        _stream()), "attention_decode_fused")
     return out
 
 

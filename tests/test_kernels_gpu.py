@@ -457,14 +457,17 @@ def test_attention_decode_cluster_merge(n_q, n_kv, d, window, splits):
         assert rel_err(a, w) < 2e-2
 
 
+@pytest.mark.parametrize("cluster", [True, False])
 @pytest.mark.parametrize("partial", [False, True])
 @pytest.mark.parametrize("n_q,n_kv,d,ps,window,rot,kvs,splits", [
     (14, 2, 64, 16, 0, 64, [640, 33, 1, 257], None), (6, 1, 32, 8, 0, 32, [100, 7], 3),
     (3, 3, 48, 8, 20, 48, [100, 19, 20, 21], None), (8, 2, 128, 32, 0, 64, [1000, 96], 4),
     (4, 2, 16, 4, 0, 0, [9, 30], 2)])
-def test_attention_decode_fused(partial, n_q, n_kv, d, ps, window, rot, kvs, splits):
-    """The fused decode kernel (partial sums + bias + rotation + cache write + attention + merge)
-    gives what the separate kernels give, and leaves the same cache behind."""
+def test_attention_decode_fused(cluster, partial, n_q, n_kv, d, ps, window, rot, kvs, splits, monkeypatch):
+    """The fused decode kernel (partial sums + bias + rotation + cache write + attention + merge, through
+    the cluster's shared memory or by the last CTA) gives what the separate kernels give, and leaves
+    the same cache behind."""
+    monkeypatch.setattr(ops(), "CLUSTER_MERGE", cluster)
     rng = np.random.default_rng(5)
     B = len(kvs)
     requests = [(kv, 1) for kv in kvs]
