@@ -144,7 +144,7 @@ class DecodeGraphs:
             host[0: B].view(np.float32)[:] = np.asarray(list(temps), dtype=np.float32)
             host[B: 2 * B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
             lo = 0
-        cap.buf[lo: hi].copy_(st["host"][lo: hi], non_blocking=True)
+        ops.copy_to_device(cap.buf, st["host"], lo, hi)
         stream = torch.cuda.current_stream()
         ev = torch.cuda.Event()
         ev.record(stream)

@@ -310,7 +310,7 @@ class Engine:
                 host[wi] = row + w
                 wi += 1
             row += n
-        dev.copy_(st["host"][:total], non_blocking=True)
+        ops.copy_to_device(dev, st["host"], 0, total)
         ev = torch.cuda.Event()
         ev.record()
         st["event"] = ev

@@ -71,6 +71,14 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def copy_to_device(dst: torch.Tensor, pinned_src: torch.Tensor, words_from: int, words_to: int) -> None:
+    """dst[words_from:words_to] = pinned_src[words_from:words_to] (both int32, same layout) on the current
+    stream, without the host-side cost of a tensor copy."""
+    _check(lib("rowwise").lab_copy_to_device(
+        ctypes.c_void_p(dst.data_ptr() + 4 * words_from), ctypes.c_void_p(pinned_src.data_ptr() + 4 * words_from),
+        ctypes.c_longlong(4 * (words_to - words_from)), _stream()), "copy_to_device", 0)
+
+
 def _ptr(t) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
