@@ -145,9 +145,10 @@ def runtime_module_path() -> str:
 
     folder = os.path.join(CSRC, "runtime")
     srcs = sorted(os.path.join(folder, f) for f in os.listdir(folder) if f.endswith(".cpp"))
-    flags = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
-             f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{folder}"]
-    digest = _digest(srcs + _headers(folder), flags + [sys.version])
+    options = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
+    flags = options + [f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{folder}"]
+    # the name depends on the sources, the options and the interpreter, not on where the checkout lies
+    digest = _digest(srcs + _headers(folder), options + [sys.version, pybind11.__version__])
     out = os.path.join(build_dir(), f"_lab_runtime-{digest}.so")
     if not os.path.exists(out):
         cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
