@@ -494,7 +494,7 @@ def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int) -> int:
     256 keys per CTA, as far as the GPU has room for the CTAs (the reference splits 1..16 ways,
     rust/engine/src/runner/model/qwen2/engine.rs:1597-1617)."""
     ctas = max(1, n_decode * n_kv * (-(-group // 16)))
-    if CLUSTER_MERGE:
+    if CLUSTER_MERGE and max_kv_len <= 8 * 256:       # beyond that, more than 8 splits serve better
         fine = min(8, -(-max_kv_len // 128), SM_COUNT // ctas)
         if fine >= 2:
             return int(fine)
