@@ -131,6 +131,7 @@ PYBIND11_MODULE(_lab_runtime, m) {
       .def_property_readonly("num_active", &Scheduler::num_active)
       .def_property_readonly("preemptions", &Scheduler::preemptions)
       .def("plan", &Scheduler::plan)
+      .def("plan_ahead", &Scheduler::plan_ahead)
       .def("portion", &Scheduler::portion)
       .def("complete", &Scheduler::complete)
       .def("abandon", &Scheduler::abandon)

@@ -12,6 +12,11 @@
 //     reaches the end of the prompt produces a token;
 //   * a request ends when its budget of new tokens is used up or it produced an
 //     end-of-sequence token (which is counted and returned).
+// Lookahead (this engine's addition): while a pure decode step runs on the device, the next
+// one may be planned and launched before the first one's tokens have reached the host
+// (`plan_ahead`): the device feeds the sampled ids forward itself.  A request that turns out
+// to have ended with the earlier step still takes part in the later one; that token is
+// dropped, and its cache is given back when the later step is completed.
 // What happens when pages run out is decided by `reserve_future`:
 //   * true (the reference's way): a request is admitted only if the pages for its whole
 //     life (prompt + new tokens - 1) are free beyond what running requests will still
@@ -52,6 +57,12 @@ struct SchedRequest {
   bool decoding = false;
   int preemptions = 0;
   long arrival = 0;
+  // lookahead: tokens sampled on the device that the host has not seen yet (0 or 1), steps whose
+  // cache entries were committed at launch, and the end that an earlier step brought while a
+  // later one was already running
+  int unseen = 0;
+  int committed_early = 0;
+  FinishReason ended = FinishReason::kNone;
 };
 
 struct PlanEntry {
@@ -131,6 +142,45 @@ class Scheduler {
     }
   }
 
+  // Plans the step after `in_flight`, a pure decode step that has been launched and not yet
+  // completed, on the assumption that none of its requests ends with it; reserves its pages.
+  // Its input tokens are the ones `in_flight` samples (they stay on the device).  Returns an
+  // empty plan, and changes nothing, when looking ahead is not possible: requests are waiting,
+  // `in_flight` is not a decode step of all running requests, one of them reaches its number of
+  // new tokens with it, or the pages for one more token each are not there.
+  std::vector<PlanEntry> plan_ahead(const std::vector<PlanEntry>& in_flight) {
+    if (!waiting_.empty() || in_flight.empty() || in_flight.size() != active_.size()) return {};
+    if ((int)in_flight.size() > cfg_.max_batch_tokens) return {};
+    for (size_t i = 0; i < in_flight.size(); ++i) {
+      const PlanEntry& e = in_flight[i];
+      const SchedRequest& r = active_[i];
+      if (r.id != e.id || e.n != 1 || !e.sample || !r.decoding || r.unseen != 0 || r.committed_early != 0) return {};
+      if (r.ended != FinishReason::kNone || r.generated + 1 >= r.max_new) return {};
+      if (cfg_.max_seq_len > 0 && e.start + 2 > cfg_.max_seq_len) return {};
+    }
+    // The step is on its way: its cache entries will be written, so they count from now on.
+    for (size_t i = 0; i < in_flight.size(); ++i) cache_->commit(in_flight[i].id, 1);
+    std::vector<StepEntry> want;
+    for (const auto& e : in_flight) want.push_back({e.id, 1});
+    if (!cache_->can_reserve(want)) {
+      for (auto& r : active_) {  // remembered, so that complete() does not commit them again
+        r.computed += 1;
+        r.committed_early = 1;
+      }
+      return {};
+    }
+    std::vector<PlanEntry> next;
+    for (size_t i = 0; i < in_flight.size(); ++i) {
+      SchedRequest& r = active_[i];
+      r.computed += 1;
+      r.committed_early = 1;
+      r.unseen = 1;
+      cache_->reserve(r.id, 1);
+      next.push_back({r.id, r.computed, 1, true});
+    }
+    return next;
+  }
+
   // Tokens of one planned portion.
   std::vector<int> portion(int64_t id, int start, int n) const {
     const SchedRequest& r = find_active(id);
@@ -144,25 +194,38 @@ class Scheduler {
     size_t next = 0;
     for (const auto& e : entries) {
       SchedRequest& r = find_active_mut(e.id);
-      cache_->commit(e.id, e.n);
-      r.computed += e.n;
+      if (r.committed_early > 0) {
+        r.committed_early -= 1;  // plan_ahead counted this step's cache entries at its launch
+      } else {
+        cache_->commit(e.id, e.n);
+        r.computed += e.n;
+      }
       if (!e.sample) continue;
       if (next >= sampled.size()) throw StateError("fewer sampled tokens than sampling entries");
       const int tok = sampled[next++];
+      if (r.ended != FinishReason::kNone) continue;  // it ended a step ago: this token is dropped
       r.tokens.push_back(tok);
       r.generated += 1;
       r.decoding = true;
     }
     if (next != sampled.size()) throw StateError("more sampled tokens than sampling entries");
-    // Finished requests leave before any peer's next step (model_runner.rs:711-722).
+    // Finished requests leave before any peer's next step (model_runner.rs:711-722), unless a
+    // later step that is already running holds them: then they leave when that step completes.
     for (auto it = active_.begin(); it != active_.end();) {
-      FinishReason why = FinishReason::kNone;
-      if (it->generated > 0 && !it->ignore_eos &&
-          std::find(it->eos.begin(), it->eos.end(), it->tokens.back()) != it->eos.end())
-        why = FinishReason::kEos;
-      else if (it->generated >= it->max_new)
-        why = FinishReason::kLength;
-      if (why != FinishReason::kNone) {
+      FinishReason why = it->ended;
+      if (why == FinishReason::kNone) {
+        if (it->generated > 0 && !it->ignore_eos &&
+            std::find(it->eos.begin(), it->eos.end(), it->tokens.back()) != it->eos.end())
+          why = FinishReason::kEos;
+        else if (it->generated >= it->max_new)
+          why = FinishReason::kLength;
+      }
+      const bool held = it->unseen > 0 && it->ended == FinishReason::kNone;  // a later step runs with it
+      if (it->unseen > 0) it->unseen -= 1;  // the token the later step took from the device has arrived
+      if (why != FinishReason::kNone && held) {
+        it->ended = why;  // leaves with the later step's completion
+        ++it;
+      } else if (why != FinishReason::kNone) {
         cache_->close(it->id);
         finish(*it, why, "");
         it = active_.erase(it);

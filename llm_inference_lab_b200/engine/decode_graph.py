@@ -42,6 +42,7 @@ class _Captured:
 
 class DecodeGraphs:
     MAX_CACHED = 16
+    MAX_KEPT_BATCH = 1024
 
     def __init__(self, engine):
         self.engine = engine
@@ -49,14 +50,13 @@ class DecodeGraphs:
         self.replays = 0
         self.captures = 0
         self._last = None
+        self._pairs_of = None
+        self._ring, self._ring_at = [], 0     # pinned buffers for the ids of steps launched with `keep`
         self._done = torch.cuda.Event()     # recorded after every replay
 
     # ------------------------------------------------------------------------------------
     def _key(self, n_requests: int, max_kv_len: int):
-        bucket = 256
-        while bucket < max_kv_len:
-            bucket *= 2
-        return (n_requests, bucket)
+        return (n_requests, max(256, 1 << (int(max_kv_len) - 1).bit_length()))
 
     def _context(self, cap: _Captured, B: int, kv_bucket: int) -> StepContext:
         eng, L, dev = self.engine, cap.layout, cap.dev
@@ -99,14 +99,20 @@ class DecodeGraphs:
     # ------------------------------------------------------------------------------------
     def step(self, requests: Sequence[int], tokens: Optional[Sequence[int]] = None,
              temps: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
-             reserved: bool = False) -> torch.Tensor:
+             reserved: bool = False, keep: bool = False):
         """One decode step for `requests` (each brings one token).  `tokens` are the input ids
         on the host; None means: the ids the previous step of the same batch sampled, which
         are still on the device.  Returns the device buffer [B] of sampled ids (valid until
-        the next step of this batch size)."""
+        the next step of this batch size); with `keep`, a ticket for `read` instead: the ids are
+        also copied into a pinned buffer of their own, so that they can be read after later steps
+        have been launched."""
         eng = self.engine
         B = len(requests)
-        pairs = [(int(r), 1) for r in requests]
+        if self._pairs_of is not None and self._pairs_of[0] == requests:
+            pairs = self._pairs_of[1]           # the same batch as last time
+        else:
+            pairs = [(int(r), 1) for r in requests]
+            self._pairs_of = (list(requests), pairs)
         if not reserved:
             done = []
             try:
@@ -145,19 +151,21 @@ class DecodeGraphs:
             host[B: 2 * B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
             lo = 0
         ops.copy_to_device(cap.buf, st["host"], lo, hi)
-        stream = torch.cuda.current_stream()
-        ev = torch.cuda.Event()
+        stream = ops.current_stream()
+        ev = st.get("own_event")
+        if ev is None:
+            ev = st["own_event"] = torch.cuda.Event()
         ev.record(stream)
         st["event"] = ev
         if fresh:
             # One eager run configures the kernels and fills the allocator, then the capture.
-            keep = cap.tokens.clone()
+            saved = cap.tokens.clone()
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 self._run(cap, ctx)
             torch.cuda.current_stream().wait_stream(side)
-            cap.tokens.copy_(keep)
+            cap.tokens.copy_(saved)
             before = ops.COUNTER.launches
             with torch.cuda.graph(cap.graph):
                 cap.logits = self._run(cap, ctx)
@@ -175,7 +183,25 @@ class DecodeGraphs:
         eng.stats.steps += 1
         eng.stats.decode_tokens += B
         self._last = cap
+        if keep:
+            if not self._ring:
+                self._ring = [(torch.zeros((self.MAX_KEPT_BATCH,), dtype=torch.int32, pin_memory=True),
+                               torch.cuda.Event()) for _ in range(4)]
+            if B > self.MAX_KEPT_BATCH:
+                raise ValueError("batch too large for the kept-token buffers")
+            buf, event = self._ring[self._ring_at]
+            self._ring_at = (self._ring_at + 1) % len(self._ring)
+            buf[:B].copy_(cap.tokens, non_blocking=True)
+            event.record(stream)
+            return (buf, event, B)
         return cap.tokens
+
+    @staticmethod
+    def read(ticket) -> list[int]:
+        """The ids a step launched with `keep` sampled: waits for that step only."""
+        buf, event, B = ticket
+        event.synchronize()
+        return buf[:B].tolist()
 
     def host_tokens(self) -> list[int]:
         """The ids the last step sampled, on the host: waits for the step (its graph ends with the

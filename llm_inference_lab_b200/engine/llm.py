@@ -33,7 +33,7 @@ class LLM:
     def __init__(self, model_dir: str, dtype: str = "bf16", *, max_batch_tokens: int = 512,
                  kv_tokens: Optional[int] = None, page_size: int = 16, max_requests: int = 64,
                  max_seq_len: Optional[int] = None, reserve_future: bool = True, cuda_graph: bool = False,
-                 device: str = "cuda:0"):
+                 lookahead: bool = True, device: str = "cuda:0"):
         self.engine = Engine(model_dir, dtype, max_tokens=kv_tokens, page_size=page_size, max_requests=max_requests,
                              max_batch_tokens=max_batch_tokens, max_seq_len=max_seq_len, device=device)
         rt = cache_mod.runtime()
@@ -43,6 +43,10 @@ class LLM:
         self.model_eos = list(self.engine.model.blueprint.eos_token_ids)
         self.cuda_graph = bool(cuda_graph)
         self.graphs = DecodeGraphs(self.engine) if self.cuda_graph else None
+        # With graphs: while a decode step runs, the next one is planned and launched before the first
+        # one's tokens have reached the host (the device feeds the sampled ids forward), so the host's
+        # work between steps no longer idles the GPU.
+        self.lookahead = bool(lookahead) and self.cuda_graph
         if self.cuda_graph:
             self.engine.enable_step_graphs()      # prompt portions of a repeating shape as well
         self.step_log: list[tuple[float, int, bool]] = []   # (time the step's tokens reached the host, tokens, decode?)
@@ -92,46 +96,70 @@ class LLM:
                 if sched.idle:
                     return
                 raise RuntimeError("the scheduler has requests left but plans no step")
-            rows = [e for e in plan if e.sample]
             pure_decode = all(e.n == 1 and e.sample for e in plan)
+            if self.graphs is not None and pure_decode:
+                last_decode_ids = self._decode_run(by_id, plan, last_decode_ids)
+                continue
+            last_decode_ids = None
+            rows = [e for e in plan if e.sample]
             sampled = []
             try:
-                if self.graphs is not None and pure_decode:
-                    # every request brings one token: replay the step from a CUDA graph
-                    ids = [e.id for e in plan]
-                    tokens = [sched.portion(e.id, e.start, 1)[0] for e in plan]
-                    if ids == last_decode_ids:
-                        # the same requests as in the step before: their temperatures and seeds are on
-                        # the device already
-                        self.graphs.step(ids, tokens, None, None, reserved=True)
-                    else:
-                        cfgs = [by_id[i]["cfg"] for i in ids]
-                        self.graphs.step(ids, tokens, [c.effective_temperature() for c in cfgs],
-                                         [c.seed for c in cfgs], reserved=True)
-                    last_decode_ids = ids
-                    sampled = self.sampler.check(self.graphs.host_tokens(), self.engine.vocab)
-                else:
-                    last_decode_ids = None
-                    cfgs = [by_id[e.id]["cfg"] for e in rows]
-                    temps = [c.effective_temperature() for c in cfgs]
-                    seeds = [c.seed for c in cfgs]
-                    entries = [Entry(e.id, sched.portion(e.id, e.start, e.n), [e.n - 1] if e.sample else [])
-                               for e in plan]
-                    logits = self.engine.step(entries, reserved=True)
-                    if logits is not None:
-                        sampled = self.sampler.pick(logits, temps, seeds, [e.start + e.n for e in rows])
+                cfgs = [by_id[e.id]["cfg"] for e in rows]
+                temps = [c.effective_temperature() for c in cfgs]
+                seeds = [c.seed for c in cfgs]
+                entries = [Entry(e.id, sched.portion(e.id, e.start, e.n), [e.n - 1] if e.sample else [])
+                           for e in plan]
+                logits = self.engine.step(entries, reserved=True)
+                if logits is not None:
+                    sampled = self.sampler.pick(logits, temps, seeds, [e.start + e.n for e in rows])
             except Exception:
                 sched.abandon(plan)
                 raise
-            now = time.perf_counter()
-            self.step_log.append((now, sum(e.n for e in plan), pure_decode))
-            for e in rows:
-                if by_id[e.id]["ttft"] is None:
-                    by_id[e.id]["ttft"] = now - by_id[e.id]["t0"]
-            sched.complete(plan, sampled)
-            self.steps += 1
-            if self.trace is not None:
-                self.trace({"event": "step_completed", "step": self.steps, "requests": len(plan),
-                            "tokens": sum(e.n for e in plan), "sampled": len(sampled),
-                            "free_pages": self.engine.free_pages()})
-            self._collect(by_id)
+            self._step_done(by_id, plan, sampled, False)
+
+    def _decode_run(self, by_id, plan, last_decode_ids):
+        """Decode steps from CUDA graphs, every request one token a step, for as long as the
+        scheduler can look ahead: step n + 1 is planned and launched before the tokens of step n are
+        read.  Returns the requests of the last step launched."""
+        sched, graphs = self.scheduler, self.graphs
+        ids = [e.id for e in plan]
+        try:
+            tokens = [sched.portion(e.id, e.start, 1)[0] for e in plan]
+            if ids == last_decode_ids:
+                # the same requests as in the step before: temperatures and seeds are on the device
+                ticket = graphs.step(ids, tokens, None, None, reserved=True, keep=True)
+            else:
+                cfgs = [by_id[i]["cfg"] for i in ids]
+                ticket = graphs.step(ids, tokens, [c.effective_temperature() for c in cfgs],
+                                     [c.seed for c in cfgs], reserved=True, keep=True)
+        except Exception:
+            sched.abandon(plan)
+            raise
+        while True:
+            ahead = sched.plan_ahead(plan) if self.lookahead else []
+            next_ticket = None
+            try:
+                if ahead:
+                    next_ticket = graphs.step(ids, None, None, None, reserved=True, keep=True)
+                sampled = self.sampler.check(graphs.read(ticket), self.engine.vocab)
+            except Exception:
+                sched.abandon(ahead if ahead else plan)
+                raise
+            self._step_done(by_id, plan, sampled, True)
+            if not ahead:
+                return ids
+            plan, ticket = ahead, next_ticket
+
+    def _step_done(self, by_id, plan, sampled, pure_decode) -> None:
+        now = time.perf_counter()
+        self.step_log.append((now, sum(e.n for e in plan), pure_decode))
+        for e in plan:
+            if e.sample and by_id[e.id]["ttft"] is None:
+                by_id[e.id]["ttft"] = now - by_id[e.id]["t0"]
+        self.scheduler.complete(plan, sampled)
+        self.steps += 1
+        if self.trace is not None:
+            self.trace({"event": "step_completed", "step": self.steps, "requests": len(plan),
+                        "tokens": sum(e.n for e in plan), "sampled": len(sampled),
+                        "free_pages": self.engine.free_pages()})
+        self._collect(by_id)

@@ -79,6 +79,22 @@ def copy_to_device(dst: torch.Tensor, pinned_src: torch.Tensor, words_from: int,
         ctypes.c_longlong(4 * (words_to - words_from)), _stream()), "copy_to_device", 0)
 
 
+_stream_objects: dict = {}
+
+
+def current_stream() -> "torch.cuda.Stream":
+    """torch's object for the current stream, found through its raw handle (the library's own
+    lookup costs several microseconds a call)."""
+    if _raw_stream is None:
+        return torch.cuda.current_stream()
+    device = torch.cuda.current_device()
+    key = (device, _raw_stream(device))
+    obj = _stream_objects.get(key)
+    if obj is None:
+        obj = _stream_objects[key] = torch.cuda.current_stream()
+    return obj
+
+
 def _ptr(t) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 

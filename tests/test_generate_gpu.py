@@ -151,3 +151,34 @@ def test_command_line(tmp_path_factory):
     assert line["dtype"] == "f32" and line["generated_tokens"] == len(expect)
     steps = [json.loads(s) for s in proc.stderr.splitlines() if s.startswith('{"event"')]
     assert len(steps) >= len(expect)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lookahead_decoding_gives_the_same_tokens(tmp_path_factory, dtype):
+    """Decode steps launched ahead of the host (the device feeds the sampled ids forward) give what
+    step-by-step decoding gives: greedy and with temperature, requests of different lengths that end
+    by length and by their end-of-sequence token at different steps, more requests than slots."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY["B"]
+    folder = folder_of(tmp_path_factory, "B", dtype)
+    rng = np.random.default_rng(11)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (3, 17, 8, 30, 1, 12)]
+    short = "f32" if dtype == "float32" else "bf16"
+    outs = {}
+    for ahead in (False, True):
+        llm = LLM(folder, short, page_size=opt["page_size"], kv_tokens=512, max_requests=4, cuda_graph=True,
+                  lookahead=ahead)
+        free = llm.generate(prompts, SamplingConfig(max_new_tokens=24, ignore_eos=True))
+        # end tokens taken from the free run: every request stops somewhere in the middle
+        configs = [SamplingConfig(max_new_tokens=5 + 4 * i, eos_token_id=free[i].tokens[3 + i], temperature=0.7,
+                                  do_sample=(i % 2 == 1), seed=5 + i) for i in range(len(prompts))]
+        stopped = llm.generate(prompts, configs)
+        outs[ahead] = ([r.tokens for r in free], [(r.tokens, r.finish_reason) for r in stopped])
+        assert llm.engine.cache.live_requests == 0 and llm.engine.free_pages()[0] == llm.engine.num_pages
+        llm.engine.cache.check_consistency()
+        if ahead:
+            assert llm.graphs.replays > 20
+    assert outs[True] == outs[False]
+    assert any(reason == "eos" for _, reason in outs[True][1]) and any(reason == "length" for _, reason in outs[True][1])

@@ -201,3 +201,128 @@ def test_windowed_group_is_budgeted_by_its_peak():
     _, done = run(sched)
     assert done[1].reason.name == "length" and len(done[1].generated) == 20
     assert cache.free_pages(0) == 6
+
+
+# ----------------------------------------------------------------------------------------
+# Lookahead: the next decode step is planned while the last one's tokens are still unknown.
+# ----------------------------------------------------------------------------------------
+
+def run_ahead(sched, next_token, max_steps=10_000):
+    """As `run`, but decode steps are planned ahead whenever the scheduler allows it: the tokens of
+    step n reach `complete` only after step n + 1 has been planned (as they do when the device feeds
+    them forward).  Returns (plans, {id: Finished}, number of steps planned ahead)."""
+    plans, done, ahead_count = [], {}, 0
+
+    def collect():
+        for f in sched.take_finished():
+            done[f.id] = f
+
+    for _ in range(max_steps):
+        plan = sched.plan()
+        collect()
+        if not plan:
+            assert sched.idle
+            break
+        while True:
+            plans.append([(e.id, e.start, e.n, e.sample) for e in plan])
+            pure = all(e.n == 1 and e.sample for e in plan)
+            ahead = sched.plan_ahead(plan) if pure else []
+            sampled = [next_token(e.id, e.start + e.n) for e in plan if e.sample]
+            sched.complete(plan, sampled)
+            collect()
+            if not ahead:
+                break
+            ahead_count += 1
+            plan = ahead
+    return plans, done, ahead_count
+
+
+def test_lookahead_gives_the_same_tokens_and_frees_everything():
+    import random
+
+    rng = random.Random(4)
+    looked_ahead = 0
+    for trial in range(40):
+        n_req = rng.randint(1, 6)
+        reqs = [(i + 1, [rng.randint(0, 50) for _ in range(rng.randint(1, 30))], rng.randint(1, 25))
+                for i in range(n_req)]
+        stop_at = {rid: rng.randint(2, 40) for rid, _, _ in reqs}       # position at which each samples its EOS
+
+        def token(rid, pos):
+            return 999 if pos >= stop_at[rid] + len(reqs[rid - 1][1]) else 100 + (rid * 7 + pos) % 50
+
+        results = []
+        for mode in ("plain", "ahead"):
+            cache, sched = make(pages=200, page_size=4, budget=16)
+            for rid, prompt, max_new in reqs:
+                sched.add(rid, prompt, max_new, [999], False)
+            if mode == "plain":
+                _, done = run(sched, token)
+                used = 0
+            else:
+                _, done, used = run_ahead(sched, token)
+            assert cache.free_pages(0) == 200 and cache.live_requests == 0
+            cache.check_consistency()
+            results.append(({rid: (f.generated, f.reason.name) for rid, f in done.items()}, used))
+        assert results[0][0] == results[1][0], f"trial {trial}"
+        looked_ahead += results[1][1]
+    assert looked_ahead > 100, "most decode steps were planned ahead"
+
+
+def test_lookahead_plans_the_next_position_and_stops_before_the_last_token():
+    cache, sched = make(budget=8)
+    sched.add(1, [1, 2, 3], 4)
+    sched.add(2, [4, 5], 6)
+    plan = sched.plan()                                   # both prompts
+    assert sched.plan_ahead(plan) == [], "a step with prompt portions is not looked ahead from"
+    sched.complete(plan, [10, 20])
+    plan = sched.plan()                                   # first decode step: positions 3 and 2
+    assert [(e.id, e.start) for e in plan] == [(1, 3), (2, 2)]
+    ahead = sched.plan_ahead(plan)
+    assert [(e.id, e.start, e.n, e.sample) for e in ahead] == [(1, 4, 1, True), (2, 3, 1, True)]
+    sched.complete(plan, [11, 21])
+    # request 1 has 2 of its 4 tokens; the step in flight gives the third, the one after it the last
+    ahead2 = sched.plan_ahead(ahead)
+    assert [(e.id, e.start) for e in ahead2] == [(1, 5), (2, 4)]
+    sched.complete(ahead, [12, 22])
+    assert sched.plan_ahead(ahead2) == [], "request 1 ends by length with the step in flight"
+    sched.complete(ahead2, [13, 23])
+    done = {f.id: f for f in sched.take_finished()}
+    assert done[1].generated == [10, 11, 12, 13] and done[1].reason.name == "length"
+    assert sched.num_active == 1
+
+
+def test_a_request_that_ends_while_the_next_step_runs_leaves_with_that_step():
+    cache, sched = make(budget=8)
+    sched.add(1, [1, 2, 3], 10, [99], False)
+    sched.add(2, [4, 5], 10, [99], False)
+    sched.complete(sched.plan(), [10, 20])
+    plan = sched.plan()
+    ahead = sched.plan_ahead(plan)
+    assert ahead
+    held = cache.free_pages(0)
+    sched.complete(plan, [99, 21])                         # request 1 samples its end-of-sequence token
+    assert sched.num_active == 2 and cache.free_pages(0) == held, "it stays until the step in flight is done"
+    assert sched.take_finished() == []
+    assert sched.plan_ahead(ahead) == [], "no further lookahead while a request is on its way out"
+    sched.complete(ahead, [55, 22])                        # its token of this step is dropped
+    done = {f.id: f for f in sched.take_finished()}
+    assert done[1].generated == [10, 99] and done[1].reason.name == "eos"
+    assert sched.num_active == 1 and cache.free_pages(0) > held
+    plan = sched.plan()
+    assert [(e.id, e.start) for e in plan] == [(2, 4)]
+    assert sched.portion(2, 4, 1) == [22]
+
+
+def test_lookahead_waits_when_requests_are_waiting_or_pages_are_short():
+    cache, sched = make(pages=3, page_size=4, budget=8, reserve_future=False)      # 12 tokens of cache
+    sched.add(1, list(range(7)), 8)
+    sched.complete(sched.plan(), [50])
+    plan = sched.plan()                                   # position 7: the second page is full after it
+    ahead = sched.plan_ahead(plan)
+    assert [(e.id, e.start) for e in ahead] == [(1, 8)], "the third page is there"
+    sched.complete(plan, [51])
+    sched.add(2, [1, 2], 2)                               # someone waits: admission comes first
+    assert sched.plan_ahead(ahead) == []
+    sched.complete(ahead, [52])
+    cache.check_consistency()
