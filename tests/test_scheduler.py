@@ -326,3 +326,17 @@ def test_lookahead_waits_when_requests_are_waiting_or_pages_are_short():
     assert sched.plan_ahead(ahead) == []
     sched.complete(ahead, [52])
     cache.check_consistency()
+
+
+def test_lookahead_without_a_free_page_falls_back_to_the_plain_plan():
+    cache, sched = make(pages=2, page_size=4, budget=8, reserve_future=False)      # 8 tokens of cache
+    sched.add(1, list(range(7)), 8)
+    sched.complete(sched.plan(), [50])
+    plan = sched.plan()                                   # position 7 fills the second page
+    assert sched.plan_ahead(plan) == [], "no page for position 8"
+    sched.complete(plan, [51])                            # the step in flight still completes as ever
+    cache.check_consistency()
+    assert sched.plan() == [], "alone and out of pages: the request ends"
+    done = {f.id: f for f in sched.take_finished()}
+    assert done[1].reason.name == "capacity" and done[1].generated == [50, 51]
+    assert cache.free_pages(0) == 2 and cache.live_requests == 0
