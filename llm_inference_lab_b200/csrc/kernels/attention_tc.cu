@@ -444,18 +444,16 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
       }
       return __bfloat162float(fa.qkv[(size_t)qs * fa.qkv_stride + col]);
     };
-    auto rnd = [](float v) { return __bfloat162float(__float2bfloat16_rn(v)); };
     const float pos = (float)(kvl - 1);
     const int half = fa.rotary_dim / 2;
-    // rotate: out = [lo*c - hi*s, hi*c + lo*s] with cos/sin rounded to bf16 and bf16 products
+    // rotate: out = [lo*c - hi*s, hi*c + lo*s] in 32-bit, rounded once
     auto rotate_into = [&](__nv_bfloat16* dst, int col0, int i) {
       if (i < half) {
         float sn, cs;
         sincosf(pos * fa.inv_freq[i], &sn, &cs);
-        const float c = rnd(cs), sv = rnd(sn);
         const float vlo = value(col0 + i), vhi = value(col0 + i + half);
-        dst[i] = __float2bfloat16_rn(rnd(vlo * c) - rnd(vhi * sv));
-        dst[i + half] = __float2bfloat16_rn(rnd(vhi * c) + rnd(vlo * sv));
+        dst[i] = __float2bfloat16_rn(vlo * cs - vhi * sn);
+        dst[i + half] = __float2bfloat16_rn(vhi * cs + vlo * sn);
       } else if (i >= 2 * half) {
         dst[i] = __float2bfloat16_rn(value(col0 + i));
       }

@@ -3,12 +3,12 @@
 // kernels are tested against.
 //
 //   out[m, n] = OutT( sum_k x[m, k] * w[n, k]  (+ bias[n]) )          w is [out, in]
-//   gated:      out[m, n] = T( T(silu(T(g))) * T(u) ),  g = x . w[n], u = x . w[inter + n]
+//   gated:      out[m, n] = T( silu(g) * u ),  g = x . w[n], u = x . w[inter + n]   (32-bit, one rounding)
 //
 // The sum over k runs in ascending order with one fused multiply-add per term, so an
 // output element does not depend on how the rows were batched.  Formulas:
 // rust/engine/src/runner/model/qwen2/kernels.rs:156-178, 393-418 (linear, bias in 32-bit,
-// one rounding), 422-448 (gate/up with the SiLU product), 1469-1486 (rounding order).
+// one rounding), 422-448 (gate/up with the SiLU product), 1469-1486 (SiLU).
 #include "common.cuh"
 
 namespace {
@@ -72,9 +72,8 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
       if (n >= N) continue;
       float v;
       if (GATED) {
-        const float g = round_to<T>(acc[0][i][j]);
-        const float u = round_to<T>(acc[GATED ? 1 : 0][i][j]);
-        v = round_to<T>(g / (1.f + expf(-g))) * u;
+        const float g = acc[0][i][j], u = acc[GATED ? 1 : 0][i][j];
+        v = g / (1.f + expf(-g)) * u;
       } else {
         v = acc[0][i][j] + (bias ? to_f32<T>(bias[n]) : 0.f);
       }

@@ -1,7 +1,7 @@
 // Matrix product for steps with many tokens on pairs of SMs: tcgen05.mma.cta_group::2.
 //
 //   out[t, n] = OutT( sum_k x[t, k] * w[n, k]  (+ bias[n]) )                 w is [out, in]
-//   gated:      out[t, n] = T( T(silu(T(g))) * T(u) ),  g = x . w[n], u = x . w[inter + n]
+//   gated:      out[t, n] = T( silu(g) * u ),  g = x . w[n], u = x . w[inter + n]   (32-bit, one rounding)
 //   split-K:    partial[z, t, n] = sum over the z-th slice of k   (32-bit, summed by the consumer)
 //
 // A cluster of two CTAs works on one tile of 256 tokens x 256 accumulator columns.  Each CTA
@@ -162,14 +162,11 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32
 }
 __device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-// T(silu(T(g))) * T(u) with the roundings of the reference (kernels.rs:1469-1486); exp and the
-// division use the hardware approximations (relative error about 2^-21, far below bfloat16's 2^-9).
-__device__ __forceinline__ float silu_gate(float g, float u) {
-  g = bf16_round(g);
-  u = bf16_round(u);
-  return bf16_round(__fdividef(g, 1.f + __expf(-g))) * u;
-}
+// silu(g) * u in 32-bit on the accumulators, rounded once by the caller (the reference rounds g, u
+// and silu(g) to its storage type first, kernels.rs:1469-1486: fewer roundings only come closer to
+// the exact value); exp and the division use the hardware approximations (relative error about
+// 2^-21, far below bfloat16's 2^-9).
+__device__ __forceinline__ float silu_gate(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 struct Params {
   void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats

@@ -4,10 +4,13 @@
 //
 // Formulas follow the reference's kernels, restated for paged storage:
 //   embedding   rust/engine/src/runner/model/qwen2/kernels.rs:46-57, 113-150
-//   rms_norm    kernels.rs:546-582   (32-bit sum, mean over the true width, two roundings)
+//   rms_norm    kernels.rs:546-582   (32-bit sum, mean over the true width)
 //   add         kernels.rs:1454-1467 (32-bit add, one rounding)
-//   rope        kernels.rs:587-631   (split-half pairing, 32-bit angle, cos/sin rounded to T)
+//   rope        kernels.rs:587-631   (split-half pairing, 32-bit angle)
 //   store       rust/engine/src/runner/kv_pool/naive_kvpool.rs:880-954 (K cached after rotation)
+// Inside an operator everything stays in 32-bit and the result is rounded to the storage type once,
+// at the operator's edge.  (The reference also rounds the normalised value before the weight, and
+// cos, sin and the four products of a rotation: fewer roundings only come closer to the exact value.)
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------------------
@@ -46,7 +49,7 @@ LAB_EXPORT int lab_embed(void* out, const void* table, const int* ids, int token
 // ----------------------------------------------------------------------------------------
 // Residual add + RMSNorm.
 //   r = x (+ delta) (+ sum_s partial[s])        32-bit add, rounded to T, written back to x
-//   y = T( T(r * rsqrt(mean(r^2) + eps)) * w )
+//   y = T( r * rsqrt(mean(r^2) + eps) * w )
 // `rows` (optional) gathers: output row i is computed from input row rows[i]; x is then
 // left untouched (used for the final norm at the positions whose logits are wanted).
 // `partial` (optional) holds `splits` 32-bit partial products [splits, tokens, hidden]
@@ -113,8 +116,7 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, T* __restrict__ x, const T
   const float inv = rsqrtf(ss / (float)hidden + eps);
   T* yr = y + (size_t)blockIdx.x * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float n = round_to<T>(rowbuf[i] * inv);
-    yr[i] = from_f32<T>(n * (i == (int)threadIdx.x ? w_first : to_f32<T>(w[i])));
+    yr[i] = from_f32<T>(rowbuf[i] * inv * (i == (int)threadIdx.x ? w_first : to_f32<T>(w[i])));
   }
 }
 
@@ -204,8 +206,7 @@ __global__ void __launch_bounds__(NORM_VEC_THREADS) add_rmsnorm_vec_kernel(
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 fw = __bfloat1622float2(hw[e]);
-      const float n0 = round_to<__nv_bfloat16>(v[k][2 * e] * inv), n1 = round_to<__nv_bfloat16>(v[k][2 * e + 1] * inv);
-      hp[e] = __floats2bfloat162_rn(n0 * fw.x, n1 * fw.y);
+      hp[e] = __floats2bfloat162_rn(v[k][2 * e] * inv * fw.x, v[k][2 * e + 1] * inv * fw.y);
     }
     *reinterpret_cast<uint4*>(yr + c * 8) = packed;
   }
@@ -311,13 +312,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     if (i < half) {
       float sn = sn0, cs = cs0;
       if (e != (int)threadIdx.x) sincosf(pos * inv_freq[i], &sn, &cs);
-      const float c = round_to<T>(cs), sv = round_to<T>(sn);
       // Both halves are read before either is written: a thread owns the pair (i, i + half).
       const float lo = value(col0 + i), hi = value(col0 + i + half);
-      const float a = round_to<T>(round_to<T>(lo * c) - round_to<T>(hi * sv));
-      const float b = round_to<T>(round_to<T>(hi * c) + round_to<T>(lo * sv));
-      dst[i] = from_f32<T>(a);
-      dst[i + half] = from_f32<T>(b);
+      dst[i] = from_f32<T>(lo * cs - hi * sn);
+      dst[i + half] = from_f32<T>(hi * cs + lo * sn);
     } else if (i >= 2 * half) {
       dst[i] = from_f32<T>(value(col0 + i));
     }
@@ -405,10 +403,9 @@ __global__ void __launch_bounds__(256) rope_kv_write_vec_kernel(
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float2 f = cs[j];
-    const float c = round_to<__nv_bfloat16>(f.x), sv = round_to<__nv_bfloat16>(f.y);
     const float l = __bfloat162float(lo[j]), h = __bfloat162float(hi[j]);
-    pl[j] = __float2bfloat16_rn(round_to<__nv_bfloat16>(l * c) - round_to<__nv_bfloat16>(h * sv));
-    ph[j] = __float2bfloat16_rn(round_to<__nv_bfloat16>(h * c) + round_to<__nv_bfloat16>(l * sv));
+    pl[j] = __float2bfloat16_rn(l * f.x - h * f.y);
+    ph[j] = __float2bfloat16_rn(h * f.x + l * f.y);
   }
   *reinterpret_cast<uint4*>(dst + i0) = olo;
   *reinterpret_cast<uint4*>(dst + i0 + half) = ohi;
@@ -452,7 +449,7 @@ LAB_EXPORT int lab_rope_kv_write(void* qkv, int row_stride, const float* partial
 }
 
 // ----------------------------------------------------------------------------------------
-// out = T( T(silu(gate)) * up ) for separately stored gate and up (kernels.rs:1469-1486).
+// out = T( silu(gate) * up ) for separately stored gate and up (kernels.rs:1469-1486).
 // gate_up: [tokens, 2 * inter] with gate in the first half of each row.
 // ----------------------------------------------------------------------------------------
 template <typename T>
@@ -464,8 +461,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
   const size_t t = i / inter, c = i - t * inter;
   const float g = to_f32<T>(gate_up[t * 2 * inter + c]);
   const float u = to_f32<T>(gate_up[t * 2 * inter + inter + c]);
-  const float a = round_to<T>(g / (1.f + expf(-g)));
-  out[i] = from_f32<T>(a * u);
+  out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
 }
 
 LAB_EXPORT int lab_silu_mul(void* out, const void* gate_up, int tokens, int inter, int dtype, cudaStream_t stream) {
