@@ -212,3 +212,49 @@ def test_steps_replayed_from_cuda_graphs(tmp_path_factory, dtype):
     assert engine.graph_replays >= 4 * 1 + 5 * 18, "the repeated shapes ran from graphs"
     check(got, ref, dtype, seqs)
     assert engine.cache.live_requests == 0
+
+
+def test_qwen25_05b_layer_sizes_long_prompt_in_bfloat16(tmp_path):
+    """The benchmark's layer sizes with two layers and a prompt of 4,500 tokens: the bfloat16 engine
+    (tcgen05 attention over 36 key tiles, the product on pairs of SMs for the long reduction, decode
+    attention with cluster merge and with the merge kernel) against the 32-bit engine, whole, in two
+    portions, and decoding beside a short request."""
+    from llm_inference_lab_b200.engine import Engine, Entry
+
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=151936, hidden_size=896,
+               intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2,
+               rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=8192, hidden_act="silu",
+               tie_word_embeddings=True)
+    folder = make_model_folder(str(tmp_path / "m"), cfg, seed=0, dtype="bfloat16", std=0.02, scales={})
+    rng = np.random.default_rng(8)
+    long_ids, short_ids = random_tokens(rng, 4520, cfg["vocab_size"]), random_tokens(rng, 620, cfg["vocab_size"])
+    places = [0, 127, 128, 2047, 4095, 4096, 4499]
+
+    def run(dtype, cut):
+        engine = Engine(folder, dtype, max_tokens=6144, page_size=16, max_requests=4, max_batch_tokens=8192)
+        out = {}
+        at = 0
+        for n in cut:
+            want = [p - at for p in places if at <= p < at + n]
+            logits = engine.step([Entry(0, long_ids[at: at + n], want)])
+            for w, row in zip(want, logits):
+                out[("long", at + w)] = row.float().cpu().numpy()
+            at += n
+        engine.step([Entry(1, short_ids[:600], [])])
+        for i in range(20):   # both decode: 4,500+ keys beside 600+ keys
+            logits = engine.step([Entry(0, [long_ids[4500 + i]], [0]), Entry(1, [short_ids[600 + i]], [0])])
+            out[("long", 4500 + i)] = logits[0].float().cpu().numpy()
+            out[("short", 600 + i)] = logits[1].float().cpu().numpy()
+        engine.close(0), engine.close(1)
+        assert engine.cache.live_requests == 0
+        return out
+
+    ref = run("float32", [4500])
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    for cut in ([4500], [1000, 3500]):
+        got = run("bfloat16", cut)
+        assert set(got) == set(ref)
+        worst = max(float(np.abs(got[k] - ref[k]).max()) for k in ref)
+        rms = float(np.sqrt(np.mean([np.mean((got[k] - ref[k]) ** 2) for k in ref])))
+        ref_rms = float(np.sqrt(np.mean([np.mean(ref[k] ** 2) for k in ref])))
+        assert worst <= BF16_MAX * scale and rms <= BF16_RMS * ref_rms, (cut, worst / scale, rms / ref_rms)
