@@ -608,21 +608,37 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   if constexpr (CLUSTER) {
     if (splits > 1) {
       cluster_sync();  // every split's state is in its shared memory
+      // This CTA merges its share of the output elements, one element per thread.  All of an
+      // element's remote loads are issued before the first is used, so their latencies overlap;
+      // the sum runs in ascending split order, as in the merge kernel.
       const uint32_t mine = smem_u32(smem) + DC_MERGE_BYTES;
       const int items = n_heads * D, share = (items + splits - 1) / splits;
       const int hi_item = min(items, (split + 1) * share);
       for (int i = split * share + tid; i < hi_item; i += DC_THREADS) {
         const int row = i / D, dim = i - row * D;
+        float ms[DC_MAX_CLUSTER], acc[DC_MAX_CLUSTER], ls[DC_MAX_CLUSTER];
+#pragma unroll
+        for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) {
+          ms[sp] = -INFINITY;
+          acc[sp] = ls[sp] = 0.f;
+          if (sp < splits) {
+            const uint32_t base = map_to_rank(mine + row * (D + 2) * 4, sp);
+            ms[sp] = ld_cluster_f32(base + D * 4);
+            acc[sp] = ld_cluster_f32(base + dim * 4);
+            ls[sp] = ld_cluster_f32(base + (D + 1) * 4);
+          }
+        }
         float big = -INFINITY;
-        for (int sp = 0; sp < splits; ++sp)
-          big = fmaxf(big, ld_cluster_f32(map_to_rank(mine + (row * (D + 2) + D) * 4, sp)));
+#pragma unroll
+        for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) big = fmaxf(big, ms[sp]);
         float num = 0.f, den = 0.f;
-        for (int sp = 0; sp < splits; ++sp) {  // ascending split order, as the merge kernel
-          const uint32_t base = map_to_rank(mine + row * (D + 2) * 4, sp);
-          const float ms = ld_cluster_f32(base + D * 4);
-          const float wt = (ms == -INFINITY) ? 0.f : exp2f(ms - big);
-          num += wt * ld_cluster_f32(base + dim * 4);
-          den += wt * ld_cluster_f32(base + (D + 1) * 4);
+#pragma unroll
+        for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) {
+          if (sp < splits) {
+            const float wt = (ms[sp] == -INFINITY) ? 0.f : exp2f(ms[sp] - big);
+            num += wt * acc[sp];
+            den += wt * ls[sp];
+          }
         }
         out[(size_t)qs * out_stride + (size_t)(head0 + row) * D + dim] =
             __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
@@ -672,13 +688,31 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, int out_
   if (q_start[b + 1] - qs != 1) return;
   const size_t slot0 = ((size_t)b * n_q + head) * splits;
   float big = -INFINITY;
-  for (int s = 0; s < splits; ++s) big = fmaxf(big, part_ml[(slot0 + s) * 2]);
+  for (int s0 = 0; s0 < splits; s0 += 8) {  // eight loads in flight
+    float ms[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ms[j] = s0 + j < splits ? part_ml[(slot0 + s0 + j) * 2] : -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) big = fmaxf(big, ms[j]);
+  }
   float num = 0.f, den = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = part_ml[(slot0 + s) * 2];
-    const float wt = (ms == -INFINITY) ? 0.f : exp2f(ms - big);
-    num += wt * part_acc[(slot0 + s) * D + dim];
-    den += wt * part_ml[(slot0 + s) * 2 + 1];
+  for (int s0 = 0; s0 < splits; s0 += 8) {  // the loads of eight splits first, then their sum in ascending order
+    float ms[8], acc[8], ls[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool in = s0 + j < splits;
+      ms[j] = in ? part_ml[(slot0 + s0 + j) * 2] : -INFINITY;
+      acc[j] = in ? part_acc[(slot0 + s0 + j) * D + dim] : 0.f;
+      ls[j] = in ? part_ml[(slot0 + s0 + j) * 2 + 1] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (s0 + j < splits) {
+        const float wt = (ms[j] == -INFINITY) ? 0.f : exp2f(ms[j] - big);
+        num += wt * acc[j];
+        den += wt * ls[j];
+      }
+    }
   }
   out[(size_t)qs * out_stride + (size_t)head * D + dim] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
 }
