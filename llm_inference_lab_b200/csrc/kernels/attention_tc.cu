@@ -324,10 +324,8 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, int rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 constexpr int DC_BN = 32, DC_THREADS = 128, DC_WARPS = 4;
@@ -335,11 +333,14 @@ constexpr int DC_STAGES = D <= 64 ? 3 : 2;
 constexpr int DC_TILE_BYTES = DC_BN * ROW_BYTES;
 constexpr int DC_WARP_BYTES = DC_STAGES * 2 * DC_TILE_BYTES;
 constexpr int DC_MERGE_BYTES = DC_WARPS * 16 * (D + 2) * 4;
-constexpr int DC_CLUSTER_BYTES = 16 * (D + 2) * 4;  // a CTA's merged state, read by its cluster
-constexpr int DC_SMEM = DC_WARPS * DC_WARP_BYTES > DC_MERGE_BYTES + DC_CLUSTER_BYTES ? DC_WARPS * DC_WARP_BYTES
-                                                                                    : DC_MERGE_BYTES + DC_CLUSTER_BYTES;
 constexpr int DC_MAX_CLUSTER = 8;  // the portable cluster size
-constexpr int DC_SMEM_FUSED = DC_SMEM + 18 * ROW_BYTES;  // + the rotated q rows, the newest key and value
+// What the splits of a cluster send one another: from each split the elements this CTA merges (all
+// shares together are at most 16 * D floats, rounded up per split) and 16 (max, sum) pairs.  The
+// area lies outside the rings, because a peer may write here while this CTA still reads its tiles.
+constexpr int DC_RECV_BYTES = ((16 * D + DC_MAX_CLUSTER * 33 + 8) * 4 + 15) / 16 * 16;
+constexpr int DC_RING_BYTES = DC_WARPS * DC_WARP_BYTES > DC_MERGE_BYTES ? DC_WARPS * DC_WARP_BYTES : DC_MERGE_BYTES;
+constexpr int DC_SMEM = DC_RING_BYTES + DC_RECV_BYTES;          // rings (then the warps' states), receive area
+constexpr int DC_SMEM_FUSED = DC_SMEM + 18 * ROW_BYTES;         // + the rotated q rows, the newest key and value
 
 // What the fused variant needs besides the plain one's arguments: it takes the fused projection
 // itself (rounded, or as split-K partial sums plus bias), rotates q for its heads, and the CTA
@@ -360,9 +361,10 @@ struct FusedDecodeArgs {
 };
 
 // CLUSTER: the splits of one (request, kv head, tile of heads) are the CTAs of one thread-block
-// cluster (grid x = cluster x = splits, at most 8).  Each leaves its (acc, max, sum) in its own
-// shared memory, and after a cluster barrier every CTA merges its share of the output elements
-// from all of them through distributed shared memory: no scratch and no merge kernel.
+// cluster (grid x = cluster x = splits, at most 8).  Every CTA merges a share of the output
+// elements: each split stores the (acc, max, sum) of those elements straight into the shared
+// memory of the CTA that merges them (remote stores do not stall, remote loads would), and after
+// one cluster barrier everyone finds all it needs at home: no scratch and no merge kernel.
 template <bool FUSED, bool CLUSTER = false>
 __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, int out_stride, const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -573,6 +575,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   }
   __syncthreads();
   const float* all = reinterpret_cast<const float*>(smem);
+  [[maybe_unused]] const uint32_t recv_base = smem_u32(smem) + DC_RING_BYTES;  // same offset in every CTA
   for (int i = tid; i < n_heads * D; i += DC_THREADS) {
     const int row = i / D, dim = i - row * D;
     float big = -INFINITY;
@@ -582,7 +585,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
 #pragma unroll
     for (int w = 0; w < DC_WARPS; ++w) {
       const float mw = all[(w * 16 + row) * (D + 2) + D];
-      const float wt = (mw == -INFINITY) ? 0.f : exp2f(mw - big);
+      const float wt = (mw == -INFINITY) ? 0.f : fast_exp2(mw - big);
       num += wt * all[(w * 16 + row) * (D + 2) + dim];
       den += wt * all[(w * 16 + row) * (D + 2) + D + 1];
     }
@@ -590,11 +593,15 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     if (splits == 1) {
       out[(size_t)qs * out_stride + (size_t)head * D + dim] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     } else if constexpr (CLUSTER) {
-      float* mine = reinterpret_cast<float*>(smem + DC_MERGE_BYTES);  // [16][D + 2], beside the warps' states
-      mine[row * (D + 2) + dim] = num;
-      if (dim == 0) {
-        mine[row * (D + 2) + D] = big;
-        mine[row * (D + 2) + D + 1] = den;
+      // to the CTA that merges element i: slot `split` of its receive area
+      const int share = (n_heads * D + splits - 1) / splits;
+      const int dest = i / share;
+      const uint32_t slot = recv_base + (uint32_t)(split * (share + 32)) * 4;
+      st_cluster_f32(map_to_rank(slot + (uint32_t)(i - dest * share) * 4, dest), num);
+      if (dim < splits) {  // the row's (max, sum) to every CTA of the cluster: thread `dim` serves CTA `dim`
+        const uint32_t ml = map_to_rank(slot + (uint32_t)(share + 2 * row) * 4, dim);
+        st_cluster_f32(ml, big);
+        st_cluster_f32(ml + 4, den);
       }
     } else {
       const size_t slot = ((size_t)b * n_q + head) * splits + split;
@@ -607,43 +614,27 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   }
   if constexpr (CLUSTER) {
     if (splits > 1) {
-      cluster_sync();  // every split's state is in its shared memory
-      // This CTA merges its share of the output elements, one element per thread.  All of an
-      // element's remote loads are issued before the first is used, so their latencies overlap;
+      cluster_sync();  // every split's stores have landed
+      // This CTA's share of the output elements, one element per thread, from its own shared memory;
       // the sum runs in ascending split order, as in the merge kernel.
-      const uint32_t mine = smem_u32(smem) + DC_MERGE_BYTES;
       const int items = n_heads * D, share = (items + splits - 1) / splits;
-      const int hi_item = min(items, (split + 1) * share);
-      for (int i = split * share + tid; i < hi_item; i += DC_THREADS) {
+      const int lo_item = split * share, hi_item = min(items, lo_item + share);
+      const float* recv = reinterpret_cast<const float*>(smem + DC_RING_BYTES);
+      for (int i = lo_item + tid; i < hi_item; i += DC_THREADS) {
         const int row = i / D, dim = i - row * D;
-        float ms[DC_MAX_CLUSTER], acc[DC_MAX_CLUSTER], ls[DC_MAX_CLUSTER];
-#pragma unroll
-        for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) {
-          ms[sp] = -INFINITY;
-          acc[sp] = ls[sp] = 0.f;
-          if (sp < splits) {
-            const uint32_t base = map_to_rank(mine + row * (D + 2) * 4, sp);
-            ms[sp] = ld_cluster_f32(base + D * 4);
-            acc[sp] = ld_cluster_f32(base + dim * 4);
-            ls[sp] = ld_cluster_f32(base + (D + 1) * 4);
-          }
-        }
         float big = -INFINITY;
-#pragma unroll
-        for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) big = fmaxf(big, ms[sp]);
+        for (int sp = 0; sp < splits; ++sp) big = fmaxf(big, recv[sp * (share + 32) + share + 2 * row]);
         float num = 0.f, den = 0.f;
-#pragma unroll
-        for (int sp = 0; sp < DC_MAX_CLUSTER; ++sp) {
-          if (sp < splits) {
-            const float wt = (ms[sp] == -INFINITY) ? 0.f : exp2f(ms[sp] - big);
-            num += wt * acc[sp];
-            den += wt * ls[sp];
-          }
+        for (int sp = 0; sp < splits; ++sp) {
+          const float* from = recv + sp * (share + 32);
+          const float ms = from[share + 2 * row];
+          const float wt = (ms == -INFINITY) ? 0.f : fast_exp2(ms - big);
+          num += wt * from[i - lo_item];
+          den += wt * from[share + 2 * row + 1];
         }
         out[(size_t)qs * out_stride + (size_t)(head0 + row) * D + dim] =
             __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
       }
-      cluster_sync();  // no CTA leaves while another still reads its shared memory
     }
   }
   if constexpr (FUSED && !CLUSTER) {
@@ -665,7 +656,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
         float num = 0.f, den = 0.f;
         for (int sp = 0; sp < splits; ++sp) {
           const float ms = part_ml[(slot0 + sp) * 2];
-          const float wt = (ms == -INFINITY) ? 0.f : exp2f(ms - big);
+          const float wt = (ms == -INFINITY) ? 0.f : fast_exp2(ms - big);
           num += wt * part_acc[(slot0 + sp) * D + dim];
           den += wt * part_ml[(slot0 + sp) * 2 + 1];
         }
@@ -708,7 +699,7 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, int out_
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (s0 + j < splits) {
-        const float wt = (ms[j] == -INFINITY) ? 0.f : exp2f(ms[j] - big);
+        const float wt = (ms[j] == -INFINITY) ? 0.f : fast_exp2(ms[j] - big);
         num += wt * acc[j];
         den += wt * ls[j];
       }
