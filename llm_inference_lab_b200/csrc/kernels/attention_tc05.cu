@@ -1,54 +1,68 @@
 // Causal prefill attention over the paged cache on the 5th-generation tensor cores, for heads
-// of 64 (-DLAB_HEAD_DIM=64) and page sizes of 8, 16, 32, 64 or 128 tokens.
+// of 64 and of 128 (-DLAB_HEAD_DIM) and page sizes of 8, 16, 32, 64 or 128 tokens.
 //
 // One CTA serves 128 query rows of one head of one request and walks the keys in tiles of 128:
 //   S = Q K^T        tcgen05.mma, Q and K tiles in 128-byte-swizzled shared memory (TMA; K is
-//                    gathered page by page through the block table), S in tensor memory
+//                    gathered page by page through the block table; a head of 128 is two swizzled
+//                    tiles of 64 columns side by side), S in tensor memory
 //   P = softmax(S)   four warps, one query row per thread: tcgen05.ld of the row, scale and
 //                    causal/window mask, running max and sum in 32-bit, exp2, P rounded to
 //                    bfloat16 and written back to tensor memory (tcgen05.st, two keys per column)
 //   O_j = P V        tcgen05.mma with P as the A operand from tensor memory and V as the N-major
-//                    B operand from shared memory (V rows lie [key][d] as cached)
-//   acc = acc * exp2(m_old - m_new) + O_j     in registers of the row's thread, 32-bit
-// Two S buffers, two P buffers and two O buffers (all 512 columns of tensor memory) let the MMAs
-// of tile j+1 run beside the softmax of tile j.  Formulas and rounding as the reference's
-// tensor-core prefill attention (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124,
-// 1295-1452): scores scaled by 1/sqrt(d) (folded into the exp2 argument), key <= query, p rounded
-// to T before PV, o = acc / sum.
+//                    B operand from shared memory (V rows lie [key][d] as cached), 64 output
+//                    columns per instruction
+// Heads of 64: two S, two P and two O buffers (all 512 columns of tensor memory); the row's thread
+// accumulates acc = acc * exp2(m_old - m_new) + O_j in registers, one tile behind, so the MMAs of
+// tile j+1 run beside the softmax of tile j.  Heads of 128: two S buffers and one O of 128 columns
+// that accumulates over all tiles in tensor memory; P overwrites the scores it came from (the next
+// scores for that buffer are issued after the product that reads P); a row's O is rescaled in place
+// only when its maximum has grown by more than a factor of 256 since the reference it is held
+// against, and divided by the sum at the end.
+// Formulas as the reference's tensor-core prefill attention
+// (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124, 1295-1452): scores scaled by 1/sqrt(d)
+// (folded into the exp2 argument), key <= query, p rounded to T before PV, o = acc / sum.
 //
 // Warp 0 loads (TMA; the page that holds a request's last keys is copied by hand with rows
 // beyond the length set to zero, and the rows of V of pages that are not fetched at all are set to
-// zero, because a masked NaN would still poison P V), warp 1 issues
-// the MMAs (the whole warp walks the loop, one elected lane issues) and owns tensor memory, warps
-// 2-5 do the softmax.  Every wait is bounded.
+// zero, because a masked NaN would still poison P V), warp 1 issues the MMAs (the whole warp walks
+// the loop, one elected lane issues) and owns tensor memory, warps 2-5 do the softmax.  Every wait
+// is bounded.
 #include <cuda.h>
 
 #include "common.cuh"
 
 #ifndef LAB_HEAD_DIM
-#error "build with -DLAB_HEAD_DIM=64"
+#error "build with -DLAB_HEAD_DIM=64 or 128"
 #endif
 
 namespace {
 
 constexpr int D = LAB_HEAD_DIM;
-static_assert(D == 64, "the tcgen05 attention kernel is built for heads of 64");
+static_assert(D == 64 || D == 128, "the tcgen05 attention kernel is built for heads of 64 and of 128");
 constexpr int BM = 128;        // query rows per CTA
 constexpr int BN = 128;        // keys per tile
 constexpr int THREADS = 192;
-constexpr int KV_STAGES = 4;
 constexpr int ROW = 128;       // bytes of a swizzled row: 64 bf16
-constexpr int Q_BYTES = BM * ROW;
-constexpr int KV_TILE = BN * ROW;         // one K or V tile
+constexpr int HALVES = D / 64; // a head's row is cut into 64-wide halves, each a swizzled tile of its own
+constexpr int HALF_BYTES = 128 * ROW;        // 128 rows (queries or keys) of one half
+// Heads of 128 keep O in tensor memory over all key tiles (rescaled only when a row's maximum has
+// grown much) and write P over the scores they were formed from: registers and tensor memory would
+// not hold an accumulator per thread and P beside two S buffers.
+constexpr bool O_IN_TMEM = D == 128;
+constexpr int KV_STAGES = D == 64 ? 4 : 2;
+constexpr int Q_BYTES = HALVES * HALF_BYTES;
+constexpr int KV_TILE = HALVES * HALF_BYTES;  // one K or V tile
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + Q_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE;
 constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_TILE;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
-// tensor memory columns: two S buffers (32-bit scores), two O buffers, two P buffers (bfloat16
-// pairs: 128 keys in 64 columns)
-constexpr int TM_S = 0, TM_O = 2 * BN, TM_P = TM_O + 2 * D, P_COLS = BN / 2, TMEM_COLS = 512;
-static_assert(TM_P + 2 * P_COLS <= TMEM_COLS, "tensor memory holds S, O and P twice");
+// tensor memory columns: two S buffers (32-bit scores); then, for heads of 64, two O buffers and two P
+// buffers (bfloat16 pairs: 128 keys in 64 columns); for heads of 128 one O of 128 columns, P in the
+// first 64 columns of the S buffer it came from
+constexpr int TM_S = 0, TM_O = 2 * BN, P_COLS = BN / 2, TMEM_COLS = 512;
+constexpr int TM_P = O_IN_TMEM ? TM_S : TM_O + 2 * D, P_STRIDE = O_IN_TMEM ? BN : P_COLS;
+static_assert(O_IN_TMEM ? TM_O + D <= TMEM_COLS : TM_P + 2 * P_COLS <= TMEM_COLS, "tensor memory holds S, O and P");
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -257,7 +271,8 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     // ---------------- loader ----------------
     if (lane == 0) {
       mbar_expect_tx(&bar->q_full, Q_BYTES);
-      tma_load_2d(smem_base + OFF_Q, &map_q, &bar->q_full, h * D, qs + r0);
+      for (int hf = 0; hf < HALVES; ++hf)
+        tma_load_2d(smem_base + OFF_Q + hf * HALF_BYTES, &map_q, &bar->q_full, h * D + hf * 64, qs + r0);
     }
     const int pages_per_tile = BN / page_size;  // at most 16: one lane looks up each page of a tile
     const int page_bytes = page_size * ROW;
@@ -299,12 +314,15 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       // Lane 0 announces the bytes (one of the barrier's two arrivals); then every lane fetches its
       // own page, so the copies of a tile are issued side by side.  The phase cannot end before the
       // second arrival below, whatever the order in which bytes are announced and land.
-      if (lane == 0) mbar_expect_tx(&bar->kv_full[s], 2 * __popc(tma_lanes) * page_bytes);
+      if (lane == 0) mbar_expect_tx(&bar->kv_full[s], 2 * HALVES * __popc(tma_lanes) * page_bytes);
       __syncwarp();
       if (kind == 1) {
         const int row = (page * n_kv + kvh) * page_size;
-        tma_load_2d(k_dst + lane * page_bytes, &map_k, &bar->kv_full[s], 0, row);
-        tma_load_2d(v_dst + lane * page_bytes, &map_v, &bar->kv_full[s], 0, row);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) {
+          tma_load_2d(k_dst + hf * HALF_BYTES + lane * page_bytes, &map_k, &bar->kv_full[s], hf * 64, row);
+          tma_load_2d(v_dst + hf * HALF_BYTES + lane * page_bytes, &map_v, &bar->kv_full[s], hf * 64, row);
+        }
       }
       if (tail_lanes) {
         // The page with the request's last keys: rows below the length are copied, the rest set to
@@ -313,15 +331,15 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         const int tail_page = __shfl_sync(0xffffffffu, page, tail_slot);
         const int k_lo = key0 + tail_slot * page_size;
         const size_t src0 = ((size_t)tail_page * n_kv + kvh) * page_size * D;
-        for (int c = lane; c < page_size * 8; c += 32) {
-          const int r = c >> 3, q8 = c & 7;
+        for (int c = lane; c < page_size * (D / 8); c += 32) {
+          const int r = c / (D / 8), q16 = c - r * (D / 8), hf = q16 >> 3, q8 = q16 & 7;
           const int tile_row = tail_slot * page_size + r;
           uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
           if (k_lo + r < kvl) {
-            kk = *reinterpret_cast<const uint4*>(cache_k + src0 + (size_t)r * D + q8 * 8);
-            vv = *reinterpret_cast<const uint4*>(cache_v + src0 + (size_t)r * D + q8 * 8);
+            kk = *reinterpret_cast<const uint4*>(cache_k + src0 + (size_t)r * D + q16 * 8);
+            vv = *reinterpret_cast<const uint4*>(cache_v + src0 + (size_t)r * D + q16 * 8);
           }
-          const int off = tile_row * ROW + ((q8 ^ (tile_row & 7)) << 4);
+          const int off = hf * HALF_BYTES + tile_row * ROW + ((q8 ^ (tile_row & 7)) << 4);
           *reinterpret_cast<uint4*>(smem + OFF_K + s * KV_TILE + off) = kk;
           *reinterpret_cast<uint4*>(smem + OFF_V + s * KV_TILE + off) = vv;
         }
@@ -332,8 +350,10 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       while (skip_lanes) {
         const int slot = __ffs(skip_lanes) - 1;
         skip_lanes &= skip_lanes - 1;
-        uint4* vz = reinterpret_cast<uint4*>(smem + OFF_V + s * KV_TILE + slot * page_bytes);
-        for (int c = lane; c < page_bytes / 16; c += 32) vz[c] = make_uint4(0, 0, 0, 0);
+        for (int hf = 0; hf < HALVES; ++hf) {
+          uint4* vz = reinterpret_cast<uint4*>(smem + OFF_V + s * KV_TILE + hf * HALF_BYTES + slot * page_bytes);
+          for (int c = lane; c < page_bytes / 16; c += 32) vz[c] = make_uint4(0, 0, 0, 0);
+        }
       }
       proxy_fence();  // the hand-written rows become visible to the tensor cores
       __syncwarp();
@@ -345,7 +365,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     // commit: the operands are uniform across the warp, as the instructions want them.
     {
       constexpr uint32_t idesc_s = instr_desc(BN, false);
-      constexpr uint32_t idesc_o = instr_desc(D, true);
+      constexpr uint32_t idesc_o = instr_desc(64, true);   // P V in pieces of 64 output columns
       auto wait_all = [&](uint64_t* b, uint32_t parity) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(b, parity, abort_flag));
       };
@@ -356,10 +376,14 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         if (!wait_all(&bar->s_empty[sb], ((j >> 1) & 1) ^ 1)) return false;
         tc_fence_after();
         // descriptors of the first 16 dimensions; each further 16 lie 32 bytes (two address units) on
-        const uint64_t qd = smem_desc_sw128(smem_base + OFF_Q), kd = smem_desc_sw128(smem_base + OFF_K + s * KV_TILE);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_bf16(tmem_base + TM_S + sb * BN, qd + 2 * k, kd + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+        for (int hf = 0; hf < HALVES; ++hf) {
+          const uint64_t qd = smem_desc_sw128(smem_base + OFF_Q + hf * HALF_BYTES),
+                         kd = smem_desc_sw128(smem_base + OFF_K + s * KV_TILE + hf * HALF_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + TM_S + sb * BN, qd + 2 * k, kd + 2 * k, idesc_s, (hf | k) > 0 ? 1u : 0u);
+        }
         umma_commit(&bar->s_full[sb]);
         return true;
       };
@@ -369,16 +393,22 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         if (!ok) break;
         const int s = j % KV_STAGES, sb = j & 1;
         ok = wait_all(&bar->p_full[sb], (j >> 1) & 1);
-        ok = ok && wait_all(&bar->o_empty[sb], ((j >> 1) & 1) ^ 1);
+        if (!O_IN_TMEM) ok = ok && wait_all(&bar->o_empty[sb], ((j >> 1) & 1) ^ 1);
         if (!ok) break;
         tc_fence_after();
-        // V rows are keys: 16 keys lie 16 * 128 bytes (128 address units) on
-        const uint64_t vd = smem_desc_sw128(smem_base + OFF_V + s * KV_TILE);
+        // V rows are keys: 16 keys lie 16 * 128 bytes (128 address units) on.  Heads of 64: O_j alone
+        // into buffer j % 2.  Heads of 128: two pieces of 64 columns, added to the one O of all tiles.
+        const uint32_t o_at = tmem_base + TM_O + (O_IN_TMEM ? 0 : sb * D);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          umma_bf16_tmem_a(tmem_base + TM_O + sb * D, tmem_base + TM_P + sb * P_COLS + kk * 8,
-                           vd + (uint64_t)(kk * 16 * ROW / 16), idesc_o, kk > 0 ? 1u : 0u);
-        umma_commit(&bar->o_full[sb]);
+        for (int hf = 0; hf < HALVES; ++hf) {
+          const uint64_t vd = smem_desc_sw128(smem_base + OFF_V + s * KV_TILE + hf * HALF_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            umma_bf16_tmem_a(o_at + hf * 64, tmem_base + TM_P + sb * P_STRIDE + kk * 8,
+                             vd + (uint64_t)(kk * 16 * ROW / 16), idesc_o,
+                             (kk > 0 || (O_IN_TMEM && j > 0)) ? 1u : 0u);
+        }
+        umma_commit(&bar->o_full[O_IN_TMEM ? 0 : sb]);
         umma_commit(&bar->kv_empty[s]);  // both products of this stage have been issued
       }
     }
@@ -391,110 +421,231 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     const int hi = row_valid ? pos : -1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    float acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
-    // m: running maximum (log2 units) after the last tile seen; l: running sum relative to m;
-    // acc: sum of P V relative to m_acc, which lags one tile behind m.
-    float m = -INFINITY, l = 0.f, m_acc = -INFINITY, m_of_prev_tile = -INFINITY;
-    bool ok = true;
-    // acc = acc * 2^(m_acc - m_j) + O_j, where O_j was formed with P relative to m_j.
-    auto accumulate = [&](int j, float m_j) {
-      const int sb = j & 1;
-      ok = ok && mbar_wait(&bar->o_full[sb], (j >> 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) return;
-      tc_fence_after();
-      const float corr = (m_acc == -INFINITY) ? 0.f : fast_exp2(m_acc - m_j);
-#pragma unroll
-      for (int half = 0; half < D / 32; ++half) {
-        uint32_t r[32];
-        tmem_ld32_issue(lane_addr + TM_O + sb * D + half * 32, r);
-        tmem_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[half * 32 + i] = acc[half * 32 + i] * corr + __uint_as_float(r[i]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->o_empty[sb]);  // the O buffer may be overwritten
-      m_acc = m_j;
-    };
-    for (int j = 0; j < n_tiles; ++j) {
-      const int sb = j & 1;
-      ok = ok && mbar_wait(&bar->s_full[sb], (j >> 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t sr[BN];
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(lane_addr + TM_S + sb * BN + c * 32, sr + c * 32);
-      tmem_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->s_empty[sb]);  // the scores are in registers: the buffer is free
-      const int key0 = (t_first + j) * BN;
-      const bool all_visible = key0 >= lo && key0 + BN - 1 <= hi;
-      // Maxima are taken over the raw scores (the scale is positive), four chains side by side;
-      // the scale is applied inside the exponent: p = 2^(s * scale - m * scale), one FMA per score.
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (all_visible) {
-#pragma unroll
-        for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
-      } else {
-#pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          if (key0 + c < lo || key0 + c > hi) sr[c] = __float_as_uint(-INFINITY);
-          mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
-        }
-      }
-      const float m_new = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
-      const float base = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen no key yet
-      l *= (m == -INFINITY) ? 0.f : fast_exp2(m - base);
-      m = m_new;
-      // P, rounded to bfloat16, into tensor memory as the A operand of P V: this row's lane, two
-      // keys per 32-bit column
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c32 = 0; c32 < BN / 64; ++c32) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int c = c32 * 64 + 2 * i;
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale_log2, -base));  // 2^(-inf) = 0 for masked keys
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale_log2, -base));
-          sum4[i & 1] += p0;
-          sum4[2 + (i & 1)] += p1;
-          pk[i] = pack_bf16(p0, p1);
-        }
-        tmem_st32(lane_addr + TM_P + sb * P_COLS + c32 * 32, pk);
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      tmem_st_wait();
-      tc_fence_before();  // the stores of P are ordered before the MMAs that the arrival releases
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->p_full[sb]);
-      // While the tensor cores form O_j, fold in O_{j-1}.
-      if (j > 0) {
-        accumulate(j - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
+    if constexpr (O_IN_TMEM) {
+      // ---- heads of 128: O accumulates in tensor memory over all tiles, relative to a reference
+      // maximum m_ref per row (log2 units); l is the running sum relative to m_ref.  m_ref follows
+      // the true maximum lazily: only when a row's maximum has grown by more than RESCALE (a factor
+      // of 256) is the row of O rescaled, so p = 2^(s - m_ref) stays below 256: exact in the exponent,
+      // rounded to bfloat16 as ever, and O and l are 32-bit.  P overwrites the scores it came from.
+      constexpr float RESCALE = 8.f;
+      const uint32_t o_addr = lane_addr + TM_O;
+      float m_ref = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int sb = j & 1;
+        ok = ok && mbar_wait(&bar->s_full[sb], (j >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-      }
-      m_of_prev_tile = m_new;
-    }
-    if (ok && n_tiles > 0) accumulate(n_tiles - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
-    if (ok && row_valid) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + (size_t)(qs + r0 + row) * out_stride + (size_t)h * D;
+        tc_fence_after();
+        uint32_t sr[BN];
 #pragma unroll
-      for (int q8 = 0; q8 < D / 8; ++q8) {
-        const uint4 packed = make_uint4(pack_bf16(acc[q8 * 8] * inv, acc[q8 * 8 + 1] * inv),
-                                        pack_bf16(acc[q8 * 8 + 2] * inv, acc[q8 * 8 + 3] * inv),
-                                        pack_bf16(acc[q8 * 8 + 4] * inv, acc[q8 * 8 + 5] * inv),
-                                        pack_bf16(acc[q8 * 8 + 6] * inv, acc[q8 * 8 + 7] * inv));
-        if ((((uintptr_t)dst) & 15) == 0) {
-          reinterpret_cast<uint4*>(dst)[q8] = packed;
+        for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(lane_addr + TM_S + sb * BN + c * 32, sr + c * 32);
+        tmem_wait();
+        const int key0 = (t_first + j) * BN;
+        const bool all_visible = key0 >= lo && key0 + BN - 1 <= hi;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (all_visible) {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
         } else {
-          const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&packed);
-          for (int e = 0; e < 8; ++e) dst[q8 * 8 + e] = hp[e];
+#pragma unroll
+          for (int c = 0; c < BN; ++c) {
+            if (key0 + c < lo || key0 + c > hi) sr[c] = __float_as_uint(-INFINITY);
+            mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+          }
+        }
+        const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
+        if (j == 0) {
+          m_ref = m_new;
+        } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE || (m_ref == -INFINITY && m_new != -INFINITY))) {
+          // Some row of this warp has outgrown its reference: every row of the warp moves to its true
+          // maximum.  The product of the previous tile must have landed in O before O is rescaled.
+          ok = ok && mbar_wait(&bar->o_full[0], (j - 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const float f = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);  // 1 for a row that has not grown
+#pragma unroll
+          for (int part = 0; part < D / 32; ++part) {
+            uint32_t r[32];
+            tmem_ld32_issue(o_addr + part * 32, r);
+            tmem_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+            tmem_st32(o_addr + part * 32, r);
+          }
+          l *= f;
+          m_ref = m_new;
+        }
+        const float base = (m_ref == -INFINITY) ? 0.f : m_ref;  // a row that has seen no key yet
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c32 = 0; c32 < BN / 64; ++c32) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c = c32 * 64 + 2 * i;
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale_log2, -base));  // 2^(-inf) = 0 for masked keys
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale_log2, -base));
+            sum4[i & 1] += p0;
+            sum4[2 + (i & 1)] += p1;
+            pk[i] = pack_bf16(p0, p1);
+          }
+          tmem_st32(lane_addr + TM_P + sb * P_STRIDE + c32 * 32, pk);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tmem_st_wait();
+        tc_fence_before();  // the loads of S and the stores of P (and of O) are ordered before the arrivals
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bar->s_empty[sb]);  // given free with P: the next scores for this buffer are
+          mbar_arrive(&bar->p_full[sb]);   // issued after the product that reads P from it
+        }
+      }
+      // The last product.  A parity names a phase only among the current one and the one before:
+      // the scores of the last tile prove the product of tile n - 3 done, no more (they were issued
+      // before the product of tile n - 2), so that one is awaited first.
+      if (ok && n_tiles > 1) {
+        ok = mbar_wait(&bar->o_full[0], (n_tiles - 2) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok && n_tiles > 0) {
+        ok = mbar_wait(&bar->o_full[0], (n_tiles - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = out + (size_t)(qs + r0 + row) * out_stride + (size_t)h * D;
+#pragma unroll
+        for (int part = 0; part < D / 32; ++part) {
+          uint32_t r[32];
+          tmem_ld32_issue(o_addr + part * 32, r);   // every lane takes part in the load
+          tmem_wait();
+          if (!row_valid || n_tiles == 0) continue;
+#pragma unroll
+          for (int q8 = 0; q8 < 4; ++q8) {
+            const uint4 packed = make_uint4(
+                pack_bf16(__uint_as_float(r[q8 * 8]) * inv, __uint_as_float(r[q8 * 8 + 1]) * inv),
+                pack_bf16(__uint_as_float(r[q8 * 8 + 2]) * inv, __uint_as_float(r[q8 * 8 + 3]) * inv),
+                pack_bf16(__uint_as_float(r[q8 * 8 + 4]) * inv, __uint_as_float(r[q8 * 8 + 5]) * inv),
+                pack_bf16(__uint_as_float(r[q8 * 8 + 6]) * inv, __uint_as_float(r[q8 * 8 + 7]) * inv));
+            __nv_bfloat16* d8 = dst + part * 32 + q8 * 8;
+            if ((((uintptr_t)d8) & 15) == 0) {
+              *reinterpret_cast<uint4*>(d8) = packed;
+            } else {
+              const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&packed);
+              for (int e = 0; e < 8; ++e) d8[e] = hp[e];
+            }
+          }
+        }
+      }
+    } else {
+      float acc[D];
+#pragma unroll
+      for (int i = 0; i < D; ++i) acc[i] = 0.f;
+      // m: running maximum (log2 units) after the last tile seen; l: running sum relative to m;
+      // acc: sum of P V relative to m_acc, which lags one tile behind m.
+      float m = -INFINITY, l = 0.f, m_acc = -INFINITY, m_of_prev_tile = -INFINITY;
+      bool ok = true;
+      // acc = acc * 2^(m_acc - m_j) + O_j, where O_j was formed with P relative to m_j.
+      auto accumulate = [&](int j, float m_j) {
+        const int sb = j & 1;
+        ok = ok && mbar_wait(&bar->o_full[sb], (j >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        tc_fence_after();
+        const float corr = (m_acc == -INFINITY) ? 0.f : fast_exp2(m_acc - m_j);
+#pragma unroll
+        for (int half = 0; half < D / 32; ++half) {
+          uint32_t r[32];
+          tmem_ld32_issue(lane_addr + TM_O + sb * D + half * 32, r);
+          tmem_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[half * 32 + i] = acc[half * 32 + i] * corr + __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->o_empty[sb]);  // the O buffer may be overwritten
+        m_acc = m_j;
+      };
+      for (int j = 0; j < n_tiles; ++j) {
+        const int sb = j & 1;
+        ok = ok && mbar_wait(&bar->s_full[sb], (j >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr[BN];
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(lane_addr + TM_S + sb * BN + c * 32, sr + c * 32);
+        tmem_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->s_empty[sb]);  // the scores are in registers: the buffer is free
+        const int key0 = (t_first + j) * BN;
+        const bool all_visible = key0 >= lo && key0 + BN - 1 <= hi;
+        // Maxima are taken over the raw scores (the scale is positive), four chains side by side;
+        // the scale is applied inside the exponent: p = 2^(s * scale - m * scale), one FMA per score.
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (all_visible) {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) {
+            if (key0 + c < lo || key0 + c > hi) sr[c] = __float_as_uint(-INFINITY);
+            mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+          }
+        }
+        const float m_new = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
+        const float base = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen no key yet
+        l *= (m == -INFINITY) ? 0.f : fast_exp2(m - base);
+        m = m_new;
+        // P, rounded to bfloat16, into tensor memory as the A operand of P V: this row's lane, two
+        // keys per 32-bit column
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c32 = 0; c32 < BN / 64; ++c32) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int c = c32 * 64 + 2 * i;
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale_log2, -base));  // 2^(-inf) = 0 for masked keys
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale_log2, -base));
+            sum4[i & 1] += p0;
+            sum4[2 + (i & 1)] += p1;
+            pk[i] = pack_bf16(p0, p1);
+          }
+          tmem_st32(lane_addr + TM_P + sb * P_COLS + c32 * 32, pk);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tmem_st_wait();
+        tc_fence_before();  // the stores of P are ordered before the MMAs that the arrival releases
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar->p_full[sb]);
+        // While the tensor cores form O_j, fold in O_{j-1}.
+        if (j > 0) {
+          accumulate(j - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
+          if (!ok) break;
+        }
+        m_of_prev_tile = m_new;
+      }
+      if (ok && n_tiles > 0) accumulate(n_tiles - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
+      if (ok && row_valid) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = out + (size_t)(qs + r0 + row) * out_stride + (size_t)h * D;
+#pragma unroll
+        for (int q8 = 0; q8 < D / 8; ++q8) {
+          const uint4 packed = make_uint4(pack_bf16(acc[q8 * 8] * inv, acc[q8 * 8 + 1] * inv),
+                                          pack_bf16(acc[q8 * 8 + 2] * inv, acc[q8 * 8 + 3] * inv),
+                                          pack_bf16(acc[q8 * 8 + 4] * inv, acc[q8 * 8 + 5] * inv),
+                                          pack_bf16(acc[q8 * 8 + 6] * inv, acc[q8 * 8 + 7] * inv));
+          if ((((uintptr_t)dst) & 15) == 0) {
+            reinterpret_cast<uint4*>(dst)[q8] = packed;
+          } else {
+            const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&packed);
+            for (int e = 0; e < 8; ++e) dst[q8 * 8 + e] = hp[e];
+          }
         }
       }
     }

@@ -486,8 +486,8 @@ def linear_gated(x, w_gate_up):
     return gemm_tc(x, w_gate_up, None, gated=True)
 
 
-# Which kernel serves requests that bring several tokens: "auto" (tcgen05 for heads of 64 once a
-# request brings more than 64 tokens, else mma.sync), "mma" or "tc05".
+# Which kernel serves requests that bring several tokens: "auto" (tcgen05 for heads of 64 and of 128
+# once a request brings more than 64 tokens, else mma.sync), "mma" or "tc05".
 PREFILL_KERNEL = "auto"
 
 
@@ -535,7 +535,7 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     max_q = max(q_lens)
     n_decode = sum(1 for n in q_lens if n == 1)
     use_tc05 = PREFILL_KERNEL == "tc05" or (PREFILL_KERNEL == "auto" and max_q > 64)
-    if max_q > 1 and use_tc05 and head_dim == 64 and page_size >= 8 and page_size <= 128 and \
+    if max_q > 1 and use_tc05 and head_dim in (64, 128) and page_size >= 8 and page_size <= 128 and \
             page_size & (page_size - 1) == 0:
         # tcgen05 kernel: tiles of 128 query rows, scores and P V on the 5th-generation tensor cores
         L5 = lib("attention_tc05", {"LAB_HEAD_DIM": head_dim})

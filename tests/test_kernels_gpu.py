@@ -412,18 +412,56 @@ TC05_CASES = [
 
 
 @pytest.mark.parametrize("n_q,n_kv,ps,window,requests", TC05_CASES)
-def test_attention_prefill_tcgen05(n_q, n_kv, ps, window, requests):
-    """The tcgen05 prefill kernel (heads of 64) against the 64-bit reference: whole prompts, portions
-    on top of a long history, ragged batches beside decode rows, windows, every supported page size.
-    Unused cache slots hold NaN: nothing beyond a request's length may leak into P V."""
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_prefill_tcgen05(d, n_q, n_kv, ps, window, requests):
+    """The tcgen05 prefill kernel (heads of 64 and of 128) against the 64-bit reference: whole prompts,
+    portions on top of a long history, ragged batches beside decode rows, windows, every supported
+    page size.  Unused cache slots hold NaN: nothing beyond a request's length may leak into P V."""
     old = ops().PREFILL_KERNEL
     ops().PREFILL_KERNEL = "tc05"
     try:
-        got, want = run_attention("tc", requests, n_q, n_kv, 64, ps, window, torch.bfloat16, seed=3)
+        got, want = run_attention("tc", requests, n_q, n_kv, d, ps, window, torch.bfloat16, seed=3)
     finally:
         ops().PREFILL_KERNEL = old
     for g, w in zip(got, want):
         assert rel_err(g, w) < 2e-2
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("pattern", ["climbing", "falling", "late_needle"])
+def test_attention_prefill_tcgen05_running_maximum(d, pattern):
+    """Scores that climb from key tile to key tile (the running maximum grows by far more than a factor
+    of 256 several times: the kernel for heads of 128 must rescale its accumulator in tensor memory),
+    scores that fall (the first tile's maximum stays the reference to the end), and one late key far
+    above all others.  Values differ from key to key, so a wrong weight shows."""
+    n_q, n_kv, ps, T = 2, 1, 16, 700
+
+    def tweak(qs, ks, vs, ck, cv, bt):
+        q, k, v = qs[0], ks[0], vs[0]
+        direction = torch.ones(d) / math.sqrt(d)
+        q[:, :, :] = (direction * 6.0).to(q.dtype)                 # every query points the same way
+        pos = torch.arange(T, dtype=torch.float32)
+        if pattern == "climbing":
+            size = pos / 128.0 * 3.0                               # + 18 in the exponent per tile of 128 keys
+        elif pattern == "falling":
+            size = (T - pos) / 128.0 * 3.0
+        else:
+            size = torch.zeros(T)
+            size[650] = 60.0
+        noise = torch.randn(T, d, generator=torch.Generator().manual_seed(1)) * 0.05
+        k[:, 0, :] = (direction[None, :] * size[:, None] * math.sqrt(d) / 6.0 * 2.0 + noise).to(k.dtype)
+        v[:, 0, :] = (torch.sin(pos)[:, None] * torch.linspace(0.5, 2.0, d)[None, :]).to(v.dtype)
+        for p in range(T):
+            ck[bt[0, p // ps], 0, p % ps, :] = k[p, 0]
+            cv[bt[0, p // ps], 0, p % ps, :] = v[p, 0]
+
+    old = ops().PREFILL_KERNEL
+    ops().PREFILL_KERNEL = "tc05"
+    try:
+        got, want = run_attention("tc", [(T, T)], n_q, n_kv, d, ps, 0, torch.bfloat16, seed=4, tweak=tweak)
+    finally:
+        ops().PREFILL_KERNEL = old
+    assert rel_err(got[0], want[0]) < 2e-2
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
