@@ -11,13 +11,12 @@
 //   O_j = P V        tcgen05.mma with P as the A operand from tensor memory and V as the N-major
 //                    B operand from shared memory (V rows lie [key][d] as cached), 64 output
 //                    columns per instruction
-// Heads of 64: two S, two P and two O buffers (all 512 columns of tensor memory); the row's thread
-// accumulates acc = acc * exp2(m_old - m_new) + O_j in registers, one tile behind, so the MMAs of
-// tile j+1 run beside the softmax of tile j.  Heads of 128: two S buffers and one O of 128 columns
-// that accumulates over all tiles in tensor memory; P overwrites the scores it came from (the next
-// scores for that buffer are issued after the product that reads P); a row's O is rescaled in place
-// only when its maximum has grown by more than a factor of 256 since the reference it is held
-// against, and divided by the sum at the end.
+// Tensor memory holds two S buffers, so that the scores of tile j+1 are formed beside the softmax of
+// tile j, and one O of D columns that accumulates over all tiles.  P overwrites the scores it came
+// from (the next scores for that buffer are issued after the product that reads P).  A row's O is
+// rescaled in place only when its maximum has grown by more than a factor of 256 since the reference
+// it is held against, and divided by the sum at the end.  (For heads of 64 an accumulator in
+// registers, rescaled every tile from two O buffers, was measured 10 % slower.)
 // Formulas as the reference's tensor-core prefill attention
 // (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124, 1295-1452): scores scaled by 1/sqrt(d)
 // (folded into the exp2 argument), key <= query, p rounded to T before PV, o = acc / sum.
@@ -45,10 +44,6 @@ constexpr int THREADS = 192;
 constexpr int ROW = 128;       // bytes of a swizzled row: 64 bf16
 constexpr int HALVES = D / 64; // a head's row is cut into 64-wide halves, each a swizzled tile of its own
 constexpr int HALF_BYTES = 128 * ROW;        // 128 rows (queries or keys) of one half
-// Heads of 128 keep O in tensor memory over all key tiles (rescaled only when a row's maximum has
-// grown much) and write P over the scores they were formed from: registers and tensor memory would
-// not hold an accumulator per thread and P beside two S buffers.
-constexpr bool O_IN_TMEM = D == 128;
 constexpr int KV_STAGES = D == 64 ? 4 : 2;
 constexpr int Q_BYTES = HALVES * HALF_BYTES;
 constexpr int KV_TILE = HALVES * HALF_BYTES;  // one K or V tile
@@ -57,12 +52,10 @@ constexpr int OFF_K = OFF_Q + Q_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE;
 constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_TILE;
 constexpr int SMEM = OFF_BAR + 256 + 1024;
-// tensor memory columns: two S buffers (32-bit scores); then, for heads of 64, two O buffers and two P
-// buffers (bfloat16 pairs: 128 keys in 64 columns); for heads of 128 one O of 128 columns, P in the
-// first 64 columns of the S buffer it came from
-constexpr int TM_S = 0, TM_O = 2 * BN, P_COLS = BN / 2, TMEM_COLS = 512;
-constexpr int TM_P = O_IN_TMEM ? TM_S : TM_O + 2 * D, P_STRIDE = O_IN_TMEM ? BN : P_COLS;
-static_assert(O_IN_TMEM ? TM_O + D <= TMEM_COLS : TM_P + 2 * P_COLS <= TMEM_COLS, "tensor memory holds S, O and P");
+// tensor memory columns: two S buffers (32-bit scores), then one O of D columns.  P (bfloat16 pairs:
+// 128 keys in 64 columns) lies in the first 64 columns of the S buffer it came from.
+constexpr int TM_S = 0, TM_O = 2 * BN, TMEM_COLS = 512;
+static_assert(TM_O + D <= TMEM_COLS, "tensor memory holds S and O");
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -200,7 +193,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 struct Barriers {
   uint64_t q_full;
   uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
-  uint64_t s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2];
+  uint64_t s_full[2], s_empty[2], p_full[2], o_full;
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -248,9 +241,8 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       mbar_init(&bar->s_full[i], 1);
       mbar_init(&bar->s_empty[i], 4);
       mbar_init(&bar->p_full[i], 4);
-      mbar_init(&bar->o_full[i], 1);
-      mbar_init(&bar->o_empty[i], 4);
     }
+    mbar_init(&bar->o_full, 1);
     bar->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -393,22 +385,21 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         if (!ok) break;
         const int s = j % KV_STAGES, sb = j & 1;
         ok = wait_all(&bar->p_full[sb], (j >> 1) & 1);
-        if (!O_IN_TMEM) ok = ok && wait_all(&bar->o_empty[sb], ((j >> 1) & 1) ^ 1);
         if (!ok) break;
         tc_fence_after();
-        // V rows are keys: 16 keys lie 16 * 128 bytes (128 address units) on.  Heads of 64: O_j alone
-        // into buffer j % 2.  Heads of 128: two pieces of 64 columns, added to the one O of all tiles.
-        const uint32_t o_at = tmem_base + TM_O + (O_IN_TMEM ? 0 : sb * D);
+        // V rows are keys: 16 keys lie 16 * 128 bytes (128 address units) on.  The product is formed in
+        // pieces of 64 output columns and added to the one O of all tiles.
+        const uint32_t o_at = tmem_base + TM_O;
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf) {
           const uint64_t vd = smem_desc_sw128(smem_base + OFF_V + s * KV_TILE + hf * HALF_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk)
-            umma_bf16_tmem_a(o_at + hf * 64, tmem_base + TM_P + sb * P_STRIDE + kk * 8,
+            umma_bf16_tmem_a(o_at + hf * 64, tmem_base + TM_S + sb * BN + kk * 8,
                              vd + (uint64_t)(kk * 16 * ROW / 16), idesc_o,
-                             (kk > 0 || (O_IN_TMEM && j > 0)) ? 1u : 0u);
+                             (kk | j) > 0 ? 1u : 0u);
         }
-        umma_commit(&bar->o_full[O_IN_TMEM ? 0 : sb]);
+        umma_commit(&bar->o_full);
         umma_commit(&bar->kv_empty[s]);  // both products of this stage have been issued
       }
     }
@@ -421,10 +412,9 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     const int hi = row_valid ? pos : -1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    if constexpr (O_IN_TMEM) {
-      // ---- heads of 128: O accumulates in tensor memory over all tiles, relative to a reference
-      // maximum m_ref per row (log2 units); l is the running sum relative to m_ref.  m_ref follows
-      // the true maximum lazily: only when a row's maximum has grown by more than RESCALE (a factor
+    {
+      // O accumulates in tensor memory over all tiles, relative to a reference maximum m_ref per row
+      // (log2 units); l is the running sum relative to m_ref.  m_ref follows the true maximum lazily: only when a row's maximum has grown by more than RESCALE (a factor
       // of 256) is the row of O rescaled, so p = 2^(s - m_ref) stays below 256: exact in the exponent,
       // rounded to bfloat16 as ever, and O and l are 32-bit.  P overwrites the scores it came from.
       constexpr float RESCALE = 8.f;
@@ -460,7 +450,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE || (m_ref == -INFINITY && m_new != -INFINITY))) {
           // Some row of this warp has outgrown its reference: every row of the warp moves to its true
           // maximum.  The product of the previous tile must have landed in O before O is rescaled.
-          ok = ok && mbar_wait(&bar->o_full[0], (j - 1) & 1, abort_flag);
+          ok = ok && mbar_wait(&bar->o_full, (j - 1) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
@@ -491,7 +481,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
             sum4[2 + (i & 1)] += p1;
             pk[i] = pack_bf16(p0, p1);
           }
-          tmem_st32(lane_addr + TM_P + sb * P_STRIDE + c32 * 32, pk);
+          tmem_st32(lane_addr + TM_S + sb * BN + c32 * 32, pk);
         }
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         tmem_st_wait();
@@ -506,11 +496,11 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       // the scores of the last tile prove the product of tile n - 3 done, no more (they were issued
       // before the product of tile n - 2), so that one is awaited first.
       if (ok && n_tiles > 1) {
-        ok = mbar_wait(&bar->o_full[0], (n_tiles - 2) & 1, abort_flag);
+        ok = mbar_wait(&bar->o_full, (n_tiles - 2) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok && n_tiles > 0) {
-        ok = mbar_wait(&bar->o_full[0], (n_tiles - 1) & 1, abort_flag);
+        ok = mbar_wait(&bar->o_full, (n_tiles - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
@@ -537,114 +527,6 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
               const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&packed);
               for (int e = 0; e < 8; ++e) d8[e] = hp[e];
             }
-          }
-        }
-      }
-    } else {
-      float acc[D];
-#pragma unroll
-      for (int i = 0; i < D; ++i) acc[i] = 0.f;
-      // m: running maximum (log2 units) after the last tile seen; l: running sum relative to m;
-      // acc: sum of P V relative to m_acc, which lags one tile behind m.
-      float m = -INFINITY, l = 0.f, m_acc = -INFINITY, m_of_prev_tile = -INFINITY;
-      bool ok = true;
-      // acc = acc * 2^(m_acc - m_j) + O_j, where O_j was formed with P relative to m_j.
-      auto accumulate = [&](int j, float m_j) {
-        const int sb = j & 1;
-        ok = ok && mbar_wait(&bar->o_full[sb], (j >> 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) return;
-        tc_fence_after();
-        const float corr = (m_acc == -INFINITY) ? 0.f : fast_exp2(m_acc - m_j);
-#pragma unroll
-        for (int half = 0; half < D / 32; ++half) {
-          uint32_t r[32];
-          tmem_ld32_issue(lane_addr + TM_O + sb * D + half * 32, r);
-          tmem_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[half * 32 + i] = acc[half * 32 + i] * corr + __uint_as_float(r[i]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar->o_empty[sb]);  // the O buffer may be overwritten
-        m_acc = m_j;
-      };
-      for (int j = 0; j < n_tiles; ++j) {
-        const int sb = j & 1;
-        ok = ok && mbar_wait(&bar->s_full[sb], (j >> 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        uint32_t sr[BN];
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(lane_addr + TM_S + sb * BN + c * 32, sr + c * 32);
-        tmem_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar->s_empty[sb]);  // the scores are in registers: the buffer is free
-        const int key0 = (t_first + j) * BN;
-        const bool all_visible = key0 >= lo && key0 + BN - 1 <= hi;
-        // Maxima are taken over the raw scores (the scale is positive), four chains side by side;
-        // the scale is applied inside the exponent: p = 2^(s * scale - m * scale), one FMA per score.
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (all_visible) {
-#pragma unroll
-          for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
-        } else {
-#pragma unroll
-          for (int c = 0; c < BN; ++c) {
-            if (key0 + c < lo || key0 + c > hi) sr[c] = __float_as_uint(-INFINITY);
-            mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
-          }
-        }
-        const float m_new = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
-        const float base = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen no key yet
-        l *= (m == -INFINITY) ? 0.f : fast_exp2(m - base);
-        m = m_new;
-        // P, rounded to bfloat16, into tensor memory as the A operand of P V: this row's lane, two
-        // keys per 32-bit column
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c32 = 0; c32 < BN / 64; ++c32) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int c = c32 * 64 + 2 * i;
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), scale_log2, -base));  // 2^(-inf) = 0 for masked keys
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), scale_log2, -base));
-            sum4[i & 1] += p0;
-            sum4[2 + (i & 1)] += p1;
-            pk[i] = pack_bf16(p0, p1);
-          }
-          tmem_st32(lane_addr + TM_P + sb * P_COLS + c32 * 32, pk);
-        }
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        tmem_st_wait();
-        tc_fence_before();  // the stores of P are ordered before the MMAs that the arrival releases
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar->p_full[sb]);
-        // While the tensor cores form O_j, fold in O_{j-1}.
-        if (j > 0) {
-          accumulate(j - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
-          if (!ok) break;
-        }
-        m_of_prev_tile = m_new;
-      }
-      if (ok && n_tiles > 0) accumulate(n_tiles - 1, m_of_prev_tile == -INFINITY ? 0.f : m_of_prev_tile);
-      if (ok && row_valid) {
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = out + (size_t)(qs + r0 + row) * out_stride + (size_t)h * D;
-#pragma unroll
-        for (int q8 = 0; q8 < D / 8; ++q8) {
-          const uint4 packed = make_uint4(pack_bf16(acc[q8 * 8] * inv, acc[q8 * 8 + 1] * inv),
-                                          pack_bf16(acc[q8 * 8 + 2] * inv, acc[q8 * 8 + 3] * inv),
-                                          pack_bf16(acc[q8 * 8 + 4] * inv, acc[q8 * 8 + 5] * inv),
-                                          pack_bf16(acc[q8 * 8 + 6] * inv, acc[q8 * 8 + 7] * inv));
-          if ((((uintptr_t)dst) & 15) == 0) {
-            reinterpret_cast<uint4*>(dst)[q8] = packed;
-          } else {
-            const __nv_bfloat16* hp = reinterpret_cast<const __nv_bfloat16*>(&packed);
-            for (int e = 0; e < 8; ++e) dst[q8 * 8 + e] = hp[e];
           }
         }
       }
