@@ -15,8 +15,9 @@
 // tile j, and one O of D columns that accumulates over all tiles.  P overwrites the scores it came
 // from (the next scores for that buffer are issued after the product that reads P).  A row's O is
 // rescaled in place only when its maximum has grown by more than a factor of 256 since the reference
-// it is held against, and divided by the sum at the end.  (For heads of 64 an accumulator in
-// registers, rescaled every tile from two O buffers, was measured 10 % slower.)
+// it is held against, and divided by the sum at the end.  (Measured slower: for heads of 64 an
+// accumulator in registers, rescaled every tile from two O buffers, by 10 %; two CTAs per SM with one
+// S buffer each, by 70 % at 2,048 tokens and 6 % at 8,192.)
 // Formulas as the reference's tensor-core prefill attention
 // (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124, 1295-1452): scores scaled by 1/sqrt(d)
 // (folded into the exp2 argument), key <= query, p rounded to T before PV, o = acc / sum.
@@ -485,6 +486,15 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         }
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         tmem_st_wait();
+        // The product of the tile before is awaited in every tile, before this warp's arrival lets
+        // the product of this tile be issued: a parity names a phase only among the current one and
+        // the one before, and at this point the barrier can only be in phase j - 1 or j.  (It has
+        // long completed: that product ran beside this tile's softmax.)
+        if (j > 0) {
+          ok = mbar_wait(&bar->o_full, (j - 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
         tc_fence_before();  // the loads of S and the stores of P (and of O) are ordered before the arrivals
         __syncwarp();
         if (lane == 0) {
@@ -492,13 +502,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
           mbar_arrive(&bar->p_full[sb]);   // issued after the product that reads P from it
         }
       }
-      // The last product.  A parity names a phase only among the current one and the one before:
-      // the scores of the last tile prove the product of tile n - 3 done, no more (they were issued
-      // before the product of tile n - 2), so that one is awaited first.
-      if (ok && n_tiles > 1) {
-        ok = mbar_wait(&bar->o_full, (n_tiles - 2) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-      }
+      // The last product: the barrier is in phase n - 1 or has completed it.
       if (ok && n_tiles > 0) {
         ok = mbar_wait(&bar->o_full, (n_tiles - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
