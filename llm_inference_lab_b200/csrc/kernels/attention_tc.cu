@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
 
 // ----------------------------------------------------------------------------------------
 // Decode: one CTA per (split of the keys, kv head x tile of 16 query heads of its group,
-// request with exactly one new token).  Each of the 4 warps streams its own 32-key tiles
+// request with exactly one new token).  Each warp streams its own tiles of keys
 // through a private ring of shared-memory stages; the warps' softmax states are merged at
 // the end.  With several splits the CTA leaves (acc, max, sum) in scratch for the merge kernel.
 // ----------------------------------------------------------------------------------------
@@ -328,7 +328,18 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-constexpr int DC_BN = 32, DC_THREADS = 128, DC_WARPS = 4;
+// A warp's instructions depend on one another (ldmatrix, mma, shuffles, exp2, mma), so a tile takes
+// a warp microseconds, and what keeps the memory system busy is the number of warps per SM.  Heads
+// of up to 64: 4 warps with tiles of 32 keys, two CTAs per SM.  Larger heads: 12 warps with tiles of
+// 16 keys in one CTA per SM, as many as registers and shared memory hold (measured at heads of 128,
+// 32 requests of 4,096 keys, 4 kv heads: 47 us, 5.7 TB/s, against 67 us with 4 warps and tiles of 32).
+#ifndef LAB_DC_BN
+#define LAB_DC_BN (LAB_HEAD_DIM > 64 ? 16 : 32)
+#endif
+#ifndef LAB_DC_WARPS
+#define LAB_DC_WARPS (LAB_HEAD_DIM > 64 ? 12 : 4)
+#endif
+constexpr int DC_BN = LAB_DC_BN, DC_WARPS = LAB_DC_WARPS, DC_THREADS = 32 * DC_WARPS;
 constexpr int DC_TILE_BYTES = DC_BN * ROW_BYTES;
 constexpr int DC_MERGE_BYTES = DC_WARPS * 16 * (D + 2) * 4;
 constexpr int DC_MAX_CLUSTER = 8;  // the portable cluster size
@@ -336,8 +347,8 @@ constexpr int DC_MAX_CLUSTER = 8;  // the portable cluster size
 // shares together are at most 16 * D floats, rounded up per split) and 16 (max, sum) pairs.  The
 // area lies outside the rings, because a peer may write here while this CTA still reads its tiles.
 constexpr int DC_RECV_BYTES = ((16 * D + DC_MAX_CLUSTER * 33 + 8) * 4 + 15) / 16 * 16;
-// Shared memory of a decode CTA.  In a cluster a warp meets two tiles at most (128 keys per CTA and
-// split), so two stages do; the footprint matters: beyond about 100 KB the CTAs of consecutive
+// Shared memory of a decode CTA.  In a cluster a warp meets two tiles at most (one or two rounds of
+// the warps per CTA and split), so two stages do; the footprint matters: beyond about 100 KB the CTAs of consecutive
 // launches no longer share SMs, and a launch of 128 CTAs measured 8.6 us instead of 5.5.
 template <bool CLUSTER>
 struct DcLayout {
@@ -718,6 +729,10 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, int out_
 }  // namespace
 
 LAB_EXPORT int lab_attention_head_dim() { return D; }
+// What the caller needs to choose the splits: the keys a decode CTA takes in one round of its warps,
+// and how many decode CTAs an SM holds (by shared memory).
+LAB_EXPORT int lab_attention_decode_keys_per_round() { return DC_BN * DC_WARPS; }
+LAB_EXPORT int lab_attention_decode_ctas_per_sm() { return DcLayout<false>::SMEM + 1024 <= 114 * 1024 ? 2 : 1; }
 
 // Scratch the decode kernel needs with `splits` > 1: floats for part_acc and part_ml.
 LAB_EXPORT long long lab_attention_decode_scratch_floats(int requests, int n_q, int splits) {

@@ -502,20 +502,35 @@ def attention_tc_supported(head_dim: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 128
 
 
-def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int) -> int:
+def decode_shape(head_dim: int) -> tuple[int, int]:
+    """(keys a decode CTA takes in one round of its warps, decode CTAs an SM holds) of the kernel
+    built for this head size."""
+    shape = _decode_shapes.get(head_dim)
+    if shape is None:
+        L = lib("attention_tc", {"LAB_HEAD_DIM": head_dim})
+        shape = _decode_shapes[head_dim] = (int(L.lab_attention_decode_keys_per_round()),
+                                            int(L.lab_attention_decode_ctas_per_sm()))
+    return shape
+
+
+_decode_shapes: dict[int, tuple[int, int]] = {}
+
+
+def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int, keys_per_round: int = 128,
+                  ctas_per_sm: int = 2) -> int:
     """How many ways the keys of a decoding request are split across CTAs.  A warp needs about
-    two microseconds per 32-key tile (its instructions depend on one another), so for latency a
-    CTA's four warps should get one tile each: 128 keys per CTA while all CTAs of the launch find
-    room at once and the splits (8 at most) can merge inside their cluster; else two tiles each,
-    256 keys per CTA, as far as the GPU has room for the CTAs (the reference splits 1..16 ways,
-    rust/engine/src/runner/model/qwen2/engine.rs:1597-1617)."""
+    two microseconds per tile (its instructions depend on one another), so for latency a
+    CTA's warps should get one tile each: one round (128 keys at heads of 64) per CTA while all
+    CTAs of the launch find room at once and the splits (8 at most) can merge inside their cluster;
+    else two rounds per CTA, as far as the GPU has room for the CTAs (the reference splits 1..16
+    ways, rust/engine/src/runner/model/qwen2/engine.rs:1597-1617)."""
     ctas = max(1, n_decode * n_kv * (-(-group // 16)))
-    if CLUSTER_MERGE and max_kv_len <= 8 * 256:       # beyond that, more than 8 splits serve better
-        fine = min(8, -(-max_kv_len // 128), SM_COUNT // ctas)
+    if CLUSTER_MERGE and max_kv_len <= 16 * keys_per_round:     # beyond that, more than 8 splits serve better
+        fine = min(8, -(-max_kv_len // keys_per_round), SM_COUNT // ctas)
         if fine >= 2:
             return int(fine)
-    room = max(1, (2 * SM_COUNT) // ctas)      # two CTAs fit an SM: no second round of CTAs
-    return int(max(1, min(room, -(-max_kv_len // 256), 32)))
+    room = max(1, (ctas_per_sm * SM_COUNT) // ctas)      # no second round of CTAs
+    return int(max(1, min(room, -(-max_kv_len // (2 * keys_per_round)), 32)))
 
 
 def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requests, q_lens, max_kv_len,
@@ -551,7 +566,7 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     if n_decode:
         if splits is None:
             span = min(max_kv_len, window) if window else max_kv_len
-            splits = decode_splits(n_decode, n_kv, n_q // n_kv, span)
+            splits = decode_splits(n_decode, n_kv, n_q // n_kv, span, *decode_shape(head_dim))
         ctas = n_decode * n_kv * (-(-(n_q // n_kv) // 16)) * splits
         in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and ctas <= SM_COUNT
         if splits > 1 and not in_cluster:
@@ -608,7 +623,7 @@ def attention_decode_fused(qkv, bias, inv_freq, rotary_dim, slots, cache_k, cach
         out = torch.empty((tokens, n_q * head_dim), dtype=torch.bfloat16, device=qkv.device)
     if splits is None:
         span = min(max_kv_len, window) if window else max_kv_len
-        splits = decode_splits(n_requests, n_kv, n_q // n_kv, span)
+        splits = decode_splits(n_requests, n_kv, n_q // n_kv, span, *decode_shape(head_dim))
     scratch = counters = None
     in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and n_requests * n_kv * splits <= SM_COUNT
     if splits > 1 and not in_cluster:
