@@ -408,9 +408,6 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
-PAIR_GEMM_TOKENS = 4096     # from this many tokens on, products with K >= 2048 run on pairs of SMs
-
-
 def _pick_bm(T: int, n_out: int, gated: bool, swap: bool, bn: int) -> int:
     """Rows of the M-side tile.  Tiles of 64 rows (swapped orientation, bn <= 64) double the CTAs of
     a decode step's products, but measured slower at the benchmark's sizes (a step of 0.85 ms
@@ -430,22 +427,31 @@ def _pick_splits(T: int, n_out: int, K: int) -> int:
     return max(1, min(-(-k_tiles // 4), SM_COUNT // tiles, 16))   # about 4 k-tiles per CTA (measured best)
 
 
-def _pick_prefill_tiles(T: int, n_out: int, K: int, allow_partial: bool) -> tuple[int, int]:
-    """(N tile, K splits) of a product with many tokens (tokens on the 128-row side).  A CTA fills
-    shared memory from L2 at a fixed rate, so wide tiles (256) do more arithmetic per byte; they
-    are taken when they still give every SM work, if need be by splitting K (measured at
-    [2048 x 4864] x [4864 x 896]: 28 us with 128-wide tiles, 23 us with 256-wide tiles and two
-    K splits; at 8,192 tokens 95 against 71 us)."""
-    m_tiles = -(-T // 128)
-    t256 = m_tiles * (-(-n_out // 256))
-    if t256 >= 1.4 * SM_COUNT:
-        return 256, 1
-    if allow_partial:
-        k_tiles = -(-K // 64)
-        splits = min(SM_COUNT // max(t256, 1), k_tiles // 16)
-        if splits >= 2:
-            return 256, splits
-    return 128, 1
+def _pick_prefill_tiles(T: int, n_out: int, K: int, allow_partial: bool) -> tuple[str, int, int]:
+    """(kernel, N tile, K splits) of a product with many tokens (tokens on the 128-row side);
+    kernel is "pair" (two CTAs per 256 x 256 tile) or "tc".  Measured on the down and output
+    projections of the 0.5B, 1.5B and 7B layer sizes at 256 to 4,096 tokens, together with the
+    norm that sums the partial products:
+    * a CTA fills shared memory from L2 at a limited rate, so tiles with more arithmetic per byte
+      run closer to the tensor cores' pace: 128 x 128 tiles take about 420 cycles per 64 elements
+      of K, 128 x 256 tiles 600, and a pair's 256 x 256 tile 900;
+    * pairs win once there are enough tiles for most of the 74 pairs of SMs and K is long
+      (down at 2,048 tokens, 1.5B: 61 against 75 us; 7B: 221 against 249 us);
+    * while 128-wide tiles fill at most one wave, they win, with K split so that the wave is
+      full and a split keeps 16 k-tiles or more (down at 2,048 tokens, 0.5B: 28 against 34 us
+      for 256-wide tiles and two splits; at 512 tokens 15 against 21 us);
+    * beyond one wave, the width whose waves cost less."""
+    m_tiles, k_tiles = -(-T // 128), -(-K // 64)
+    pairs = -(-T // 256) * (-(-n_out // 256))
+    if k_tiles >= 32 and pairs >= 48:
+        return "pair", 256, 1
+    t128, t256 = m_tiles * (-(-n_out // 128)), m_tiles * (-(-n_out // 256))
+    if t128 <= SM_COUNT:
+        splits = max(1, min(SM_COUNT // t128, k_tiles // 16)) if allow_partial else 1
+        return "tc", 128, splits
+    if -(-t256 // SM_COUNT) * 600 < -(-t128 // SM_COUNT) * 420:
+        return "tc", 256, 1
+    return "tc", 128, 1
 
 
 def _tc_operands(x, w) -> bool:
@@ -462,14 +468,11 @@ def linear(x, w, bias=None, out_f32=False, allow_partial=False):
     if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w):
         return gemm_plain(x, w, bias, out_f32=out_f32)
     T = x.shape[0]
-    if T >= PAIR_GEMM_TOKENS and x.shape[1] >= 2048:
-        # long reductions over many tokens: pairs of SMs, each CTA loading half of the weight tile
-        # (measured at [T x 4864] x [4864 x 896]: 33 against 39 us at 4,096 tokens, 63 against 71 us
-        # at 8,192; at 2,048 tokens and for the other products of a layer the single-CTA kernel is
-        # as fast or faster)
-        return gemm_tc2(x, w, bias, out_f32=out_f32)
     if T > 128:
-        bn, splits = _pick_prefill_tiles(T, w.shape[0], x.shape[1], allow_partial and bias is None and not out_f32)
+        kind, bn, splits = _pick_prefill_tiles(T, w.shape[0], x.shape[1],
+                                               allow_partial and bias is None and not out_f32)
+        if kind == "pair":
+            return gemm_tc2(x, w, bias, out_f32=out_f32)
         if splits > 1:
             return gemm_tc(x, w, None, swap=False, bn=bn, splits=splits)
         return gemm_tc(x, w, bias, out_f32=out_f32, swap=False, bn=bn)
