@@ -486,6 +486,12 @@ def linear_gated(x, w_gate_up):
     """silu(x @ wg.T) * (x @ wu.T) with w_gate_up = [wg; wu]."""
     if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w_gate_up):
         return gemm_plain(x, w_gate_up, None, gated=True)
+    # Pairs of SMs (256 tokens x 128 features per tile, gate rows in one CTA and up rows in the other)
+    # once their tiles fill most of the 74 pairs: measured 6 to 12 % faster from there on at the 0.5B,
+    # 1.5B and 7B layer sizes (2,048 tokens: 31.7 against 33.7, 76 against 85, 349 against 385 us).
+    T, inter = x.shape[0], w_gate_up.shape[0] // 2
+    if -(-T // 256) * (-(-inter // 128)) >= 64:
+        return gemm_tc2(x, w_gate_up, None, gated=True)
     return gemm_tc(x, w_gate_up, None, gated=True)
 
 
