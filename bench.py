@@ -34,6 +34,15 @@ QWEN25_05B = dict(
     intermediate_size=4864, num_hidden_layers=24, num_attention_heads=14, num_key_value_heads=2,
     rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=4096, hidden_act="silu",
     tie_word_embeddings=True, use_sliding_window=False, eos_token_id=151645)
+# Further sizes of the same architecture (--shape), for measurements beyond the headline configuration.
+SHAPES = {
+    "0.5B": QWEN25_05B,
+    "1.5B": dict(QWEN25_05B, hidden_size=1536, intermediate_size=8960, num_hidden_layers=28, num_attention_heads=12,
+                 num_key_value_heads=2, max_position_embeddings=8192),
+    "7B": dict(QWEN25_05B, vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+               num_attention_heads=28, num_key_value_heads=4, max_position_embeddings=16384,
+               tie_word_embeddings=False),
+}
 PROMPT_LEN, NEW_TOKENS, PREFILL_TOKENS, PAGE_SIZE = 512, 256, 2048, 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -98,7 +107,7 @@ def model_folder(cfg_dict, layers):
     from llm_inference_lab_b200.weights import write_random_model
 
     cfg_dict = dict(cfg_dict, num_hidden_layers=layers)
-    folder = os.path.join(tempfile.gettempdir(), f"lab_b200_bench_qwen2_L{layers}_{os.getuid()}")
+    folder = os.path.join(tempfile.gettempdir(), f"lab_b200_bench_qwen2_H{cfg_dict['hidden_size']}_L{layers}_{os.getuid()}")
     marker = os.path.join(folder, ".complete")
     if not os.path.exists(marker):
         cfg = resolve(cfg_dict).config_class.from_dict(cfg_dict)
@@ -113,7 +122,7 @@ def decode_bytes(cfg, layers, batch, mean_ctx):
     d = h // cfg["num_attention_heads"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     per_layer = (nq + 2 * nkv) * d * h + (nq + 2 * nkv) * d + nq * d * h + 3 * h * i + 2 * h
-    weights = 2 * (layers * per_layer + v * h + h)
+    weights = 2 * (layers * per_layer + v * h + h)   # the head's matrix once (tied or not, a decode step reads one)
     cache = 2 * batch * mean_ctx * layers * 2 * nkv * d
     return weights + cache
 
@@ -217,13 +226,17 @@ def run_e2e(folder, batch, steps, warmup):
 
 
 def main() -> int:
+    global PROMPT_LEN, PREFILL_TOKENS
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"],
+    ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--shape", default="0.5B", choices=sorted(SHAPES),
+                    help="layer sizes of another model of the architecture (the headline is 0.5B)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens each request holds before decoding")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the prefill")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through LLM.generate")
@@ -241,23 +254,27 @@ def main() -> int:
         return 2
     warmup = max(args.warmup, 3)
     steps = max(1, min(args.steps, NEW_TOKENS - warmup - 2))
+    PROMPT_LEN = args.prompt_len
+    cfg = SHAPES[args.shape]
+    args.layers = args.layers or cfg["num_hidden_layers"]
+    headline = args.shape == "0.5B" and PROMPT_LEN == 512
+    max_seq = max(4096, PROMPT_LEN + NEW_TOKENS + PAGE_SIZE)
+    live = max(64 if headline else 0, args.batch)      # requests that hold pages at the same time
 
     import numpy as np
     import torch
     from llm_inference_lab_b200.engine import Engine
     from llm_inference_lab_b200.engine.decode_graph import DecodeGraphs
 
-    cfg = QWEN25_05B
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()
     rng = np.random.default_rng(0)
-    engine = Engine(folder, "bf16", max_tokens=64 * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + 4096, page_size=PAGE_SIZE,
-                    max_requests=64, max_batch_tokens=8192, max_seq_len=4096)
+    engine = Engine(folder, "bf16", max_tokens=live * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + 4096, page_size=PAGE_SIZE,
+                    max_requests=live, max_batch_tokens=max(8192, PROMPT_LEN), max_seq_len=max_seq)
     graphs = DecodeGraphs(engine)
     engine.enable_step_graphs()   # a prefill of a repeating shape is replayed from a CUDA graph
 
     if args.only_prefill:
-        global PREFILL_TOKENS
         PREFILL_TOKENS = args.only_prefill
         pms = run_prefill(engine, rng, repeats=2)
         print(json.dumps({"prefill_tokens": PREFILL_TOKENS, "ms": round(pms, 4), "layers": args.layers,
@@ -271,18 +288,20 @@ def main() -> int:
     achieved = nbytes / (ms / steps / 1e3) / 1e9
 
     line = {
-        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-0.5B)",
+        "metric": f"decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-{args.shape})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02) seed 0, uniform-random token ids",
         "config": {
-            "model": "Qwen2.5-0.5B shape", "global_batch": args.batch, "seq_len": 4096, "parallelism": "single-gpu",
+            "model": f"Qwen2.5-{args.shape} shape", "global_batch": args.batch, "seq_len": max_seq,
+            "parallelism": "single-gpu",
             "layers": args.layers, "layers_of_config": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
-            "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_embeddings": True,
+            "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_embeddings": cfg["tie_word_embeddings"],
             "prompt_len": PROMPT_LEN, "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE,
-            "decode": "cuda-graph, device feedback", "l2": "inputs larger than L2 (1 GB of weights per step)",
+            "decode": "cuda-graph, device feedback",
+            "l2": f"inputs larger than L2 ({nbytes / 1e9:.1f} GB of weights and cache per step)",
             "peaks": pk_src},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
@@ -295,14 +314,14 @@ def main() -> int:
         line["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS,
                            "ms": round(pms, 4), "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
         points = {}
-        for b in (1, 64):
+        for b in ((1, 64) if headline else ()):
             k = min(steps, 100)
             bms, _, _ = run_decode(engine, graphs, b, k, warmup, rng)
             points[f"decode_b{b}"] = round(b * k / (bms / 1e3), 1)
         line["points"] = points
     del graphs, engine
     torch.cuda.empty_cache()
-    if not args.skip_e2e:
+    if not args.skip_e2e and headline:
         try:
             line["e2e"] = {k: (round(v, 1) if isinstance(v, float) else v)
                            for k, v in run_e2e(folder, args.batch, steps, warmup).items()}
