@@ -4,8 +4,9 @@
 //   gated:      out[t, n] = T( silu(g) * u ),  g = x . w[n], u = x . w[inter + n]   (32-bit, one rounding)
 //   split-K:    partial[z, t, n] = sum over the z-th slice of k   (32-bit, summed by the consumer)
 //
-// A cluster of two CTAs works on one tile of 256 tokens x 256 accumulator columns.  Each CTA
-// loads its own 128 token rows (A) and only HALF of the weight tile (128 of the 256 rows of B);
+// A cluster of two CTAs works on one tile of 256 tokens x BN accumulator columns (256, or 224 or
+// 192 where that fills the rounds of the pairs better).  Each CTA
+// loads its own 128 token rows (A) and only HALF of the weight tile (BN / 2 of the BN rows of B);
 // one MMA of M = 256, issued by the leader CTA, reads A from both CTAs' shared memory and each
 // half of B from the CTA that holds it, and leaves each CTA the accumulator rows of its own
 // tokens in its own tensor memory.  A CTA therefore fills 32 KB of shared memory per k-tile
@@ -31,18 +32,28 @@
 namespace {
 
 constexpr int BM = 128;   // token rows per CTA (the pair's MMA has M = 256)
-constexpr int BN = 256;   // accumulator columns of a tile; each CTA loads BN / 2 weight rows
 constexpr int BK = 64;    // bf16 elements per k-tile: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = (BN / 2) * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 6;
 constexpr int ACC_BUFS = 2;
-constexpr int TMEM_COLS = ACC_BUFS * BN;
-constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
-static_assert(TMEM_COLS == 512, "two accumulators fill tensor memory");
+constexpr int ACC_STRIDE = 256;                   // columns of tensor memory between the two accumulators
+constexpr int TMEM_COLS = ACC_BUFS * ACC_STRIDE;  // two accumulators fill tensor memory
+// BN: accumulator columns of a tile (256, 224 or 192); each CTA loads BN / 2 weight rows.  The host
+// takes the width whose tiles fill the rounds of the pairs best: 608 half-tiles of gate/up at 2,048
+// tokens are 4.1 rounds of 74 pairs at 256 columns and 4.8 rounds of shorter tiles at 224.
+template <int BN>
+struct Tile {
+  static_assert(BN % 32 == 0 && BN <= ACC_STRIDE && BN >= 64, "N of an M = 256 MMA, halves in whole swizzle groups");
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 192 * 1024 / STAGE_BYTES > 8 ? 8 : 192 * 1024 / STAGE_BYTES;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  // Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 256 over the pair, N = BN.
+  static constexpr uint32_t IDESC =
+      (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  static_assert((2 * STAGES + 2 * ACC_BUFS) * 8 + 8 <= 512, "the barriers outgrow their 512 bytes");
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -146,8 +157,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;                  // layout: 128-byte swizzle
   return d;
 }
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 256 over the pair, N = BN.
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
 // 32 consecutive accumulator columns of this thread's lane; the registers are valid after tmem_wait().
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
@@ -180,9 +189,11 @@ struct Params {
   int m_tiles, n_tiles, splits;  // tiles of 256 tokens, tiles of output features, split-K planes
 };
 
-template <bool GATED, typename OutT>
+template <bool GATED, typename OutT, int BN>
 __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_b, Params p) {
+  constexpr int STAGES = Tile<BN>::STAGES, STAGE_BYTES = Tile<BN>::STAGE_BYTES;
+  constexpr uint32_t IDESC = Tile<BN>::IDESC;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(tiles + STAGES * STAGE_BYTES);  // used in the leader only
@@ -280,7 +291,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         ok = wait_all(&acc_empty[buf], (use & 1) ^ 1);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t acc_addr = tmem_base + buf * BN;
+        const uint32_t acc_addr = tmem_base + buf * ACC_STRIDE;
         for (int i = 0; i < n_kt; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -310,7 +321,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       const uint32_t use = (uint32_t)(local / ACC_BUFS);
       const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag);
       tc_fence_after();
-      const uint32_t lane_addr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t lane_addr = tmem_base + buf * ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
       const int m = m0 + (int)rank * BM + quarter * 32 + lane;  // this thread's token row
       const bool partial = p.split_stride != 0;
       const bool go = __all_sync(0xffffffffu, ok && !*abort_flag);
@@ -322,8 +333,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[buf]), 0));
       };
+      // 32 columns at a time; the last chunk of a tile whose width is no multiple of 32 reads on into
+      // columns that belong to nothing (they lie inside the accumulator's 256) and stores only its own.
+      constexpr int CHUNKS = (OUT_COLS + 31) / 32;
+      const int n_end = min(p.n_out, n0 + OUT_COLS);
 #pragma unroll 1
-      for (int c = 0; c < OUT_COLS / 32 && go; ++c) {
+      for (int c = 0; c < CHUNKS && go; ++c) {
         uint32_t r[32];
         float v[32];
         if (n_kt > 0) {
@@ -343,48 +358,50 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
-        if (c == OUT_COLS / 32 - 1) release();
+        if (c == CHUNKS - 1) release();
         const int n = n0 + c * 32;
-        if (m >= p.tokens || n >= p.n_out) continue;
+        if (m >= p.tokens || n >= n_end) continue;
         if (partial) {
           float* dst = (float*)p.out + split * p.split_stride + (size_t)m * p.ld_out + n;
-          if (n + 32 <= p.n_out && (((uintptr_t)dst) & 15) == 0) {
+          const bool aligned = (((uintptr_t)dst) & 15) == 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < 8; ++j) {
+            if (aligned && n + 4 * j + 4 <= n_end) {
               reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n + j < p.n_out) dst[j] = v[j];
+              for (int e = 0; e < 4; ++e)
+                if (n + 4 * j + e < n_end) dst[4 * j + e] = v[4 * j + e];
+            }
           }
         } else {
           if (p.bias) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n + j < p.n_out) v[j] += __bfloat162float(p.bias[n + j]);
+              if (n + j < n_end) v[j] += __bfloat162float(p.bias[n + j]);
           }
           OutT* dst = (OutT*)p.out + (size_t)m * p.ld_out + n;
-          if (n + 32 <= p.n_out && (((uintptr_t)dst) & 15) == 0) {
-            if (sizeof(OutT) == 2) {
+          const bool aligned = (((uintptr_t)dst) & 15) == 0;
+          constexpr int PER = 16 / (int)sizeof(OutT);   // elements of a 16-byte store
 #pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
+          for (int g = 0; g < 32 / PER; ++g) {
+            if (aligned && n + g * PER + PER <= n_end) {
+              if constexpr (sizeof(OutT) == 2) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(v[q4 * 8 + 2 * e], v[q4 * 8 + 2 * e + 1]);
+                  __nv_bfloat162 h = __floats2bfloat162_rn(v[g * 8 + 2 * e], v[g * 8 + 2 * e + 1]);
                   w[e] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                reinterpret_cast<uint4*>(dst)[q4] = make_uint4(w[0], w[1], w[2], w[3]);
+                reinterpret_cast<uint4*>(dst)[g] = make_uint4(w[0], w[1], w[2], w[3]);
+              } else {
+                reinterpret_cast<float4*>(dst)[g] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              for (int e = 0; e < PER; ++e)
+                if (n + g * PER + e < n_end) dst[g * PER + e] = from_f32<OutT>(v[g * PER + e]);
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n + j < p.n_out) dst[j] = from_f32<OutT>(v[j]);
           }
         }
       }
@@ -419,13 +436,13 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Map of a row-major bf16 matrix [rows, K] with row stride ld (elements); box = [64, 128 rows].
-int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld) {
+// Map of a row-major bf16 matrix [rows, K] with row stride ld (elements); box = [64, box_rows].
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return (int)cudaErrorNotSupported;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -433,10 +450,11 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld) {
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <bool GATED, typename OutT>
+template <bool GATED, typename OutT, int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, long long tiles, cudaStream_t stream) {
+  constexpr int SMEM = Tile<BN>::SMEM;
   static int max_pairs = 0;  // clusters of two CTAs that the device holds at once
-  auto kern = gemm_tc2_kernel<GATED, OutT>;
+  auto kern = gemm_tc2_kernel<GATED, OutT, BN>;
   if (max_pairs == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -475,23 +493,66 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, long l
   return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
 }
 
+template <bool GATED, typename OutT>
+int launch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, long long tiles, cudaStream_t s) {
+  switch (bn) {
+    case 256: return launch<GATED, OutT, 256>(ma, mb, p, tiles, s);
+    case 224: return launch<GATED, OutT, 224>(ma, mb, p, tiles, s);
+    case 192: return launch<GATED, OutT, 192>(ma, mb, p, tiles, s);
+  }
+  return (int)cudaErrorInvalidValue;
+}
+
+// The tile width whose rounds over the pairs of SMs cost least, the wider on a tie.  A round of
+// narrower tiles is shorter, but less than in proportion (measured per round against 256 columns:
+// 224 columns 0.89 with a long K and no gain in the gated product, whose tiles have few k-tiles and
+// an epilogue as long as their MMAs; 192 columns 0.84), so a narrower tile pays where it saves a
+// round, fits the output's width or gives more pairs a tile.
+int pick_bn(int tokens, int n_out, bool gated, int splits) {
+  static int pairs = 0;
+  if (pairs == 0) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2)
+      sms = 148;
+    pairs = sms / 2;
+  }
+  const long long m_tiles = (tokens + 2 * BM - 1) / (2 * BM);
+  int best = 256;
+  long long best_cost = -1;
+  for (int bn : {256, 224, 192}) {
+    const int out_cols = gated ? bn / 2 : bn;
+    const long long tiles = m_tiles * ((n_out + out_cols - 1) / out_cols) * splits;
+    const int round_cost = bn == 256 ? 256 : (bn == 224 ? (gated ? 256 : 240) : (gated ? 215 : 210));
+    const long long cost = ((tiles + pairs - 1) / pairs) * round_cost;
+    if (best_cost < 0 || cost < best_cost) {
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
 }  // namespace
 
 // x: [tokens, K] bf16 (row stride ldx), w: [n_out (x2 when gated), K] bf16 contiguous.
 // out: bf16 or f32 [tokens, ld_out]; with splits > 1, `out` is the partial buffer
 // [splits, tokens, ld_out] of floats (no bias, not gated).
+// bn: accumulator columns of a tile, 256, 224 or 192; 0: the width that fills the rounds of the pairs best.
 LAB_EXPORT int lab_gemm_tc2(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
-                            int ldx, int ld_out, int gated, int out_f32, int splits, cudaStream_t stream) {
+                            int ldx, int ld_out, int gated, int out_f32, int splits, int bn, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA
   if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return (int)cudaErrorInvalidValue;  // 16-byte bases for TMA
   if (splits < 1 || (splits > 1 && (gated || !out_f32 || bias))) return (int)cudaErrorInvalidValue;
   if (gated && (out_f32 || bias)) return (int)cudaErrorInvalidValue;
+  if (bn == 0) bn = pick_bn(tokens, n_out, gated != 0, splits);
+  if (bn != 256 && bn != 224 && bn != 192) return (int)cudaErrorInvalidValue;
   const int w_rows = gated ? 2 * n_out : n_out;
   CUtensorMap ma, mb;
   int rc;
-  if ((rc = make_map(&ma, x, tokens, K, ldx))) return rc;
-  if ((rc = make_map(&mb, w, w_rows, K, K))) return rc;
+  if ((rc = make_map(&ma, x, tokens, K, ldx, BM))) return rc;
+  if ((rc = make_map(&mb, w, w_rows, K, K, bn / 2))) return rc;
   Params p;
   p.out = out;
   p.bias = (const __nv_bfloat16*)bias;
@@ -502,12 +563,12 @@ LAB_EXPORT int lab_gemm_tc2(void* out, const void* x, const void* w, const void*
   p.k_tiles_per_split = (p.k_tiles + splits - 1) / splits;
   p.split_stride = splits > 1 ? (long long)tokens * ld_out : 0;
   p.up_offset = n_out;
-  const int out_cols = gated ? BN / 2 : BN;
+  const int out_cols = gated ? bn / 2 : bn;
   p.m_tiles = (tokens + 2 * BM - 1) / (2 * BM);
   p.n_tiles = (n_out + out_cols - 1) / out_cols;
   p.splits = splits;
   const long long tiles = (long long)p.m_tiles * p.n_tiles * splits;
-  if (gated) return launch<true, __nv_bfloat16>(ma, mb, p, tiles, stream);
-  if (out_f32) return launch<false, float>(ma, mb, p, tiles, stream);
-  return launch<false, __nv_bfloat16>(ma, mb, p, tiles, stream);
+  if (gated) return launch_bn<true, __nv_bfloat16>(bn, ma, mb, p, tiles, stream);
+  if (out_f32) return launch_bn<false, float>(bn, ma, mb, p, tiles, stream);
+  return launch_bn<false, __nv_bfloat16>(bn, ma, mb, p, tiles, stream);
 }

@@ -377,10 +377,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
 
 
 def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
-             out_f32: bool = False, splits: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
+             out_f32: bool = False, splits: int = 1, out: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
     """out = x @ w.T (+ bias) on pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 tokens by 256
     accumulator columns, each CTA of a pair loading half of the weight tile.  For steps with many
-    tokens; `splits` > 1 returns 32-bit partial products [splits, tokens, out]."""
+    tokens; `splits` > 1 returns 32-bit partial products [splits, tokens, out].  `bn`: accumulator
+    columns of a tile (256, 224 or 192; 0: the width whose tiles fill the rounds of the pairs best)."""
     _on_gpu(x, w, bias, out)
     T, K = x.shape
     n_out = w.shape[0] // 2 if gated else w.shape[0]
@@ -404,7 +405,7 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         assert out.dtype == odt and out.stride(1) == 1
         ld_out, f32 = out.stride(0), out_f32
     _check(lib("gemm_tc2").lab_gemm_tc2(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                        int(gated), int(f32), splits, _stream()), "gemm_tc2")
+                                        int(gated), int(f32), splits, bn, _stream()), "gemm_tc2")
     return out
 
 

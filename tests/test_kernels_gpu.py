@@ -256,16 +256,18 @@ def test_gemm_tc_swapped_tile_rows(bm, T, N, K, gated, bias, bn, splits):
     (700, 130, 1000, False, False, 5), (3000, 1152, 72, False, True, 1), (1, 8, 8, False, False, 1),
     (4500, 896, 4864, False, False, 1),
 ])
-def test_gemm_tc2_exact(T, N, K, gated, bias, splits):
+@pytest.mark.parametrize("bn", [0, 256, 224, 192])
+def test_gemm_tc2_exact(T, N, K, gated, bias, splits, bn):
     """The product on pairs of SMs (tcgen05.mma.cta_group::2) with exactly representable inputs: equal
     to the 64-bit product; ragged token counts and feature counts, several tiles per pair, split K,
-    the gated epilogue (gate rows in one CTA of the pair, up rows in the other)."""
+    the gated epilogue (gate rows in one CTA of the pair, up rows in the other), every tile width
+    (widths whose gated half is no multiple of 32 end in a partial chunk of columns)."""
     g = torch.Generator().manual_seed(26)
     x = (torch.randint(-4, 5, (T, K), generator=g).float() / 4).bfloat16()
     w = (torch.randint(-4, 5, (N * (2 if gated else 1), K), generator=g).float() / 8).bfloat16()
     b = (torch.randint(-8, 9, (N,), generator=g).float() / 2).bfloat16() if bias else None
     out = ops().gemm_tc2(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), gated=gated,
-                         out_f32=not gated, splits=splits)
+                         out_f32=not gated, splits=splits, bn=bn)
     ops().take_device_errors()
     ref = x.double() @ w.double().T
     if splits > 1:
