@@ -247,7 +247,7 @@ def main() -> int:
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "pochenai/llm-inference-lab is a Rust + cuTile engine: no cargo/rustc or cuTile toolchain "
-                          "offline, and pip cannot install it (its pyproject.toml holds no engine)"}))
+                          "offline, and the offline pip install stops at metadata-generation-failed (its pyproject.toml holds no engine)"}))
         return 0
     if args.gpus != 1:
         print(json.dumps({"error": "this engine runs on one GPU; --gpus must be 1", "n_gpus": args.gpus}))
