@@ -159,6 +159,55 @@ def trace_mixed(sequences, rng, max_live=4, max_portion=9, decode_after=0.6):
     return steps
 
 
+def random_config(rng, layers=None):
+    """A random Qwen2 configuration and page size: head sizes in steps of 16, any number of heads and
+    groups, widths and intermediate sizes that are multiples of 8 or only of 2, any vocabulary,
+    sometimes a window on the later layers."""
+    head_dim = int(rng.choice([16, 32, 48, 64, 64, 80, 96, 112, 128, 128]))
+    n_kv = int(rng.choice([1, 2, 3, 4]))
+    n_heads = n_kv * int(rng.choice([1, 2, 3, 4, 7, 8]))
+    n_layers = int(rng.integers(1, 4)) if layers is None else layers
+    cfg = dict(
+        architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=int(rng.integers(40, 3000)),
+        hidden_size=int(rng.choice([8, 8, 8, 2])) * int(rng.integers(4, 40)),
+        intermediate_size=int(rng.choice([8, 8, 16, 2])) * int(rng.integers(4, 60)),
+        num_hidden_layers=n_layers, num_attention_heads=n_heads, num_key_value_heads=n_kv, head_dim=head_dim,
+        rms_norm_eps=float(rng.choice([1e-6, 1e-5, 3e-6])), rope_theta=float(rng.choice([1e4, 1e6, 5e4])),
+        max_position_embeddings=int(rng.choice([96, 200, 400, 700])), hidden_act="silu",
+        tie_word_embeddings=bool(rng.random() < 0.5), use_sliding_window=bool(rng.random() < 0.25), eos_token_id=None)
+    if cfg["use_sliding_window"]:
+        cfg.update(sliding_window=int(rng.integers(3, 150)), max_window_layers=int(rng.integers(0, n_layers)))
+    return cfg, int(rng.choice([16, 16, 16, 4, 8, 32, 64]))
+
+
+def trace_random(sequences, rng, max_live=4, sizes=(1, 1, 1, 2, 3, 7, 16, 40, 65, 130, 300)):
+    """Requests start in random order and at random times; every step takes a portion of random size
+    (single tokens, a few, or hundreds) from most of the live ones."""
+    waiting = list(sequences)
+    rng.shuffle(waiting)
+    at = {name: 0 for name in waiting}
+    live, steps = [], []
+    while live or waiting:
+        while waiting and len(live) < max_live and rng.random() < 0.7:
+            live.append(waiting.pop())
+        if not live:
+            live.append(waiting.pop())
+        entries, end = [], []
+        for name in list(live):
+            if rng.random() < 0.2 and len(live) > 1:
+                continue
+            size = int(min(len(sequences[name]) - at[name], rng.choice(list(sizes))))
+            entries.append({"id": name, "tokens": sequences[name][at[name]: at[name] + size],
+                            "want": list(range(size))})
+            at[name] += size
+            if at[name] == len(sequences[name]):
+                end.append(name)
+                live.remove(name)
+        if entries:
+            steps.append({"step": len(steps), "entries": entries, "end": end})
+    return steps
+
+
 def tokens_needed(steps, page=64):
     """Most tokens live requests hold at any time, each rounded up to a multiple of `page`."""
     held = {}
