@@ -166,7 +166,9 @@ class Engine:
         return [self.cache.free_pages(g) for g in range(self.cache.num_groups)]
 
     # ------------------------------------------------------------------------------------
-    def validate(self, entries: Sequence[Entry]) -> None:
+    def validate(self, entries: Sequence[Entry], reserved: bool = False) -> None:
+        """Refuses a step before anything runs.  With ``reserved`` the cache already counts this
+        step's tokens for every entry."""
         if not entries:
             raise InvalidInput("a step needs at least one entry")
         seen = set()
@@ -179,8 +181,9 @@ class Engine:
             if n == 0:
                 raise InvalidInput(f"request {e.request}: no tokens in this step")
             held = self.cache.reserved(e.request) if self.cache.has(e.request) else 0
-            if held + n > self.max_seq_len:
-                raise InvalidInput(f"request {e.request}: {held + n} tokens exceed the maximum sequence length "
+            after = held if reserved else held + n
+            if after > self.max_seq_len:
+                raise InvalidInput(f"request {e.request}: {after} tokens exceed the maximum sequence length "
                                    f"{self.max_seq_len}")
             lo, hi = min(e.tokens), max(e.tokens)
             if lo < 0 or hi >= self.vocab:
@@ -201,7 +204,7 @@ class Engine:
         With ``reserved`` the caller (the scheduler) has reserved the pages already.
         """
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
-        self.validate(entries)
+        self.validate(entries, reserved)
         opened = []
         taken = []
         try:

@@ -57,6 +57,28 @@ def test_greedy_equals_plain_in_32_bit(tmp_path_factory, name):
     assert llm.engine.cache.live_requests == 0 and llm.engine.free_pages()[0] == llm.engine.num_pages
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_prompt_that_fills_the_maximum_length(tmp_path_factory, graph):
+    """A prompt of most of the model's positions, generated up to the very last one: the step function
+    counts the tokens the scheduler has reserved once, not twice.  One token more is refused."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY["A"]
+    most = cfg["max_position_embeddings"]
+    folder = folder_of(tmp_path_factory, "A", "float32")
+    rng = np.random.default_rng(4)
+    fits = random_tokens(rng, most - 8, cfg["vocab_size"])      # the ninth token is sampled at the last position
+    too_long = random_tokens(rng, most - 7, cfg["vocab_size"])
+    llm = LLM(folder, "f32", page_size=opt["page_size"], kv_tokens=2 * most, max_requests=4, max_batch_tokens=64,
+              cuda_graph=graph)
+    a, b = llm.generate([fits, too_long], SamplingConfig(max_new_tokens=9, ignore_eos=True))
+    pcfg, w = read_model_folder(folder)
+    assert a.finish_reason == "length" and a.tokens == plain_greedy(pcfg, w, fits, 9)
+    assert b.finish_reason == "invalid" and "maximum sequence length" in b.message and b.tokens == []
+    assert llm.engine.cache.live_requests == 0 and llm.engine.free_pages()[0] == llm.engine.num_pages
+
+
 @pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 0.25)])
 def test_mixed_batch_with_temperature(tmp_path_factory, dtype, slack):
     """Configuration B's workload: four requests with prompts of 1/7/33/70 tokens, portions of at

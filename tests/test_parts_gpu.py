@@ -434,3 +434,128 @@ def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
         have = np.concatenate(got[k])
         assert np.abs(have - want[k][: len(have)]).max() < 1e-4, k
     engine.close(0), engine.close(1)
+
+
+# ----------------------------------------------------------------------------------------
+# A run order in which one layer reads the keys and values that another layer cached.
+# ----------------------------------------------------------------------------------------
+
+def define_toy_shared_cache():
+    from llm_inference_lab_b200 import register_architecture
+    from llm_inference_lab_b200.config.base import ModelConfig, optional, positive, required
+    from llm_inference_lab_b200.parts import LayerCall, LayerSpec, ModelBlueprint, PartSpec
+
+    @dataclasses.dataclass
+    class SharedConfig(ModelConfig):
+        architecture = "ToySharedCacheLM"
+        vocab_size: int = required(int, positive)
+        hidden_size: int = required(int, positive)
+        inner_size: int = required(int, positive)
+        heads: int = required(int, positive)
+        kv_heads: int = required(int, positive)
+        head_size: int = required(int, positive)
+        theta: float = optional(float, 10000.0)
+        eps: float = optional(float, 1e-5)
+        max_positions: int = optional(int, 256)
+
+    def blueprint(cfg):
+        layers = []
+        for i in range(3):
+            p = f"blocks.{i}."
+            mixer = PartSpec("gqa_attention", {
+                "hidden": cfg.hidden_size, "n_heads": cfg.heads, "n_kv_heads": cfg.kv_heads,
+                "head_dim": cfg.head_size, "qkv_bias": True, "out_bias": False, "window": 0,
+                "position": PartSpec("rope", {"theta": cfg.theta, "rotary_dim": cfg.head_size})}, prefix=p + "attn.")
+            ffn = PartSpec("gated_mlp", {"hidden": cfg.hidden_size, "intermediate": cfg.inner_size, "act": "silu"},
+                           prefix=p + "ff.")
+            norms = tuple(PartSpec("rmsnorm", {"hidden": cfg.hidden_size, "eps": cfg.eps}, prefix=p + f"n{j}.")
+                          for j in range(2))
+            layers.append(LayerSpec("prenorm", mixer, ffn, norms, hidden=cfg.hidden_size))
+        # Layer 2 forms its own queries but attends over what layer 0 cached; it caches nothing.
+        order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 0, write=False))
+        return ModelBlueprint(
+            hidden=cfg.hidden_size, vocab=cfg.vocab_size,
+            embedding=PartSpec("token_embedding", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size}, prefix="emb."),
+            layers=tuple(layers), order=order,
+            final_norm=PartSpec("rmsnorm", {"hidden": cfg.hidden_size, "eps": cfg.eps}, prefix="out_norm."),
+            head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size, "tied_to": None},
+                          prefix="head."),
+            max_positions=cfg.max_positions)
+
+    register_architecture("ToySharedCacheLM", SharedConfig, blueprint)
+    return SharedConfig
+
+
+def toy_shared_reference(folder, ids):
+    from plain_qwen2 import plain_attention, plain_rope
+    import json
+    cfg = json.load(open(f"{folder}/config.json"))
+    _, w = read_model_folder(folder)
+    n_h, n_kv, d, theta, eps = cfg["heads"], cfg["kv_heads"], cfg["head_size"], cfg["theta"], cfg["eps"]
+    T = len(ids)
+    pos = np.arange(T)
+    x = w["emb.weight"][np.asarray(ids)]
+    cached = {}
+    for layer, cache, write in ((0, 0, True), (1, 1, True), (2, 0, False)):
+        p = f"blocks.{layer}."
+        h = plain_rms_norm(x, w[p + "n0.weight"], eps)
+        q = plain_rope(plain_linear(h, w[p + "attn.q_proj.weight"], w[p + "attn.q_proj.bias"]).reshape(T, n_h, d),
+                       pos, theta)
+        if write:
+            k = plain_rope(plain_linear(h, w[p + "attn.k_proj.weight"], w[p + "attn.k_proj.bias"]).reshape(T, n_kv, d),
+                           pos, theta)
+            v = plain_linear(h, w[p + "attn.v_proj.weight"], w[p + "attn.v_proj.bias"]).reshape(T, n_kv, d)
+            cached[cache] = (k, v)
+        k, v = cached[cache]
+        r = x + plain_linear(plain_attention(q, k, v, pos).reshape(T, n_h * d), w[p + "attn.o_proj.weight"])
+        x = r + plain_gated_mlp(plain_rms_norm(r, w[p + "n1.weight"], eps), w[p + "ff.gate_proj.weight"],
+                                w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+    return plain_linear(plain_rms_norm(x, w["out_norm.weight"], eps), w["head.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_reads_the_cache_another_layer_fills(tmp_path, dtype):
+    """The run order is data: its third call reads cache 0, which the first call fills, and writes
+    nothing.  Whole prompts, portions beside single tokens, and pages used again."""
+    from llm_inference_lab_b200.engine import Engine, Entry
+    from llm_inference_lab_b200.weights import write_random_model
+
+    Config = define_toy_shared_cache()
+    cfg = Config.from_dict(dict(vocab_size=83, hidden_size=48, inner_size=72, heads=4, kv_heads=2, head_size=16))
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = write_random_model(cfg, str(tmp_path / "shared"), seed=11, dtype=tdt, std=0.15)
+    engine = Engine(folder, dtype, max_tokens=128, page_size=8, max_requests=3)
+    assert len(engine.model.cache_plan.needs) == 2 and len(engine.views) == 2, "three calls, two caches"
+    rng = np.random.default_rng(2)
+    seqs = {0: random_tokens(rng, 45, 83), 1: random_tokens(rng, 14, 83), 2: random_tokens(rng, 80, 83)}
+    want = {k: toy_shared_reference(folder, ids) for k, ids in seqs.items()}
+
+    def ok(have, ref, what):
+        have = have.astype(np.float64)
+        if dtype == "float32":
+            assert np.abs(have - ref).max() < 1e-4, what
+        else:
+            assert np.abs(have - ref).max() <= 0.12 * np.abs(ref).max(), what
+
+    got = {0: [], 1: []}
+    at0 = at1 = 0
+    for n0 in [6, 2, 9, 1, 1, 8, 3, 15]:
+        entries = [Entry(0, seqs[0][at0: at0 + n0], list(range(n0)))]
+        if at1 < len(seqs[1]):
+            entries.append(Entry(1, seqs[1][at1: at1 + 1], [0]))
+        logits = engine.step(entries).cpu().numpy()
+        got[0].append(logits[:n0])
+        if len(entries) == 2:
+            got[1].append(logits[n0:])
+            at1 += 1
+        at0 += n0
+    assert at0 == 45
+    for k in (0, 1):
+        have = np.concatenate(got[k])
+        ok(have, want[k][: len(have)], f"request {k} in portions")
+    engine.close(0), engine.close(1)
+    # 80 tokens need 10 of the 16 pages: some of them held request 0's keys a moment ago.
+    whole = engine.step([Entry(2, seqs[2], list(range(80)))]).cpu().numpy()
+    ok(whole, want[2], "whole prompt on pages used again")
+    engine.close(2)
+    assert engine.free_pages() == [engine.num_pages]
