@@ -225,6 +225,45 @@ def run_e2e(folder, batch, steps, warmup):
             "note": "LLM.generate; each step is launched one step ahead of the host's read of the sampled ids"}
 
 
+def run_serve(folder, requests, chunk, new_tokens, max_seq, lo=128, hi=2048):
+    """Continuous batching through LLM.generate: `requests` prompts of lo..hi tokens arrive at once, prompts
+    are cut into portions under a budget of `chunk` tokens a step (decoding requests first), and every
+    request decodes `new_tokens` tokens.  Timed on the host around the whole call, after two untimed
+    runs of the same work (they compile, and capture the graphs the timed run replays)."""
+    import numpy as np
+    import torch
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    rng = np.random.default_rng(2)
+    lengths = [int(n) for n in rng.integers(lo, hi + 1, requests)]
+    need = sum(-(-(n + new_tokens) // PAGE_SIZE) * PAGE_SIZE for n in lengths)
+    llm = LLM(folder, "bf16", max_batch_tokens=chunk, page_size=PAGE_SIZE, kv_tokens=need + 64 * PAGE_SIZE,
+              max_requests=requests, max_seq_len=max_seq, cuda_graph=True)
+    prompts = [[int(t) for t in rng.integers(0, llm.engine.vocab, n)] for n in lengths]
+    sampling = SamplingConfig(max_new_tokens=new_tokens, ignore_eos=True)
+    for _ in range(2):      # the second run captures the step shapes that came twice
+        llm.generate(prompts, sampling)
+    torch.cuda.synchronize()
+    llm.step_log.clear()
+    steps0 = llm.steps
+    t0 = time.perf_counter()
+    results = llm.generate(prompts, sampling)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    assert all(r.finish_reason == "length" and len(r.tokens) == new_tokens for r in results)
+    generated = requests * new_tokens
+    decode_steps = sum(1 for _, _, is_decode in llm.step_log if is_decode)
+    return {"workload": f"continuous batching: {requests} requests at once, prompts of {lo}..{hi} tokens, "
+                        f"{chunk} tokens a step, {new_tokens} new tokens each",
+            "seconds": round(seconds, 4), "prompt_tokens": sum(lengths), "generated_tokens": generated,
+            "total_tokens_per_s": round((sum(lengths) + generated) / seconds, 1),
+            "generated_tokens_per_s": round(generated / seconds, 1),
+            "steps": llm.steps - steps0, "pure_decode_steps": decode_steps,
+            "ttft_ms_median": round(1e3 * statistics.median(r.ttft for r in results), 2),
+            "preemptions": sum(r.preemptions for r in results)}
+
+
 def main() -> int:
     global PROMPT_LEN, PREFILL_TOKENS
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -240,6 +279,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the prefill")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through LLM.generate")
+    ap.add_argument("--serve", type=int, default=0, metavar="REQUESTS",
+                    help="instead of the headline run: REQUESTS prompts of 128..2,048 tokens through LLM.generate "
+                         "with 512 tokens a step and 128 new tokens each (continuous batching); prints its own line")
     ap.add_argument("--only-prefill", type=int, default=0, metavar="TOKENS",
                     help="run only a prefill of TOKENS tokens a few times and print its time (for profiling)")
     args = ap.parse_args()
@@ -268,6 +310,12 @@ def main() -> int:
 
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()
+    if args.serve:
+        out = run_serve(folder, args.serve, 512, 128, max(max_seq, 2048 + 128 + PAGE_SIZE))
+        out.update({"model": f"Qwen2.5-{args.shape} shape", "layers": args.layers,
+                    "layers_of_config": cfg["num_hidden_layers"], "dtype": "bf16"})
+        print(json.dumps(out))
+        return 0
     rng = np.random.default_rng(0)
     engine = Engine(folder, "bf16", max_tokens=live * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + 4096, page_size=PAGE_SIZE,
                     max_requests=live, max_batch_tokens=max(8192, PROMPT_LEN), max_seq_len=max_seq)

@@ -250,8 +250,11 @@ class Engine:
                 ops.COUNTER.launches += cap["launches"]
                 self.graph_replays += 1
                 return cap["logits"]
-            self._seen[sig] = self._seen.get(sig, 0) + 1
-            if self._seen[sig] >= 2:
+            # Captured the second time a shape comes; a shape whose graph was pushed out by newer
+            # ones is captured again only at its 4th, 8th, 16th... coming, so a workload of ever
+            # changing shapes does not pay for a capture at every step.
+            seen = self._seen[sig] = self._seen.get(sig, 0) + 1
+            if seen >= 2 and seen & (seen - 1) == 0:
                 return self._capture(sig, entries, bucket)
         ctx, logit_rows = self._pack(entries)
         return self.model.forward(ctx, self.views, logit_rows)
