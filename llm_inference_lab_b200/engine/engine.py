@@ -253,6 +253,8 @@ class Engine:
             # Captured the second time a shape comes; a shape whose graph was pushed out by newer
             # ones is captured again only at its 4th, 8th, 16th... coming, so a workload of ever
             # changing shapes does not pay for a capture at every step.
+            if len(self._seen) > 4096:      # shapes that never came back: forget the counts
+                self._seen.clear()
             seen = self._seen[sig] = self._seen.get(sig, 0) + 1
             if seen >= 2 and seen & (seen - 1) == 0:
                 return self._capture(sig, entries, bucket)
