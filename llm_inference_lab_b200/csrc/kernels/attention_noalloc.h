@@ -5,7 +5,7 @@
  *
  * Who needs it: code that runs where device memory cannot be allocated.  Examples are a
  * plugin inside a host application that owns the whole device heap and forbids cudaMalloc,
- * a callback that runs while allocation would deadlock or break a capture, a real-time loop
+ * a callback during which the host forbids allocation, a real-time loop
  * that may not block on the allocator, and a caller that has only raw device pointers and no
  * tensor library.  Such callers still pass the inputs and the output; what they cannot supply
  * is the scratch for the per-split partial results, so that scratch is a fixed array inside
