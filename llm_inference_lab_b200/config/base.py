@@ -130,3 +130,32 @@ def read_config_json(path: str) -> dict[str, Any]:
     if not isinstance(raw, dict):
         raise ConfigError(f"{path} must hold a JSON object")
     return raw
+
+
+def read_generation_eos(model_dir: str) -> tuple[int, ...] | None:
+    """End-of-sequence ids from an optional ``generation_config.json`` beside ``config.json``.
+
+    The reference reads that file if it exists and lets its ``eos_token_id`` (one id or a
+    list) replace the model configuration's single id
+    (rust/engine/src/runner/loader.rs:199-205; rust/engine/src/runner/model/qwen2/engine.rs:403-407).
+    Its other keys (do_sample, temperature, top_k, top_p, max_new_tokens) are per-request
+    options there and are not taken from the file.  Returns None if the file is absent or
+    names no id.
+    """
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.exists(path):
+        return None
+    try:
+        with open(path) as fh:
+            raw = json.load(fh)
+    except json.JSONDecodeError as exc:
+        raise ConfigError(f"{path} is not valid JSON: {exc}") from None
+    if not isinstance(raw, dict):
+        raise ConfigError(f"{path} must hold a JSON object")
+    eos = raw.get("eos_token_id")
+    if eos is None:
+        return None
+    ids = [eos] if isinstance(eos, int) and not isinstance(eos, bool) else eos
+    if not isinstance(ids, list) or not all(isinstance(t, int) and not isinstance(t, bool) and t >= 0 for t in ids):
+        raise ConfigError(f"{path}: 'eos_token_id' must be a non-negative integer or a list of them")
+    return tuple(ids)

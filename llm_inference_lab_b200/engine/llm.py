@@ -13,6 +13,7 @@ import time
 from typing import Optional, Sequence, Union
 
 from ..cache import manager as cache_mod
+from ..config.base import read_generation_eos
 from ..sampling import Sampler, SamplingConfig
 from .decode_graph import DecodeGraphs
 from .engine import Engine, Entry
@@ -40,7 +41,10 @@ class LLM:
         self.scheduler = rt.Scheduler(self.engine.cache, max_batch_tokens, self.engine.max_seq_len, max_requests,
                                       reserve_future)
         self.sampler = Sampler(self.engine.device)
-        self.model_eos = list(self.engine.model.blueprint.eos_token_ids)
+        # generation_config.json, where the folder has one, names the ids that end a sequence
+        # (rust/engine/src/runner/model/qwen2/engine.rs:403-407); else the model configuration does.
+        file_eos = read_generation_eos(model_dir) if isinstance(model_dir, str) else None
+        self.model_eos = list(file_eos if file_eos is not None else self.engine.model.blueprint.eos_token_ids)
         self.cuda_graph = bool(cuda_graph)
         self.graphs = DecodeGraphs(self.engine) if self.cuda_graph else None
         # With graphs: while a decode step runs, the next one is planned and launched before the first

@@ -97,3 +97,24 @@ def test_run_order_is_data():
     with pytest.raises(ValueError, match="no layer call writes"):
         cache_plan(unread)
     assert copy.deepcopy(bp) == bp
+
+
+def test_generation_config_end_tokens(tmp_path):
+    import json
+    from llm_inference_lab_b200.config import ConfigError, read_generation_eos
+
+    assert read_generation_eos(str(tmp_path)) is None, "the file is optional"
+    path = tmp_path / "generation_config.json"
+    path.write_text(json.dumps({"do_sample": True, "temperature": 0.7}))
+    assert read_generation_eos(str(tmp_path)) is None, "no id named"
+    path.write_text(json.dumps({"eos_token_id": 151645}))
+    assert read_generation_eos(str(tmp_path)) == (151645,)
+    path.write_text(json.dumps({"eos_token_id": [151645, 151643]}))
+    assert read_generation_eos(str(tmp_path)) == (151645, 151643)
+    for bad in ({"eos_token_id": "x"}, {"eos_token_id": [1, -2]}, {"eos_token_id": [1.5]}, {"eos_token_id": True}):
+        path.write_text(json.dumps(bad))
+        with pytest.raises(ConfigError, match="eos_token_id"):
+            read_generation_eos(str(tmp_path))
+    path.write_text("{not json")
+    with pytest.raises(ConfigError, match="not valid JSON"):
+        read_generation_eos(str(tmp_path))
