@@ -29,6 +29,7 @@ from ..kernels import ops
 from ..models.builder import CausalLM, load_model
 from ..parts.base import CacheView, GroupView, StepContext
 from ..parts.spec import FixedState, PagedKV
+from .. import profiling
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
           "fp32": torch.float32}
@@ -205,6 +206,16 @@ class Engine:
         """
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
         self.validate(entries, reserved)
+        if not profiling.ON:
+            return self._step(entries, reserved)
+        # The reference's label: a prefill step if any request brings more than one token or holds
+        # nothing yet (rust/engine/src/runner/model/qwen2/engine.rs:862-864).
+        prefill = any(len(e.tokens) > 1 or not self.cache.has(e.request) or self.cache.length(e.request) == 0
+                      for e in entries)
+        with profiling.scoped_range("step.prefill" if prefill else "step.decode"):
+            return self._step(entries, reserved)
+
+    def _step(self, entries: Sequence[Entry], reserved: bool) -> Optional[torch.Tensor]:
         opened = []
         taken = []
         try:

@@ -15,6 +15,7 @@ import dataclasses
 import torch
 
 from ..parts.base import CacheView, StepContext, lookup
+from ..profiling import scoped_range
 from ..parts.spec import CacheNeed, FixedState, ModelBlueprint, PagedKV, TensorSpec
 
 
@@ -92,21 +93,25 @@ class CausalLM:
         self.final_norm = lookup("norm", bp.final_norm.kind)(bp.final_norm, weights, dtype, device)
         self.head = lookup("head", bp.head.kind)(bp.head, weights, dtype, device)
         self.order = bp.order
+        self.range_names = [f"layer.{call.layer}" for call in bp.order]     # profiling ranges
         self.cache_plan = cache_plan(bp)
 
     def forward(self, ctx: StepContext, caches: list[CacheView], logit_rows: torch.Tensor | None):
         """Runs the rows of `ctx`; returns 32-bit logits [len(logit_rows), vocab] or None."""
-        x = self.embedding.forward(ctx.token_ids)
+        with scoped_range("embedding"):
+            x = self.embedding.forward(ctx.token_ids)
         pending = None
-        for call in self.order:
+        for call, name in zip(self.order, self.range_names):
             view = caches[call.cache]
             if not call.write:
                 view = dataclasses.replace(view, write=False)
-            x, pending = self.blocks[call.layer].forward(x, pending, ctx, view)
+            with scoped_range(name):
+                x, pending = self.blocks[call.layer].forward(x, pending, ctx, view)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
-        h = self.final_norm.forward_add(x, pending, rows=logit_rows)
-        return self.head.forward(h)
+        with scoped_range("final_norm+head"):
+            h = self.final_norm.forward_add(x, pending, rows=logit_rows)
+            return self.head.forward(h)
 
 
 def load_model(model_dir: str, dtype: torch.dtype, device) -> tuple[CausalLM, object]:

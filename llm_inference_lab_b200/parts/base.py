@@ -130,6 +130,9 @@ class Block:
 
     def __init__(self, mixer: Mixer, ffn: FeedForward, norms: list[Norm]):
         self.mixer, self.ffn, self.norms = mixer, ffn, norms
+        # names of the profiling ranges around the two halves of a block
+        self.mixer_range = "mixer." + str(getattr(getattr(mixer, "spec", None), "kind", type(mixer).__name__))
+        self.ffn_range = "feed_forward." + str(getattr(getattr(ffn, "spec", None), "kind", type(ffn).__name__))
 
     def forward(self, x, pending, ctx: StepContext, cache: CacheView):
         """`pending` is what the previous block still owes the residual stream (or None)."""

@@ -1,6 +1,7 @@
 """Arrangements of a mixer and a feed-forward around the residual stream."""
 from __future__ import annotations
 
+from ..profiling import scoped_range
 from .base import Block, register_part
 
 
@@ -14,10 +15,12 @@ class PreNormBlock(Block):
     n_norms = 2
 
     def forward(self, x, pending, ctx, cache):
-        h = self.norms[0].forward_add(x, pending)
-        a = self.mixer.forward(h, ctx, cache)
-        h = self.norms[1].forward_add(x, a)
-        return x, self.ffn.forward(h, ctx)
+        with scoped_range(self.mixer_range):
+            h = self.norms[0].forward_add(x, pending)
+            a = self.mixer.forward(h, ctx, cache)
+        with scoped_range(self.ffn_range):
+            h = self.norms[1].forward_add(x, a)
+            return x, self.ffn.forward(h, ctx)
 
 
 register_part("block", "prenorm", PreNormBlock)
