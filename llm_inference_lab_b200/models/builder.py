@@ -16,7 +16,7 @@ import torch
 
 from ..parts.base import CacheView, StepContext, lookup
 from ..profiling import scoped_range
-from ..parts.spec import CacheNeed, FixedState, ModelBlueprint, PagedKV, TensorSpec
+from ..parts.spec import CacheNeed, ModelBlueprint, PagedKV, TensorSpec
 
 
 def _part_classes(bp: ModelBlueprint):

@@ -2,7 +2,6 @@
 implementation: greedy tokens, temperature sampling with a seed, continuous batching with
 portions of prompts, end-of-sequence, and preemption when pages run out."""
 import json
-import os
 import subprocess
 import sys
 

@@ -3,7 +3,6 @@ the framework takes new kinds of parts without a change to its files: a toy mixe
 of its own, a toy feed-forward with routing, a toy position encoding, and the toy architectures
 that use them beside the framework's parts, all defined here."""
 import dataclasses
-import math
 
 import numpy as np
 import pytest

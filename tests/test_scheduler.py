@@ -2,7 +2,6 @@
 portions under the token budget, decoding, finishing and freeing, and what happens when
 pages run out.  The method follows the reference's `SteppedModel` tests
 (rust/engine/src/runner/model_runner.rs:987-1106, 1209-2683)."""
-import pytest
 
 from llm_inference_lab_b200.cache import CacheManager, GroupConfig
 from llm_inference_lab_b200.cache.manager import runtime
