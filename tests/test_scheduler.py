@@ -339,3 +339,94 @@ def test_lookahead_without_a_free_page_falls_back_to_the_plain_plan():
     done = {f.id: f for f in sched.take_finished()}
     assert done[1].reason.name == "capacity" and done[1].generated == [50, 51]
     assert cache.free_pages(0) == 2 and cache.live_requests == 0
+
+
+# ----------------------------------------------------------------------------------------
+# Random workloads: pools of every tightness, both admission policies, windows, late arrivals.
+# ----------------------------------------------------------------------------------------
+
+def test_random_workloads_give_the_scripted_tokens_and_every_page_back():
+    """The scripted step answers with a token that depends on request and position only, so whatever
+    the scheduler decides (portions, waiting, preemption and recomputation, lookahead), a request
+    that finishes must have exactly the tokens it would have alone; one that fails with `capacity`
+    must be one that cannot fit alone; and every page and state slot comes back."""
+    import random
+
+    outcomes = {"length": 0, "eos": 0, "capacity": 0, "invalid": 0, "preemptions": 0}
+    for trial in range(250):
+        rng = random.Random(trial)
+        page = rng.choice([1, 2, 4, 8, 16])
+        window = rng.choice([0, 0, 0, 5, 17])
+        reqs = [(i + 1, [rng.randint(0, 50) for _ in range(rng.randint(1, 40))], rng.randint(0, 30))
+                for i in range(rng.randint(1, 9))]
+        life = [len(p) + max(n, 1) - 1 for _, p, n in reqs]
+        biggest = max(-(-n // page) for n in life)
+        pages = rng.randint(max(1, biggest - 1), max(sum(-(-n // page) for n in life), biggest) + 2)
+        budget = rng.choice([1, 2, 3, 8, 16, 64])
+        reserve = rng.random() < 0.5
+        max_seq = rng.choice([0, 0, 45, 70])
+        ahead_on = rng.random() < 0.6
+        eos_on = rng.random() < 0.6
+        stop = {rid: rng.randint(1, 35) for rid, _, _ in reqs}
+
+        def token(rid, pos):
+            if eos_on and pos >= stop[rid] + len(reqs[rid - 1][1]):
+                return 999
+            return 100 + (rid * 7 + pos) % 50
+
+        groups = [GroupConfig(page, 0, pages)] + ([GroupConfig(page, window, pages)] if window else [])
+        cache = CacheManager(groups, rng.randint(1, 9))
+        sched = runtime().Scheduler(cache, budget, max_seq, 0, reserve)
+        late = [(rid, p, n, [999], False) for rid, p, n in reqs][::-1]
+        for _ in range(rng.randint(0, len(late))):
+            sched.add(*late.pop())
+        done = {}
+
+        def collect():
+            for f in sched.take_finished():
+                assert f.id not in done, "a request finishes once"
+                done[f.id] = f
+
+        for _ in range(100_000):
+            while late and rng.random() < 0.3:
+                sched.add(*late.pop())
+            plan = sched.plan()
+            collect()
+            if not plan:
+                if late:
+                    sched.add(*late.pop())
+                    continue
+                assert sched.idle, "requests are left but nothing is planned"
+                break
+            while True:
+                assert sum(e.n for e in plan) <= budget
+                pure = all(e.n == 1 and e.sample for e in plan)
+                ahead = sched.plan_ahead(plan) if (pure and ahead_on) else []
+                sched.complete(plan, [token(e.id, e.start + e.n) for e in plan if e.sample])
+                collect()
+                if not ahead:
+                    break
+                plan = ahead
+        where = f"trial {trial}"
+        assert set(done) == {rid for rid, _, _ in reqs}, where
+        for rid, prompt, n in reqs:
+            f = done[rid]
+            want = []
+            for i in range(n):
+                want.append(token(rid, len(prompt) + i))
+                if want[-1] == 999:
+                    break
+            reason = f.reason.name
+            outcomes[reason] += 1
+            outcomes["preemptions"] += f.preemptions
+            if reason in ("length", "eos"):
+                assert list(f.generated) == want, where
+                assert reason == ("eos" if want and want[-1] == 999 else "length"), where
+            elif reason == "invalid":
+                assert max_seq and len(prompt) + max(n, 1) - 1 > max_seq, where
+            else:
+                assert reason == "capacity" and -(-(len(prompt) + max(n, 1) - 1) // page) > pages, where
+                assert list(f.generated) == want[: len(f.generated)], where
+        assert all(cache.free_pages(g) == pages for g in range(len(groups))) and cache.live_requests == 0, where
+        cache.check_consistency()
+    assert outcomes["preemptions"] > 100 and outcomes["capacity"] > 5 and outcomes["invalid"] > 20, outcomes
