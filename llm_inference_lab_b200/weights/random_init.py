@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import os
 import zlib
+from concurrent.futures import ThreadPoolExecutor
 from typing import Sequence
 
 import numpy as np
@@ -22,13 +23,15 @@ from .safetensors_io import save_file
 def random_tensor(spec: TensorSpec, seed: int, std: float, norm_std: float, scales: dict[str, float]) -> torch.Tensor:
     rng = np.random.default_rng([seed & 0xFFFFFFFF, zlib.crc32(spec.name.encode())])
     values = rng.standard_normal(size=spec.shape, dtype=np.float32)
+    # in place: a model of billions of values is made of tensors of hundreds of megabytes
     if spec.init == "norm":
-        values = 1.0 + norm_std * values
+        values *= np.float32(norm_std)
+        values += np.float32(1.0)
     else:
-        values = std * values
+        values *= np.float32(std)
     for pattern, scale in scales.items():
         if pattern in spec.name:
-            values = values * np.float32(scale)
+            values *= np.float32(scale)
     return torch.from_numpy(np.ascontiguousarray(values, dtype=np.float32))
 
 
@@ -44,10 +47,15 @@ def write_random_model(config, folder: str, seed: int = 0, dtype: torch.dtype = 
 
     arch = resolve(config.to_dict())
     specs: Sequence[TensorSpec] = expected_tensors(arch.blueprint(config))
-    tensors = {}
-    for spec in specs:
+
+    def make(spec: TensorSpec) -> torch.Tensor:
         t = random_tensor(spec, seed, std, norm_std, scales or {})
-        tensors[spec.name] = t if spec.keep_f32 else t.to(dtype)
+        return t if spec.keep_f32 else t.to(dtype)
+
+    # Every tensor has a stream of its own, so they can be drawn side by side (NumPy's generator
+    # releases the interpreter lock); the values do not depend on the number of threads.
+    with ThreadPoolExecutor(max_workers=max(1, min(8, os.cpu_count() or 1))) as pool:
+        tensors = dict(zip((spec.name for spec in specs), pool.map(make, specs)))
     os.makedirs(folder, exist_ok=True)
     config.save(folder)
     save_file(tensors, os.path.join(folder, "model.safetensors"), metadata={"format": "pt", "seed": str(seed)})
