@@ -138,9 +138,11 @@ def save_file(tensors: dict[str, torch.Tensor], path: str, metadata: dict[str, s
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store dtype {t.dtype} of tensor {name!r}")
-        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
-        header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
-        offset += len(raw)
+        # a view of the tensor's own bytes: nothing is copied before the write
+        raw = memoryview(t.reshape(-1).view(torch.uint8).numpy()) if t.numel() else memoryview(b"")
+        header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
+                        "data_offsets": [offset, offset + raw.nbytes]}
+        offset += raw.nbytes
         blobs.append(raw)
     text = json.dumps(header, separators=(",", ":")).encode()
     text += b" " * ((8 - len(text) % 8) % 8)
