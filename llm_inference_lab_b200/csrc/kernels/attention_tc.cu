@@ -765,16 +765,19 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
                          float scale, int splits, float* scratch, bool may_cluster, cudaStream_t stream) {
   if (requests <= 0) return 0;
   const bool cluster = may_cluster && splits >= 2 && splits <= DC_MAX_CLUSTER;
-  if (n_q % n_kv || splits < 1 || (splits > 1 && !cluster && scratch == nullptr)) return (int)cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
+  if (n_kv <= 0 || n_q % n_kv || splits < 1 || (splits > 1 && !cluster && scratch == nullptr)) return (int)cudaErrorInvalidValue;
+  // The shared-memory limit is an attribute of the kernel on one device: set once per device.
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+  if (!configured[device]) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          DcLayout<false>::SMEM);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(attention_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                DcLayout<true>::SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[device] = true;
   }
   const int group = n_q / n_kv, m_tiles = (group + 15) / 16;
   dim3 grid(splits, n_kv * m_tiles, requests);
@@ -929,7 +932,7 @@ LAB_EXPORT int lab_attention_decode_noalloc(void* out, int out_stride, const voi
                                             const int* kv_len, const int* block_table, int max_blocks, int requests,
                                             int n_q, int n_kv, int page_size, int num_pages, int window, float scale,
                                             int splits, cudaStream_t stream) {
-  if (splits < 1 || requests < 0 || n_q <= 0) return (int)cudaErrorInvalidValue;
+  if (splits < 1 || requests < 0 || n_q <= 0 || n_kv <= 0) return (int)cudaErrorInvalidValue;
   if (lab_attention_decode_scratch_floats(requests, n_q, splits) > LAB_NOALLOC_MAX_FLOATS) return LAB_NOALLOC_TOO_LARGE;
   int device = -1;
   cudaError_t e = cudaGetDevice(&device);

@@ -22,7 +22,8 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from ..parts.base import GroupView, StepContext
+from ..parts.base import StepContext
+from .engine import InvalidInput
 
 
 @dataclasses.dataclass
@@ -45,11 +46,15 @@ class DecodeGraphs:
     MAX_KEPT_BATCH = 1024
 
     def __init__(self, engine):
+        if engine.stateful:
+            # A mixer with state of its own may index it on the host, and the warm-up run before a
+            # capture would advance it twice: such models step eagerly.
+            raise ValueError("decode graphs do not serve models with fixed-size per-request state")
         self.engine = engine
         self.cached: dict[tuple, _Captured] = {}
         self.replays = 0
         self.captures = 0
-        self._last = None
+        self._last, self._last_requests = None, None
         self._pairs_of = None
         self._ring, self._ring_at = [], 0     # pinned buffers for the ids of steps launched with `keep`
         self._done = torch.cuda.Event()     # recorded after every replay
@@ -59,20 +64,9 @@ class DecodeGraphs:
         return (n_requests, max(256, 1 << (int(max_kv_len) - 1).bit_length()))
 
     def _context(self, cap: _Captured, B: int, kv_bucket: int) -> StepContext:
-        eng, L, dev = self.engine, cap.layout, cap.dev
-        n_groups = len(eng.group_windows)
-
-        def view(at, n):
-            return dev[at: at + n]
-
-        width = eng.max_blocks
-        groups = [GroupView(eng.page_size, eng.group_windows[g], view(L.row_slot[g], B),
-                            view(L.block_table[g], B * width).view(B, width)) for g in range(n_groups)]
-        return StepContext(
-            dtype=eng.dtype, device=eng.device, n_tokens=B, n_requests=B, token_ids=cap.tokens,
-            row_req=view(L.row_req, B), row_pos=view(L.row_pos, B), q_start=view(L.q_start, B + 1),
-            kv_len=view(L.kv_len, B), pos0=view(L.pos0, B), state_slot=view(L.state_slot, B), groups=groups,
-            q_lens=[1] * B, kv_lens=[kv_bucket] * B, state_slots=[], max_q_len=1, max_kv_len=kv_bucket)
+        eng = self.engine
+        widths = [eng.max_blocks] * len(eng.group_windows)
+        return eng._context(cap.dev, cap.layout, widths, B, B, [1] * B, [kv_bucket] * B, [], cap.tokens)
 
     def _run(self, cap: _Captured, ctx: StepContext) -> torch.Tensor:
         logits = self.engine.model.forward(ctx, self.engine.views, cap.rows)
@@ -112,20 +106,42 @@ class DecodeGraphs:
             pairs = self._pairs_of[1]           # the same batch as last time
         else:
             pairs = [(int(r), 1) for r in requests]
+            if len(set(requests)) != B or B == 0:
+                raise InvalidInput("a decode step needs one entry per request, and at least one")
             self._pairs_of = (list(requests), pairs)
-        if not reserved:
-            done = []
-            try:
-                for r, _ in pairs:
-                    eng.cache.reserve(r, 1)
-                    done.append(r)
-            except Exception:
-                for r in done:
-                    eng.cache.rollback(r)
-                raise
+        if tokens is not None and not all(0 <= t < eng.vocab for t in tokens):
+            raise InvalidInput(f"token id outside [0, {eng.vocab})")
+        same_batch = self._last is not None and self._last_requests == requests
+        if tokens is None and not same_batch:
+            raise InvalidInput("no input ids given, and the previous step was not one of these requests")
+        began = eng._begin(pairs, reserved)
+        try:
+            cap = self._launch(pairs, B, tokens, temps, seeds, same_batch)
+        except Exception:
+            eng._fail(began)
+            raise
+        eng._end(pairs, reserved)
+        self._last, self._last_requests = cap, list(requests)
+        if keep:
+            if not self._ring:
+                self._ring = [(torch.zeros((self.MAX_KEPT_BATCH,), dtype=torch.int32, pin_memory=True),
+                               torch.cuda.Event()) for _ in range(4)]
+            if B > self.MAX_KEPT_BATCH:
+                raise ValueError("batch too large for the kept-token buffers")
+            buf, event = self._ring[self._ring_at]
+            self._ring_at = (self._ring_at + 1) % len(self._ring)
+            buf[:B].copy_(cap.tokens, non_blocking=True)
+            event.record(ops.current_stream())
+            return (buf, event, B)
+        return cap.tokens
+
+    def _launch(self, pairs, B, tokens, temps, seeds, same_batch) -> _Captured:
+        """Uploads the step's metadata into the buffers of the graph that serves it (captured now if
+        it is new) and replays it."""
+        eng = self.engine
         max_kv = max(eng.cache.reserved(r) for r, _ in pairs)
         if max_kv > eng.max_seq_len:
-            raise ValueError("a request exceeds the maximum sequence length")
+            raise InvalidInput("a request exceeds the maximum sequence length")
         key = self._key(B, max_kv)
         fresh = key not in self.cached
         if fresh:
@@ -139,16 +155,23 @@ class DecodeGraphs:
         host = st["np"]
         eng.cache.pack(pairs, cap.layout, host[2 * B:], 0, 0)
         lo, hi = 2 * B, 2 * B + n_meta
+        moved = cap is not self._last
         if tokens is not None:
             host[hi: hi + B] = np.asarray(tokens, dtype=np.int32)
             hi += B
-        elif self._last is not None and self._last is not cap and self._last.tokens.numel() == B:
+        elif moved:
             # the previous step of this batch ran from another graph (its context outgrew a bucket):
             # the ids it sampled move over on the device
             cap.tokens.copy_(self._last.tokens, non_blocking=True)
         if temps is not None:
             host[0: B].view(np.float32)[:] = np.asarray(list(temps), dtype=np.float32)
             host[B: 2 * B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
+            lo = 0
+        elif same_batch and moved:
+            # ... and so do the temperatures and seeds, which live in each graph's own buffer
+            cap.buf[0: 2 * B].copy_(self._last.buf[0: 2 * B], non_blocking=True)
+        elif not same_batch:
+            host[0: 2 * B] = 0          # nobody said otherwise: greedy
             lo = 0
         ops.copy_to_device(cap.buf, st["host"], lo, hi)
         stream = ops.current_stream()
@@ -177,24 +200,7 @@ class DecodeGraphs:
         self._done.record(stream)
         ops.COUNTER.launches += cap.launches
         self.replays += 1
-        if not reserved:
-            for r, _ in pairs:
-                eng.cache.commit(r, 1)
-        eng.stats.steps += 1
-        eng.stats.decode_tokens += B
-        self._last = cap
-        if keep:
-            if not self._ring:
-                self._ring = [(torch.zeros((self.MAX_KEPT_BATCH,), dtype=torch.int32, pin_memory=True),
-                               torch.cuda.Event()) for _ in range(4)]
-            if B > self.MAX_KEPT_BATCH:
-                raise ValueError("batch too large for the kept-token buffers")
-            buf, event = self._ring[self._ring_at]
-            self._ring_at = (self._ring_at + 1) % len(self._ring)
-            buf[:B].copy_(cap.tokens, non_blocking=True)
-            event.record(stream)
-            return (buf, event, B)
-        return cap.tokens
+        return cap
 
     @staticmethod
     def read(ticket) -> list[int]:

@@ -110,6 +110,7 @@ class Engine:
                 self.views.append(CacheView(need, state=state))
             else:
                 self.views.append(CacheView(None))
+        self.stateful = any(v.state is not None for v in self.views)
         self.max_blocks = -(-self.max_seq_len // self.page_size)
         self.stats = EngineStats()
         self._staging = [self._new_staging() for _ in range(3)]
@@ -142,12 +143,13 @@ class Engine:
         time).  The logits a replayed step returns live in the graph's buffer: read them before the
         next step of the same shape.  Models with fixed-size per-request state keep running eagerly
         (their mixers may index the state on the host)."""
-        self._graphs_on = all(v.state is None for v in self.views)
+        self._graphs_on = not self.stateful
         self._graphs_max = max_cached
 
     # ------------------------------------------------------------------------------------
     def open(self, request: int) -> None:
-        """A new request: takes a state slot and clears its fixed-size state."""
+        """A new request: takes a state slot.  Its fixed-size state is cleared here and again by the
+        first step that brings it tokens (the scheduler opens requests without the engine)."""
         slot = self.cache.open(int(request))
         for view in self.views:
             if view.state is not None:
@@ -216,34 +218,70 @@ class Engine:
             return self._step(entries, reserved)
 
     def _step(self, entries: Sequence[Entry], reserved: bool) -> Optional[torch.Tensor]:
-        opened = []
-        taken = []
+        pairs = [(int(e.request), len(e.tokens)) for e in entries]
+        began = self._begin(pairs, reserved)
         try:
-            for e in entries:
-                if not self.cache.has(e.request):
-                    self.open(e.request)
-                    opened.append(e.request)
-            if not reserved:
-                for e in entries:
-                    self.cache.reserve(e.request, len(e.tokens))
-                    taken.append(e.request)
             logits = self._run(entries)
         except Exception:
-            for r in taken:
-                self.cache.rollback(r)
-            for r in opened:
-                self.cache.close(r)
+            self._fail(began)
             raise
+        self._end(pairs, reserved)
+        return logits
+
+    # The three pieces of every step's book-keeping, shared by the eager path, the step graphs and
+    # the decode graphs: begin (open, reserve, prepare fixed-size state), then end or fail.
+    def _begin(self, pairs, reserved: bool):
+        """Opens unknown requests, reserves pages unless the caller has, and prepares fixed-size
+        state: a request that holds no committed token yet (new, or preempted and reopened, whoever
+        opened it) starts from zeros, and the rows of the step's requests are saved so that a
+        failed step can put them back.  Returns what `_fail` needs."""
+        opened, taken, saved = [], [], None
+        try:
+            for r, _ in pairs:
+                if not self.cache.has(r):
+                    self.cache.open(r)
+                    opened.append(r)
+            if not reserved:
+                for r, n in pairs:
+                    self.cache.reserve(r, n)
+                    taken.append(r)
+            if self.stateful:
+                slots = torch.tensor([self.cache.state_slot(r) for r, _ in pairs], dtype=torch.long,
+                                     device=self.device)
+                fresh = [i for i, (r, _) in enumerate(pairs) if self.cache.length(r) == 0]
+                saved = []
+                for view in self.views:
+                    if view.state is None:
+                        continue
+                    if fresh:
+                        view.state[slots[fresh]] = 0
+                    saved.append((view.state, slots, view.state[slots]))
+        except Exception:
+            self._fail((opened, taken, None))
+            raise
+        return opened, taken, saved
+
+    def _fail(self, began) -> None:
+        """A step failed: fixed-size state goes back to what it was, pages reserved here are given
+        back, requests opened here are closed."""
+        opened, taken, saved = began
+        for state, slots, rows in saved or ():
+            state[slots] = rows
+        for r in taken:
+            self.cache.rollback(r)
+        for r in opened:
+            self.cache.close(r)
+
+    def _end(self, pairs, reserved: bool) -> None:
         if not reserved:
-            for e in entries:
-                self.cache.commit(e.request, len(e.tokens))
+            for r, n in pairs:
+                self.cache.commit(r, n)
         self.stats.steps += 1
-        for e in entries:
-            if len(e.tokens) == 1 and self.cache.reserved(e.request) > 1:
+        for r, n in pairs:
+            if n == 1 and self.cache.reserved(r) > 1:
                 self.stats.decode_tokens += 1
             else:
-                self.stats.prefill_tokens += len(e.tokens)
-        return logits
+                self.stats.prefill_tokens += n
 
     # ------------------------------------------------------------------------------------
     def _run(self, entries: Sequence[Entry]):
@@ -286,7 +324,7 @@ class Engine:
         dev = torch.zeros((total,), dtype=torch.int32, device=self.device)
         self._fill(entries, layout, widths, dev, tok_at, want_at)
         q_lens = [n for _, n in pairs]
-        ctx = self._context(dev, layout, widths, T, B, q_lens, [bucket] * B, [], tok_at)
+        ctx = self._context(dev, layout, widths, T, B, q_lens, [bucket] * B, [], dev[tok_at: tok_at + T])
         rows = dev[want_at: want_at + n_want] if n_want else None
         # One eager run (it also configures kernels and warms the allocator), then the capture.
         # Running the step more than once is harmless: it writes the same cache entries again.
@@ -334,7 +372,7 @@ class Engine:
         ev.record()
         st["event"] = ev
 
-    def _context(self, dev, layout, widths, T, B, q_lens, kv_lens, state_slots, tok_at) -> StepContext:
+    def _context(self, dev, layout, widths, T, B, q_lens, kv_lens, state_slots, token_ids) -> StepContext:
         def view(at, n):
             return dev[at: at + n]
 
@@ -343,7 +381,7 @@ class Engine:
                             view(layout.block_table[g], B * widths[g]).view(B, widths[g])) for g in range(n_groups)]
         return StepContext(
             dtype=self.dtype, device=self.device, n_tokens=T, n_requests=B,
-            token_ids=view(tok_at, T), row_req=view(layout.row_req, T), row_pos=view(layout.row_pos, T),
+            token_ids=token_ids, row_req=view(layout.row_req, T), row_pos=view(layout.row_pos, T),
             q_start=view(layout.q_start, B + 1), kv_len=view(layout.kv_len, B), pos0=view(layout.pos0, B),
             state_slot=view(layout.state_slot, B), groups=groups, q_lens=q_lens, kv_lens=kv_lens,
             state_slots=state_slots, max_q_len=max(q_lens), max_kv_len=max(kv_lens))
@@ -365,6 +403,6 @@ class Engine:
         self._fill(entries, layout, widths, dev, tok_at, want_at)
         ctx = self._context(dev, layout, widths, T, B, [n for _, n in pairs],
                             [self.cache.reserved(r) for r, _ in pairs],
-                            [self.cache.state_slot(r) for r, _ in pairs], tok_at)
+                            [self.cache.state_slot(r) for r, _ in pairs], dev[tok_at: tok_at + T])
         logit_rows = dev[want_at: want_at + n_want] if n_want else None
         return ctx, logit_rows

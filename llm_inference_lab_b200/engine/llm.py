@@ -45,7 +45,8 @@ class LLM:
         # (rust/engine/src/runner/model/qwen2/engine.rs:403-407); else the model configuration does.
         file_eos = read_generation_eos(model_dir) if isinstance(model_dir, str) else None
         self.model_eos = list(file_eos if file_eos is not None else self.engine.model.blueprint.eos_token_ids)
-        self.cuda_graph = bool(cuda_graph)
+        # Models with fixed-size per-request state step eagerly (see DecodeGraphs).
+        self.cuda_graph = bool(cuda_graph) and not self.engine.stateful
         self.graphs = DecodeGraphs(self.engine) if self.cuda_graph else None
         # With graphs: while a decode step runs, the next one is planned and launched before the first
         # one's tokens have reached the host (the device feeds the sampled ids forward), so the host's

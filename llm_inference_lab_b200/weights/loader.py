@@ -4,9 +4,10 @@ The loader is given the list of tensors the model's parts want (`TensorSpec`)
 and checks the whole folder against it before a single byte moves: tensors
 that are wanted but absent, present but not wanted, or of another shape are
 reported together in one `WeightsError`.  Stored precision is kept: bfloat16
-stays bfloat16, a tensor stored in 32-bit stays 32-bit, float16 and float64
-are converted to the nearest kept type (bfloat16 and float32), integer tables
-become int32.  A part then casts what its kernels need (a float32 engine
+stays bfloat16, a tensor stored in 32-bit stays 32-bit, float16 is widened to
+float32 (exact; narrowing it to bfloat16 here would cost a 32-bit engine three
+bits of every weight), float64 is narrowed to float32, integer tables become
+int32.  A part then casts what its kernels need (a float32 engine
 widens everything; a bfloat16 engine narrows matrices that were stored wider,
 round to nearest even) unless the tensor is marked ``keep_f32``.
 Names and shapes are the checkpoint's own; nothing is renamed
@@ -42,9 +43,9 @@ class WeightsError(ValueError):
 
 
 def kept_dtype(stored: torch.dtype) -> torch.dtype:
-    if stored in (torch.bfloat16, torch.float16):
+    if stored == torch.bfloat16:
         return torch.bfloat16
-    if stored in (torch.float32, torch.float64):
+    if stored in (torch.float16, torch.float32, torch.float64):
         return torch.float32
     if stored in (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8, torch.bool):
         return torch.int32

@@ -46,9 +46,23 @@ TINY_E = dict(
     rope_theta=500000.0, max_position_embeddings=128, hidden_act="silu", tie_word_embeddings=False,
     use_sliding_window=False, eos_token_id=None)
 
+# Two whose heads are the sizes the tcgen05 attention is built for (64 and 128), with positions enough for
+# portions of more than 64 tokens, which is where that kernel takes over from the mma.sync one.
+TINY_F = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=311, hidden_size=256, intermediate_size=176,
+    num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6,
+    rope_theta=1e6, max_position_embeddings=448, hidden_act="silu", tie_word_embeddings=True,
+    use_sliding_window=False, eos_token_id=None)
+TINY_G = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=205, hidden_size=160, intermediate_size=232,
+    num_hidden_layers=3, num_attention_heads=2, num_key_value_heads=1, head_dim=128, rms_norm_eps=1e-5,
+    rope_theta=10000.0, max_position_embeddings=400, hidden_act="silu", tie_word_embeddings=False,
+    use_sliding_window=True, sliding_window=150, max_window_layers=2, eos_token_id=None)
+
 TINY = {"A": (TINY_A, dict(seed=0, page_size=4)), "B": (TINY_B, dict(seed=1, page_size=16)),
         "C": (TINY_C, dict(seed=2, page_size=8)), "D": (TINY_D, dict(seed=3, page_size=32)),
-        "E": (TINY_E, dict(seed=4, page_size=64))}
+        "E": (TINY_E, dict(seed=4, page_size=64)), "F": (TINY_F, dict(seed=5, page_size=16)),
+        "G": (TINY_G, dict(seed=6, page_size=32))}
 
 # Random weights N(0, 0.02) make attention nearly uniform and would hide a misplaced key;
 # the q and k projections are scaled up so that scores spread over several units (more would only amplify rounding).

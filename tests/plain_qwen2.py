@@ -154,16 +154,26 @@ def layer_window(cfg, layer):
     return 0
 
 
-def plain_forward(cfg, w, ids):
-    """Logits [T, vocab] of one whole sequence.  engine.rs:916-1130, 1298-1341"""
+def plain_hidden(cfg, w, ids):
+    """The final norm's output [T, hidden] of one whole sequence.  engine.rs:916-1130, 1298-1311"""
     ids = np.asarray(ids, dtype=np.int64)
     positions = np.arange(len(ids))
     x = plain_embedding(ids, w["model.embed_tokens.weight"])
     for layer in range(cfg["num_hidden_layers"]):
         x = plain_block(x, w, layer, cfg, positions)
-    x = plain_rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    return plain_rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+
+
+def plain_head(cfg, w, hidden):
+    """Logits of rows of the final norm's output; the head is the embedding table when tied.
+    engine.rs:299-303, 1312-1341"""
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
-    return plain_linear(x, head)
+    return plain_linear(hidden, head)
+
+
+def plain_forward(cfg, w, ids):
+    """Logits [T, vocab] of one whole sequence."""
+    return plain_head(cfg, w, plain_hidden(cfg, w, ids))
 
 
 def plain_argmax(logits):

@@ -203,3 +203,36 @@ def test_lookahead_decoding_gives_the_same_tokens(tmp_path_factory, dtype):
             assert llm.graphs.replays > 20
     assert outs[True] == outs[False]
     assert any(reason == "eos" for _, reason in outs[True][1]) and any(reason == "length" for _, reason in outs[True][1])
+
+
+def test_temperatures_and_seeds_follow_a_batch_from_graph_to_graph(tmp_path_factory):
+    """Decode graphs are captured per context bucket, each with buffers of its own: when a batch's
+    longest context crosses a bucket's edge (256 tokens), its temperatures and seeds must move to the
+    next graph with it, and a greedy batch that later uses a graph must not inherit them."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY["B"]
+    cfg = dict(cfg, max_position_embeddings=512)
+    folder = str(tmp_path_factory.mktemp("genB512"))
+    make_model_folder(folder, cfg, opt["seed"], "float32")
+    rng = np.random.default_rng(21)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (246, 240, 250)]
+    hot = SamplingConfig(max_new_tokens=20, do_sample=True, temperature=0.8, seed=13, ignore_eos=True)
+    cold = SamplingConfig(max_new_tokens=20, ignore_eos=True)
+    outs = {}
+    for graph in (False, True):
+        llm = LLM(folder, "f32", page_size=16, kv_tokens=1024, max_requests=4, max_batch_tokens=512, cuda_graph=graph)
+        first = [r.tokens for r in llm.generate(prompts, hot)]
+        second = [r.tokens for r in llm.generate(prompts, cold)]     # same batch size, same graphs, greedy
+        third = [r.tokens for r in llm.generate(prompts, hot)]
+        outs[graph] = (first, second, third)
+        if graph:
+            assert len(llm.graphs.cached) >= 2, "the batch crossed from one context bucket to the next"
+    assert outs[True] == outs[False]
+    assert outs[True][0] == outs[True][2] and outs[True][0] != outs[True][1]
+    pcfg, w = read_model_folder(folder)
+    for prompt, tokens in zip(prompts, outs[True][1]):
+        assert tokens == plain_greedy(pcfg, w, prompt, 20)
+    for prompt, tokens in zip(prompts, outs[True][0]):
+        check_teacher_forced(folder, prompt, tokens, 0.8, 13, 1e-4)

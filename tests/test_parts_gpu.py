@@ -256,6 +256,78 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     assert engine.cache.free_state_slots == 3
 
 
+def toy_greedy(folder, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(np.argmax(toy_reference(folder, ids)[-1])))
+    return ids[len(prompt):]
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_toy_state_survives_the_scheduler(tmp_path, graph):
+    """The toy architecture through `LLM.generate`: more requests than state slots, so slots are used
+    again (whoever opened the request, its state starts from zero); prompts cut into portions; a pool
+    so tight that a request is preempted and recomputed (its state starts over); with `cuda_graph`
+    asked for, which a model with state of its own declines.  Greedy tokens equal the NumPy toy's."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+    from llm_inference_lab_b200.weights import write_random_model
+
+    ToyConfig = define_toy()
+    cfg = ToyConfig.from_dict(dict(vocab_size=97, hidden_size=32, num_layers=3, inner_size=48, heads=2))
+    folder = write_random_model(cfg, str(tmp_path / "toy"), seed=5, dtype=torch.float32, std=0.08)
+    rng = np.random.default_rng(1)
+    prompts = [random_tokens(rng, n, 97) for n in (11, 3, 20, 7, 15)]
+    want = [toy_greedy(folder, p, 10) for p in prompts]
+    sampling = SamplingConfig(max_new_tokens=10, ignore_eos=True)
+    llm = LLM(folder, "f32", page_size=4, kv_tokens=256, max_requests=2, max_batch_tokens=6, cuda_graph=graph)
+    assert llm.engine.stateful and llm.graphs is None
+    assert [r.tokens for r in llm.generate(prompts, sampling)] == want
+    assert [r.tokens for r in llm.generate(prompts[::-1], sampling)] == want[::-1], "slots left dirty by the first run"
+    tight = LLM(folder, "f32", page_size=4, kv_tokens=56, max_requests=3, max_batch_tokens=8, reserve_future=False,
+                cuda_graph=graph)
+    results = tight.generate(prompts, sampling)
+    assert tight.scheduler.preemptions >= 1
+    assert [r.tokens for r in results] == want
+    for x in (llm, tight):
+        assert x.engine.cache.live_requests == 0 and x.engine.free_pages()[0] == x.engine.num_pages
+        x.engine.cache.check_consistency()
+
+
+def test_a_failed_step_leaves_state_and_pages_as_they_were(tmp_path):
+    """A step that fails after its mixers have advanced their state (here: the head raises) gives its
+    pages back and puts the state of its requests back, so the same step can be run again."""
+    from llm_inference_lab_b200.engine import Engine, Entry
+    from llm_inference_lab_b200.engine.decode_graph import DecodeGraphs
+    from llm_inference_lab_b200.weights import write_random_model
+
+    ToyConfig = define_toy()
+    cfg = ToyConfig.from_dict(dict(vocab_size=97, hidden_size=32, num_layers=3, inner_size=48, heads=2))
+    folder = write_random_model(cfg, str(tmp_path / "toy"), seed=6, dtype=torch.float32, std=0.08)
+    engine = Engine(folder, "float32", max_tokens=128, page_size=4, max_requests=3)
+    with pytest.raises(ValueError, match="fixed-size per-request state"):
+        DecodeGraphs(engine)
+    rng = np.random.default_rng(2)
+    a, b = random_tokens(rng, 14, 97), random_tokens(rng, 9, 97)
+    engine.step([Entry(0, a[:6], []), Entry(1, b[:5], [])])
+    free, states = engine.free_pages(), [v.state.clone() for v in engine.views if v.state is not None]
+    head = engine.model.head.forward
+
+    def broken(x):
+        raise RuntimeError("the head fails")
+
+    engine.model.head.forward = broken
+    with pytest.raises(RuntimeError, match="the head fails"):
+        engine.step([Entry(0, a[6:11], [4]), Entry(1, b[5:6], [0]), Entry(2, a[:3], [2])])
+    engine.model.head.forward = head
+    assert engine.free_pages() == free and not engine.has(2) and engine.length(0) == 6 and engine.length(1) == 5
+    assert all(torch.equal(s, v.state) for s, v in zip(states, [v for v in engine.views if v.state is not None]))
+    logits = engine.step([Entry(0, a[6:11], [4]), Entry(1, b[5:6], [0]), Entry(2, a[:3], [2])]).cpu().numpy()
+    for row, (ids, pos) in zip(logits, [(a, 10), (b, 5), (a, 2)]):
+        assert np.abs(row - toy_reference(folder, ids[: pos + 1])[pos]).max() < 1e-4
+    engine.cache.check_consistency()
+
+
 # ----------------------------------------------------------------------------------------
 # A toy feed-forward with routing and a toy position encoding, again defined here only.
 # ----------------------------------------------------------------------------------------

@@ -3,6 +3,7 @@ each request alone and whole; most of it in one step and the last 32 tokens one 
 portions of changing size down to two tokens; and mixed, up to four live requests, portions
 of some beside decoded tokens of others, with so few pages that they are used again.
 In 32-bit and in bfloat16, for three tiny configurations that differ in every size."""
+import json
 import os
 
 import numpy as np
@@ -21,6 +22,13 @@ F32_ABS = 1e-4
 # largest error against the largest logit, and the root-mean-square error against the
 # root-mean-square logit.  Measured: up to 0.072 and 0.036 (configuration B).
 BF16_MAX, BF16_RMS = 0.12, 0.06
+
+
+def bf16_bounds(layers):
+    """(max, rms) bounds of the bfloat16 error, relative to the logits' size, for a model of `layers`
+    layers: every layer's operators round once more, so the error grows with depth."""
+    return BF16_MAX, BF16_RMS
+
 # bfloat16 results of two cuts of the same work go through kernels with other tile shapes
 # and differ by rounding only.
 BF16_CUT = 0.08
@@ -52,14 +60,30 @@ def make_trace(kind, seqs):
     return trace_mixed(seqs, np.random.default_rng(3))
 
 
-def check(got, ref, dtype, seqs):
+def record(**what):
+    """With LAB_ERROR_LOG=FILE in the environment every comparison appends its figures to FILE (the
+    bounds above were set from such a run)."""
+    path = os.environ.get("LAB_ERROR_LOG")
+    if path:
+        with open(path, "a") as fh:
+            fh.write(json.dumps(dict(test=os.environ.get("PYTEST_CURRENT_TEST", ""), **what)) + "\n")
+
+
+def check(got, ref, dtype, seqs, layers=3):
     assert set(got) == {(n, p) for n, ids in seqs.items() for p in range(len(ids))}, "every position was asked for"
+    check_rows(got, ref, dtype, layers)
+
+
+def check_rows(got, ref, dtype, layers=3):
     if dtype == "float32":
         err, scale, where = worst_error(got, ref)
+        record(dtype=dtype, abs=err, scale=scale)
         assert err <= F32_ABS, f"max abs error {err:.3e} at {where} (largest logit {scale:.2f})"
     else:
         mx, rms, where = error_stats(got, ref)
-        assert mx <= BF16_MAX and rms <= BF16_RMS, f"relative max {mx:.3e}, rms {rms:.3e}, worst at {where}"
+        record(dtype=dtype, max=mx, rms=rms, layers=layers)
+        bound_max, bound_rms = bf16_bounds(layers)
+        assert mx <= bound_max and rms <= bound_rms, f"relative max {mx:.3e}, rms {rms:.3e}, worst at {where}"
 
 
 @pytest.mark.parametrize("kind", ["whole", "tail", "portions", "mixed"])
@@ -76,7 +100,7 @@ def test_replay(tmp_path_factory, name, dtype, kind):
                     max_batch_tokens=max(need, 64))
     total_pages = engine.free_pages()
     got = run_trace_inprocess(engine, steps)
-    check(got, ref, dtype, seqs)
+    check(got, ref, dtype, seqs, cfg["num_hidden_layers"])
     assert engine.free_pages() == total_pages and engine.cache.live_requests == 0, "everything was given back"
     engine.cache.check_consistency()
     if kind == "mixed":
@@ -124,28 +148,29 @@ def test_random_configurations_and_traces(tmp_path, seed, dtype):
     if seed % 3 == 1:
         engine.enable_step_graphs()
     got = run_trace_inprocess(engine, steps)
-    check(got, plain_logits(folder, seqs), dtype, seqs)
+    check(got, plain_logits(folder, seqs), dtype, seqs, cfg["num_hidden_layers"])
     engine.cache.check_consistency()
     assert engine.cache.live_requests == 0 and engine.free_pages() == [engine.num_pages] * engine.cache.num_groups
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16")])
-def test_trace_run_program(tmp_path_factory, tmp_path, name, dtype):
-    """bin/trace_run as a user starts it: mixed trace, pool sized by --max-tokens."""
+@pytest.mark.parametrize("name,dtype,page", [("A", "float32", None), ("B", "bfloat16", None), ("C", "float32", None),
+                                             ("C", "bfloat16", None), ("A", "float32", 24)])
+def test_trace_run_program(tmp_path_factory, tmp_path, name, dtype, page):
+    """bin/trace_run as a user starts it: mixed trace, pool sized by --max-tokens (counted in units of
+    64 tokens a request, also with pages of 24 tokens, which do not divide 64)."""
     folder, cfg, opt, seqs, ref, _ = model_case(tmp_path_factory, name, dtype)
     steps = make_trace("mixed", seqs)
     # one step in which nothing is wanted: no file may appear for it
     steps[1]["entries"] = [dict(e, want=[]) for e in steps[1]["entries"]]
     skipped = {(e["id"], p) for e in make_trace("mixed", seqs)[1]["entries"] for p in range(len(e["tokens"]))}
-    got = run_trace_program(folder, dtype, steps, str(tmp_path / "out"), tokens_needed(steps))
+    got = run_trace_program(folder, dtype, steps, str(tmp_path / "out"), tokens_needed(steps), page_size=page)
     assert not os.path.exists(tmp_path / "out" / "1.f32")
     assert len(got) + len(skipped) == sum(len(v) for v in seqs.values())
     if dtype == "float32":
         err, scale, where = worst_error(got, ref)
         assert err <= F32_ABS, f"max abs error {err:.3e} at {where}"
     else:
-        mx, rms, where = error_stats(got, ref)
-        assert mx <= BF16_MAX and rms <= BF16_RMS, f"relative max {mx:.3e}, rms {rms:.3e} at {where}"
+        check_rows(got, ref, dtype, cfg["num_hidden_layers"])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -164,7 +189,7 @@ def test_long_decode_and_first_tokens(tmp_path_factory, name, dtype):
               "end": ["long"] if p == n - 1 else []} for p in range(n)]
     engine = Engine(folder, dtype, max_tokens=-(-n // 64) * 64, page_size=opt["page_size"], max_requests=2)
     got = run_trace_inprocess(engine, steps)
-    check(got, ref, dtype, {"long": ids})
+    check(got, ref, dtype, {"long": ids}, cfg["num_hidden_layers"])
     first = {k: v for k, v in got.items() if k[1] < 2}
     if dtype == "float32":
         err, _, where = worst_error(first, ref)
@@ -190,29 +215,166 @@ def test_windowed_group_gives_pages_back(tmp_path_factory):
     engine.cache.check_consistency()
 
 
-def test_qwen25_05b_layer_sizes_in_32_bit(tmp_path):
-    """The benchmark's layer sizes (hidden 896, 14/2 heads of 64, intermediate 4864, vocabulary
-    151,936, theta 1e6, tied head) with two of the 24 layers and N(0, 0.02) weights: the 32-bit
-    engine against the plain implementation, whole and in portions beside decoded tokens."""
+QWEN25_05B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=151936, hidden_size=896,
+                  intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2,
+                  rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=4096, hidden_act="silu",
+                  tie_word_embeddings=True)
+
+
+def thin_wants(steps):
+    """Logits of 151,936 columns: ask for the first and the last place of every portion only."""
+    for st in steps:
+        for e in st["entries"]:
+            e["want"] = sorted({0, len(e["tokens"]) - 1})
+    return steps
+
+
+@pytest.fixture(scope="module", params=["float32", "bfloat16"])
+def case_05b(request, tmp_path_factory):
+    """The benchmark's layer sizes (hidden 896, 14/2 heads of 64, intermediate 4864, vocabulary 151,936,
+    theta 1e6, tied head) with two of the 24 layers and N(0, 0.02) weights; four sequences of 200 to 260
+    tokens and the plain implementation's final hidden states for them (the head is applied to the
+    rows a trace asks for)."""
+    from plain_qwen2 import plain_hidden, read_model_folder
+
+    dtype = request.param
+    folder = make_model_folder(str(tmp_path_factory.mktemp(f"qwen05b_{dtype}")), QWEN25_05B, seed=0, dtype=dtype,
+                               std=0.02, scales={})
+    rng = np.random.default_rng(2)
+    seqs = {f"s{i}": random_tokens(rng, n, QWEN25_05B["vocab_size"]) for i, n in enumerate((230, 201, 260, 215))}
+    pcfg, w = read_model_folder(folder)
+    hidden = {name: plain_hidden(pcfg, w, ids) for name, ids in seqs.items()}
+    head = w["model.embed_tokens.weight"]
+    del w
+    yield dtype, folder, seqs, hidden, head, {}
+
+
+@pytest.mark.parametrize("kind", ["whole", "tail", "portions", "mixed"])
+def test_qwen25_05b_layer_sizes(case_05b, kind):
+    """The engine at the benchmark's layer sizes against the plain implementation under all four ways
+    of cutting, in 32-bit and in bfloat16 (whose whole prompts and long portions run on the tcgen05
+    attention), with a pool so small in the mixed trace that pages are used again."""
     from llm_inference_lab_b200.engine import Engine
 
-    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=151936, hidden_size=896,
-               intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14, num_key_value_heads=2,
-               rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=4096, hidden_act="silu",
-               tie_word_embeddings=True)
+    dtype, folder, seqs, hidden, head, runs = case_05b
+    steps = thin_wants(trace_mixed(seqs, np.random.default_rng(1), max_portion=90, decode_after=0.85)
+                       if kind == "mixed" else make_trace(kind, seqs))
+    need = tokens_needed(steps, page=16)
+    engine = Engine(folder, dtype, max_tokens=need, page_size=16, max_requests=4, max_batch_tokens=max(need, 512))
+    total_pages = engine.free_pages()
+    got = run_trace_inprocess(engine, steps)
+    ref = {}
+    for name in seqs:
+        rows = sorted(p for n, p in got if n == name)
+        ref[name] = dict(zip(rows, hidden[name][rows] @ head.T))
+    check_rows(got, ref, dtype, layers=2)
+    assert engine.free_pages() == total_pages and engine.cache.live_requests == 0
+    engine.cache.check_consistency()
+    if kind == "mixed":
+        asked = sum(-(-len(ids) // 16) for ids in seqs.values())
+        assert asked > 1.2 * total_pages[0], "pages were used again"
+    # cut against cut, on the places both asked for
+    runs[kind] = got
+    if "whole" in runs and kind != "whole":
+        both = [k for k in got if k in runs["whole"]]
+        assert both
+        worst = max(float(np.abs(got[k] - runs["whole"][k]).max()) for k in both)
+        scale = max(float(np.abs(runs["whole"][k]).max()) for k in both)
+        assert worst <= (1e-5 if dtype == "float32" else BF16_CUT * scale), f"cut changed logits by {worst:.3e}"
+
+
+def test_qwen25_05b_all_24_layers_in_32_bit(tmp_path):
+    """Once at full depth: all 24 layers of the benchmark's configuration in 32-bit, one whole prompt of
+    64 tokens, logits at its last 8 places against the plain implementation.  (The slowest test of the
+    suite: it writes and reads two gigabytes of weights; deselect with -k 'not all_24_layers'.)"""
+    from plain_qwen2 import plain_hidden, read_model_folder
+    from llm_inference_lab_b200.engine import Engine, Entry
+
+    cfg = dict(QWEN25_05B, num_hidden_layers=24)
     folder = make_model_folder(str(tmp_path / "m"), cfg, seed=0, dtype="float32", std=0.02, scales={})
-    rng = np.random.default_rng(2)
-    seqs = {"a": random_tokens(rng, 40, cfg["vocab_size"]), "b": random_tokens(rng, 23, cfg["vocab_size"])}
-    ref = plain_logits(folder, seqs)
-    engine = Engine(folder, "float32", max_tokens=256, page_size=16, max_requests=4)
-    for steps in (trace_whole(seqs), trace_mixed(seqs, np.random.default_rng(1), max_portion=7)):
-        for st in steps:   # logits of 151,936 columns: ask for the last place of each portion only
-            for e in st["entries"]:
-                e["want"] = [len(e["tokens"]) - 1]
-        got = run_trace_inprocess(engine, steps)
-        err, scale, where = worst_error(got, ref)
-        assert err <= F32_ABS, f"max abs error {err:.3e} at {where} (largest logit {scale:.2f})"
+    ids = random_tokens(np.random.default_rng(3), 64, cfg["vocab_size"])
+    engine = Engine(folder, "float32", max_tokens=64, page_size=16, max_requests=1)
+    got = engine.step([Entry(0, ids, list(range(56, 64)))]).cpu().numpy()
+    engine.close(0)
+    del engine
+    pcfg, w = read_model_folder(folder)
+    want = plain_hidden(pcfg, w, ids)[56:] @ w["model.embed_tokens.weight"].T
+    err = float(np.abs(got - want).max())
+    record(dtype="float32", abs=err, scale=float(np.abs(want).max()), layers=24)
+    assert err <= F32_ABS, f"max abs error {err:.3e} (largest logit {np.abs(want).max():.2f})"
+
+
+@pytest.mark.parametrize("kind", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_reference_tiny_model(tmp_path_factory, dtype, kind):
+    """The reference's own tiny model (its shape and closed-form weights, rebuilt bit for bit) under the
+    four cuts, held to the reference's own bounds for it: 1e-4 in 32-bit; in bfloat16 0.03 against the
+    32-bit weights' logits and 0.01 between a cut and whole prompts (absolute; the logits are of size 1)."""
+    import reference_tiny as rt
+    from llm_inference_lab_b200.engine import Engine
+
+    key = ("reference_tiny", dtype)
+    if key not in _cache:
+        folder = rt.write_reference_tiny(str(tmp_path_factory.mktemp(f"reftiny_{dtype}")), dtype)
+        exact = rt.write_reference_tiny(str(tmp_path_factory.mktemp(f"reftiny_exact_{dtype}")), "float32")
+        rng = np.random.default_rng(12)
+        seqs = {f"h{i}": list(h) for i, h in enumerate(rt.HISTORIES)}
+        seqs.update({f"r{i}": random_tokens(rng, n, 257) for i, n in enumerate((64, 40, 57, 2, 19, 64))})
+        _cache[key] = (folder, seqs, plain_logits(exact, seqs), {})
+    folder, seqs, ref, runs = _cache[key]
+    steps = make_trace(kind, seqs)
+    need = tokens_needed(steps, page=16)
+    engine = Engine(folder, dtype, max_tokens=need, page_size=16, max_requests=8, max_batch_tokens=max(need, 64))
+    got = run_trace_inprocess(engine, steps)
+    assert set(got) == {(n, p) for n, ids in seqs.items() for p in range(len(ids))}
+    err, scale, where = worst_error(got, ref)
+    record(dtype=dtype, abs=err, scale=scale)
+    assert err <= (rt.F32_ABS if dtype == "float32" else rt.BF16_F32_ABS), f"{err:.3e} at {where} (logits of {scale:.2f})"
     assert engine.cache.live_requests == 0
+    runs[kind] = got
+    if "whole" in runs and kind != "whole":
+        worst = max(float(np.abs(got[k] - runs["whole"][k]).max()) for k in got)
+        assert worst <= (1e-5 if dtype == "float32" else rt.BF16_CUT_ABS), f"cut changed logits by {worst:.3e}"
+
+
+def big_portions(seqs):
+    return trace_portions(seqs, sizes=(130, 70, 2, 90, 65, 129))
+
+
+@pytest.mark.parametrize("kind", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["F", "G"])
+def test_replay_heads_of_64_and_128(tmp_path_factory, name, dtype, kind):
+    """Configurations whose heads are 64 and 128 wide, with sequences of 150 to 440 tokens cut into whole
+    prompts and portions of more than 64 tokens: in bfloat16 these run on the tcgen05 attention, which
+    here meets the plain model by construction, several layers deep, on peaky attention."""
+    from llm_inference_lab_b200.engine import Engine
+    from llm_inference_lab_b200.kernels import ops
+
+    key = (name, dtype, "long")
+    cfg, opt = TINY[name]
+    if key not in _cache:
+        folder = make_model_folder(str(tmp_path_factory.mktemp(f"tiny{name}_{dtype}")), cfg, opt["seed"], dtype)
+        rng = np.random.default_rng(15)
+        seqs = {f"r{i}": random_tokens(rng, min(n, cfg["max_position_embeddings"]), cfg["vocab_size"])
+                for i, n in enumerate((150, 333, 440, 66, 200, 257))}
+        _cache[key] = (folder, seqs, plain_logits(folder, seqs), {})
+    folder, seqs, ref, runs = _cache[key]
+    steps = {"whole": trace_whole, "tail": trace_tail_decode, "portions": big_portions}.get(
+        kind, lambda s: trace_mixed(s, np.random.default_rng(4), max_portion=140, decode_after=0.9))(seqs)
+    need = tokens_needed(steps, page=opt["page_size"])
+    engine = Engine(folder, dtype, max_tokens=need, page_size=opt["page_size"], max_requests=8,
+                    max_batch_tokens=max(need, 64))
+    before = ops.COUNTER.launches
+    got = run_trace_inprocess(engine, steps)
+    assert ops.COUNTER.launches > before
+    check(got, ref, dtype, seqs, cfg["num_hidden_layers"])
+    assert engine.cache.live_requests == 0 and engine.free_pages() == [engine.num_pages] * engine.cache.num_groups
+    runs[kind] = got
+    if "whole" in runs and kind != "whole":
+        scale = max(float(np.abs(v).max()) for v in runs["whole"].values())
+        worst = max(float(np.abs(got[k] - runs["whole"][k]).max()) for k in got)
+        assert worst <= (1e-5 if dtype == "float32" else BF16_CUT * scale), f"cut changed logits by {worst:.3e}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -237,7 +399,7 @@ def test_steps_replayed_from_cuda_graphs(tmp_path_factory, dtype):
             got[(name, p)] = engine.step([Entry(i, [ids[p]], [0])])[0].float().cpu().numpy()
         engine.close(i)
     assert engine.graph_replays >= 4 * 1 + 5 * 18, "the repeated shapes ran from graphs"
-    check(got, ref, dtype, seqs)
+    check(got, ref, dtype, seqs, cfg["num_hidden_layers"])
     assert engine.cache.live_requests == 0
 
 

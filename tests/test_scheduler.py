@@ -430,3 +430,29 @@ def test_random_workloads_give_the_scripted_tokens_and_every_page_back():
         assert all(cache.free_pages(g) == pages for g in range(len(groups))) and cache.live_requests == 0, where
         cache.check_consistency()
     assert outcomes["preemptions"] > 100 and outcomes["capacity"] > 5 and outcomes["invalid"] > 20, outcomes
+
+
+def test_decoding_requests_never_outnumber_the_budget():
+    """A request decodes only after a portion of its prompt ran, and prompts get what the decoding
+    requests leave of the budget: so the decoding requests of a step never exceed the budget, none
+    of them is ever left out of a step, and a small budget only delays the prompts behind them (the
+    reference's order, batch_policy.rs:36-87).  The tokens equal those of an unconstrained run."""
+    outs = []
+    for budget in (2, 3, 64):
+        cache, sched = make(budget=budget)
+        for rid in range(5):
+            sched.add(rid, [1, 2][: 1 + rid % 2], 6)
+        plans, done = run(sched, next_token=lambda rid, pos: 10 * rid + pos)
+        outs.append({k: v.generated for k, v in done.items()})
+        running = set()
+        for p in plans:
+            assert sum(n for _, _, n, _ in p) <= budget
+            decoding = {rid for rid, start, n, sample in p if rid in running}
+            assert decoding == running, "a decoding request was left out of a step"
+            for rid, start, n, sample in p:
+                if sample:
+                    running.add(rid)
+            running -= {rid for rid in running if any(e[0] == rid and e[1] + e[2] >= len([1, 2][: 1 + rid % 2]) + 5
+                                                      for e in p)}
+        assert cache.free_pages(0) == 64
+    assert outs[0] == outs[1] == outs[2]

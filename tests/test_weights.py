@@ -68,17 +68,22 @@ def test_tied_checkpoint_may_carry_a_head_copy(tmp_path):
 
 
 def test_kept_dtypes(tmp_path):
-    assert kept_dtype(torch.bfloat16) == torch.bfloat16 and kept_dtype(torch.float16) == torch.bfloat16
+    assert kept_dtype(torch.bfloat16) == torch.bfloat16 and kept_dtype(torch.float16) == torch.float32
     assert kept_dtype(torch.float32) == torch.float32 and kept_dtype(torch.float64) == torch.float32
     assert kept_dtype(torch.int64) == torch.int32
     path = str(tmp_path / "t.safetensors")
     save_file({"a": torch.tensor([1.5, -0.0], dtype=torch.float32), "b": torch.arange(4, dtype=torch.int64),
-               "c": torch.tensor([[1.0, 2.0]], dtype=torch.bfloat16)}, path)
+               "c": torch.tensor([[1.0, 2.0]], dtype=torch.bfloat16),
+               "h": torch.tensor([1.0009765625, 3.0e-5], dtype=torch.float16)}, path)
     from llm_inference_lab_b200.parts.spec import TensorSpec
     os.rename(path, str(tmp_path / "model.safetensors"))
-    out = load_weights(str(tmp_path), [TensorSpec("a", (2,)), TensorSpec("b", (4,)), TensorSpec("c", (1, 2))], "cpu")
+    out = load_weights(str(tmp_path), [TensorSpec("a", (2,)), TensorSpec("b", (4,)), TensorSpec("c", (1, 2)),
+                                       TensorSpec("h", (2,))], "cpu")
     assert out["a"].dtype == torch.float32 and out["b"].dtype == torch.int32 and out["c"].dtype == torch.bfloat16
     assert torch.signbit(out["a"][1]) and out["b"].tolist() == [0, 1, 2, 3]
+    # float16 reaches a 32-bit engine exactly (1 + 2^-10 has no bfloat16)
+    assert out["h"].dtype == torch.float32
+    assert out["h"].tolist() == torch.tensor([1.0009765625, 3.0e-5], dtype=torch.float16).float().tolist()
 
 
 def test_sharded_index_and_broken_files(tmp_path):
