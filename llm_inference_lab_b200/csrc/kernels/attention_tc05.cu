@@ -27,9 +27,7 @@
 // zero, because a masked NaN would still poison P V), warp 1 issues the MMAs (the whole warp walks
 // the loop, one elected lane issues) and owns tensor memory, warps 2-5 do the softmax.  Every wait
 // is bounded.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #ifndef LAB_HEAD_DIM
 #error "build with -DLAB_HEAD_DIM=64 or 128"
@@ -59,137 +57,8 @@ constexpr int TM_S = 0, TM_O = 2 * BN, TMEM_COLS = 512;
 static_assert(TM_O + D <= TMEM_COLS, "tensor memory holds S and O");
 constexpr float LOG2E = 1.4426950408889634f;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: gives up after about two seconds, records it, and lets every role drain.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > 2000000000ull) {
-      *abort_flag = 1;
-      lab_set_error(LAB_ERR_WAIT_TIMEOUT);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          smem_dst),
-      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// The MMA and commit wrappers are called by every lane of a converged warp with the same
-// arguments; one elected lane issues the instruction.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile(
-      "{\n\t.reg .pred e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-// The same with the A operand in tensor memory: lane = row, a 32-bit column holds two consecutive
-// bfloat16 elements of K (16 elements of K = 8 columns from a_tmem on).
-__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t a_tmem, uint64_t desc_b, uint32_t idesc,
-                                                 uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
-      "r"(a_tmem), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-// 128-byte-swizzled tile whose rows are 128 bytes; 8-row groups lie 1024 bytes apart.  The same
-// descriptor serves a K-major operand (rows = M or N, 16 elements of K are 32 bytes along the row)
-// and an N-major operand (rows = K, a row holds 64 elements of N).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;            // leading byte offset: one 16-byte unit (a single atom wide)
-  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;            // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;            // 128-byte swizzle
-  return d;
-}
 // bf16 x bf16 -> f32, M = 128, N = n; b_n_major: the B operand is N-major (V as cached) instead of K-major.
-__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_n_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_n_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(BM >> 4) << 24);
-}
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-// 32 consecutive columns of this thread's lane are written from r[0..31].
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_n_major) { return umma_instr_desc(BM, n, b_n_major); }
 
 struct Barriers {
   uint64_t q_full;
@@ -245,13 +114,10 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     }
     mbar_init(&bar->o_full, 1);
     bar->abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bar->tmem_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(&bar->tmem_slot, TMEM_COLS);
   }
   tc_fence_before();
   __syncthreads();
@@ -540,37 +406,8 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = (EncodeTiledFn)sym;
-  }
-  return fn;
-}
-// bf16 matrix [rows, cols] with row stride ld (elements); box = [64 columns, box_rows], 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return (int)cudaErrorNotSupported;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
 }  // namespace
@@ -595,10 +432,10 @@ LAB_EXPORT int lab_attention_prefill_tc05(void* out, int out_stride, const void*
     return (int)cudaErrorInvalidValue;
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = make_map(&mq, q, total_rows, n_q * D, q_stride, BM))) return rc;
+  if ((rc = lab_make_map_bf16(&mq, q, total_rows, n_q * D, q_stride, BM))) return rc;
   const long long cache_rows = (long long)num_pages * n_kv * page_size;
-  if ((rc = make_map(&mk, cache_k, cache_rows, D, D, page_size))) return rc;
-  if ((rc = make_map(&mv, cache_v, cache_rows, D, D, page_size))) return rc;
+  if ((rc = lab_make_map_bf16(&mk, cache_k, cache_rows, D, D, page_size))) return rc;
+  if ((rc = lab_make_map_bf16(&mv, cache_v, cache_rows, D, D, page_size))) return rc;
   static bool configured = false;
   if (!configured) {
     cudaError_t e =

@@ -30,9 +30,7 @@
 // Formulas and rounding order: rust/engine/src/runner/model/qwen2/kernels.rs:156-178,
 // 393-418 (32-bit accumulation, bias added in 32-bit, one rounding), 422-448 and 1469-1486
 // (gate/up with the SiLU product), 300-387 (split-K partials merged in 32-bit).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -41,136 +39,6 @@ constexpr int BK = 64;   // bf16 elements per k-tile: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
-
-// ---- PTX wrappers ----------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: gives up after about two seconds and reports it.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > 2000000000ull) {
-      *abort_flag = 1;
-      lab_set_error(LAB_ERR_WAIT_TIMEOUT);
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
-               "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// The MMA and commit wrappers are called by every lane of a converged warp with the same
-// arguments; one elected lane issues the instruction (measured: about half the issue time of a
-// loop that a single lane walks alone).
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile(
-      "{\n\t.reg .pred e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
-      : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]^T, bf16 inputs, 32-bit accumulate.
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128B-swizzled:
-// 8-row groups lie 1024 bytes apart (stride byte offset), the leading offset is one 16-byte unit.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);  // start address, bits [0, 14)
-  d |= (uint64_t)1 << 16;                  // leading byte offset (16 bytes), bits [16, 30)
-  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset, bits [32, 46)
-  d |= (uint64_t)1 << 46;                  // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                  // layout: 128-byte swizzle
-  return d;
-}
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = m (64 or 128), N = n.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
-      "[%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// 32 consecutive accumulator columns of this thread's lane; the registers are valid after tmem_wait().
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// silu(g) * u in 32-bit on the accumulators, rounded once by the caller (the reference rounds g, u
-// and silu(g) to its storage type first, kernels.rs:1469-1486: fewer roundings only come closer to
-// the exact value); exp and the division use the hardware approximations (relative error about
-// 2^-21, far below bfloat16's 2^-9).
-__device__ __forceinline__ float silu_gate(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 struct Params {
   void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats
@@ -242,7 +110,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(tmem_slot, S::TMEM_COLS);
   tc_fence_before();
@@ -326,7 +194,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   } else if (warp == 1) {
     {
       // ---- MMA issuer: the whole warp walks the loop, one elected lane issues ----
-      constexpr uint32_t idesc = instr_desc(TM, BN);
+      constexpr uint32_t idesc = umma_instr_desc(TM, BN);
       auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
       };
@@ -386,7 +254,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         released = true;
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
       };
       if constexpr (!SWAP) {
         // thread = token row m; columns = output features, 32 at a time
@@ -544,37 +412,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 }
 
 // ---- host side -------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = (EncodeTiledFn)sym;
-  }
-  return fn;
-}
-
-// Map of a row-major bf16 matrix [rows, K] with row stride ld (elements); box = [64, box_rows].
-int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return (int)cudaErrorNotSupported;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
-}
-
 template <int TM, int BN, bool GATED, bool SWAP, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
   using S = Shape<TM, BN, GATED, SWAP>;
@@ -611,6 +448,22 @@ int dispatch_bn(int bm, int bn, const CUtensorMap& ma, const CUtensorMap& mb, co
   return (int)cudaErrorInvalidValue;
 }
 
+// For tests of the bounded waits: one warp waits on a barrier that nobody ever arrives at, with a
+// limit of `limit_ns`.  The wait gives up, the library's error word says that a wait ran out, and the
+// kernel returns; the context stays usable.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    mbar_init_fence();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait(&bar, 0, &abort_flag, limit_ns);
+  if (threadIdx.x == 0) *gave_up = ok ? 0 : 1;
+}
+
 }  // namespace
 
 // x: [tokens, K] bf16 (row stride ldx), w: [n_out (x2 when gated), K] bf16 contiguous.
@@ -640,16 +493,16 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
   int rc;
   if (!swap) {
     const int box_b = gated ? bn / 2 : bn;
-    if ((rc = make_map(&ma, x, tokens, K, ldx, BM))) return rc;
-    if ((rc = make_map(&mb, w, w_rows, K, K, box_b))) return rc;
+    if ((rc = lab_make_map_bf16(&ma, x, tokens, K, ldx, BM))) return rc;
+    if ((rc = lab_make_map_bf16(&mb, w, w_rows, K, K, box_b))) return rc;
     p.m_rows = tokens;
     p.n_rows = n_out;
     p.m_tiles = (tokens + BM - 1) / BM;
     p.n_tiles = (n_out + box_b - 1) / box_b;
   } else {
     const int m_rows_tile = gated ? bm / 2 : bm;
-    if ((rc = make_map(&ma, w, w_rows, K, K, m_rows_tile))) return rc;
-    if ((rc = make_map(&mb, x, tokens, K, ldx, bn))) return rc;
+    if ((rc = lab_make_map_bf16(&ma, w, w_rows, K, K, m_rows_tile))) return rc;
+    if ((rc = lab_make_map_bf16(&mb, x, tokens, K, ldx, bn))) return rc;
     if (gated && bn > 64) return (int)cudaErrorInvalidValue;  // the exchange buffer is sized for up to 64 tokens
     p.m_rows = n_out;
     p.n_rows = tokens;
@@ -682,4 +535,11 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
   }
   if (out_f32) return dispatch_bn<false, false, float>(bm, bn, ma, mb, p, grid, stream);
   return dispatch_bn<false, false, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
+}
+
+// Launches the wait that nothing ends (see wait_probe_kernel); the limit is capped at 50 ms.
+LAB_EXPORT int lab_gemm_tc_wait_probe(unsigned long long limit_ns, int* gave_up, cudaStream_t stream) {
+  if (limit_ns > 50000000ull) limit_ns = 50000000ull;
+  wait_probe_kernel<<<1, 32, 0, stream>>>(limit_ns, gave_up);
+  return (int)cudaGetLastError();
 }

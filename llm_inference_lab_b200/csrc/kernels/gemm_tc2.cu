@@ -25,9 +25,7 @@
 // Formulas and rounding order: rust/engine/src/runner/model/qwen2/kernels.rs:156-178,
 // 393-418 (32-bit accumulation, bias added in 32-bit, one rounding), 422-448 and 1469-1486
 // (gate/up with the SiLU product), 300-387 (split-K partials merged in 32-bit).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -55,7 +53,6 @@ struct Tile {
   static_assert((2 * STAGES + 2 * ACC_BUFS) * 8 + 8 <= 512, "the barriers outgrow their 512 bytes");
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -70,46 +67,9 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
 // Arrival on a barrier of any CTA of the cluster (address in the cluster's shared window).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: gives up after about two seconds and reports it.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > 2000000000ull) {
-      *abort_flag = 1;
-      lab_set_error(LAB_ERR_WAIT_TIMEOUT);
-      return false;
-    }
-  }
 }
 // A tile into this CTA's shared memory; the bytes are counted on `bar_cluster_addr`, a barrier of
 // the pair's leader.  No multicast: each CTA fetches what it holds.
@@ -121,9 +81,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
 // Called by every lane of a converged warp with the same arguments; one elected lane issues.
 // The arrival reaches the barrier at this address in every CTA of `cta_mask`.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
@@ -146,37 +103,6 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128B-swizzled:
-// 8-row groups lie 1024 bytes apart (stride byte offset), the leading offset is one 16-byte unit.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);  // start address, bits [0, 14)
-  d |= (uint64_t)1 << 16;                  // leading byte offset (16 bytes), bits [16, 30)
-  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset, bits [32, 46)
-  d |= (uint64_t)1 << 46;                  // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                  // layout: 128-byte swizzle
-  return d;
-}
-
-// 32 consecutive accumulator columns of this thread's lane; the registers are valid after tmem_wait().
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// silu(g) * u in 32-bit on the accumulators, rounded once by the caller (the reference rounds g, u
-// and silu(g) to its storage type first, kernels.rs:1469-1486: fewer roundings only come closer to
-// the exact value); exp and the division use the hardware approximations (relative error about
-// 2^-21, far below bfloat16's 2^-9).
-__device__ __forceinline__ float silu_gate(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
-
 struct Params {
   void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats
   const __nv_bfloat16* bias;
@@ -221,7 +147,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       mbar_init(&acc_empty[a], 8);  // the four epilogue warps of each CTA
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {
     // one warp of each CTA of the pair, with the same destination: the same columns in both
@@ -264,7 +190,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         for (int i = 0; i < n_kt; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { alive = false; break; }
+          if (!mbar_wait<true>(&empty[s], ph ^ 1, abort_flag)) { alive = false; break; }
           if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
           const uint32_t bar = map_to_rank(smem_u32(&full[s]), 0);
           uint8_t* a_dst = tiles + s * STAGE_BYTES;
@@ -278,7 +204,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     if (leader) {
       // ---- MMA issuer of the pair: the whole warp walks the loop, one elected lane issues ----
       auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
-        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+        return __all_sync(0xffffffffu, mbar_wait<true>(bar, parity, abort_flag));
       };
       int it = 0, local = 0;
       bool ok = true;
@@ -319,7 +245,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       locate(tile, m0, n0, kt0, n_kt, split);
       const int buf = local % ACC_BUFS;
       const uint32_t use = (uint32_t)(local / ACC_BUFS);
-      const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag);
+      const bool ok = mbar_wait<true>(&acc_full[buf], use & 1, abort_flag);
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
       const int m = m0 + (int)rank * BM + quarter * 32 + lane;  // this thread's token row
@@ -419,36 +345,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
 }
 
 // ---- host side -------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = (EncodeTiledFn)sym;
-  }
-  return fn;
-}
-
-// Map of a row-major bf16 matrix [rows, K] with row stride ld (elements); box = [64, box_rows].
-int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return (int)cudaErrorNotSupported;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
-}
 
 template <bool GATED, typename OutT, int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, long long tiles, cudaStream_t stream) {
@@ -551,8 +447,8 @@ LAB_EXPORT int lab_gemm_tc2(void* out, const void* x, const void* w, const void*
   const int w_rows = gated ? 2 * n_out : n_out;
   CUtensorMap ma, mb;
   int rc;
-  if ((rc = make_map(&ma, x, tokens, K, ldx, BM))) return rc;
-  if ((rc = make_map(&mb, w, w_rows, K, K, bn / 2))) return rc;
+  if ((rc = lab_make_map_bf16(&ma, x, tokens, K, ldx, BM))) return rc;
+  if ((rc = lab_make_map_bf16(&mb, w, w_rows, K, K, bn / 2))) return rc;
   Params p;
   p.out = out;
   p.bias = (const __nv_bfloat16*)bias;

@@ -449,34 +449,6 @@ LAB_EXPORT int lab_rope_kv_write(void* qkv, int row_stride, const float* partial
 }
 
 // ----------------------------------------------------------------------------------------
-// out = T( silu(gate) * up ) for separately stored gate and up (kernels.rs:1469-1486).
-// gate_up: [tokens, 2 * inter] with gate in the first half of each row.
-// ----------------------------------------------------------------------------------------
-template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
-  pdl_trigger();
-  pdl_wait();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const size_t t = i / inter, c = i - t * inter;
-  const float g = to_f32<T>(gate_up[t * 2 * inter + c]);
-  const float u = to_f32<T>(gate_up[t * 2 * inter + inter + c]);
-  out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
-}
-
-LAB_EXPORT int lab_silu_mul(void* out, const void* gate_up, int tokens, int inter, int dtype, cudaStream_t stream) {
-  const size_t total = (size_t)tokens * inter;
-  if (total == 0) return 0;
-  const int threads = 256;
-  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  if (dtype == LAB_F32)
-    return (int)lab_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)out,
-                           (const float*)gate_up, inter, total);
-  return (int)lab_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out,
-                         (const __nv_bfloat16*)gate_up, inter, total);
-}
-
-// ----------------------------------------------------------------------------------------
 // A copy from pinned host memory to the device on a stream: what a step's metadata takes.  Called
 // directly, it costs the host a fraction of what the same copy costs through a tensor library.
 // ----------------------------------------------------------------------------------------

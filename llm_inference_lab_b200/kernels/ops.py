@@ -129,6 +129,16 @@ def take_device_errors() -> None:
                               f"{DEVICE_ERRORS.get(out.value, out.value)}")
 
 
+def wait_probe(limit_ms: float = 2.0) -> bool:
+    """Runs the tensor-core product library's test kernel whose wait nothing ends, with a limit of
+    `limit_ms` (50 at most).  Returns True if the wait gave up, as it must; the library's error word
+    then says that a bounded wait ran out (`take_device_errors` raises)."""
+    flag = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    _check(lib("gemm_tc").lab_gemm_tc_wait_probe(ctypes.c_ulonglong(int(limit_ms * 1e6)), _ptr(flag), _stream()),
+           "wait_probe")
+    return bool(flag.item())
+
+
 # ----------------------------------------------------------------------------------------
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     _on_gpu(ids, table)
@@ -225,16 +235,6 @@ def rope_kv_write_table(qkv, table, rotary_dim, slots, cache_k, cache_v, n_q, n_
     return qkv[:, : n_q * head_dim]
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    tokens, two_i = gate_up.shape
-    inter = two_i // 2
-    if out is None:
-        out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
-    _check(lib("rowwise").lab_silu_mul(_ptr(out), _ptr(gate_up), tokens, inter, dtype_code(gate_up.dtype), _stream()),
-           "silu_mul")
-    return out
-
-
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
                out_f32: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
     """out = x @ w.T (+ bias) on the ordinary arithmetic units; `gated`: silu(x@wg.T) * (x@wu.T), w = [wg; wu]."""
@@ -317,7 +317,19 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seeds:
 # the plain kernels as well, which tests use to tell a kernel fault from a model fault.
 # ----------------------------------------------------------------------------------------
 _force_plain = False
-SM_COUNT = 148
+_sm_count = 0
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (the host's choices of tiles and splits go by
+    it, as the kernels' own grids do); 148, a B200's, where no device is present."""
+    global _sm_count
+    if _sm_count == 0:
+        if torch.cuda.is_available():
+            _sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+        else:
+            _sm_count = 148
+    return _sm_count
 
 
 def force_plain(flag: bool) -> bool:
@@ -423,9 +435,9 @@ def _pick_splits(T: int, n_out: int, K: int) -> int:
         return 1
     tiles = -(-n_out // 128)
     k_tiles = -(-K // 64)
-    if tiles >= SM_COUNT // 2 or k_tiles < 8:
+    if tiles >= sm_count() // 2 or k_tiles < 8:
         return 1
-    return max(1, min(-(-k_tiles // 4), SM_COUNT // tiles, 16))   # about 4 k-tiles per CTA (measured best)
+    return max(1, min(-(-k_tiles // 4), sm_count() // tiles, 16))   # about 4 k-tiles per CTA (measured best)
 
 
 def _pick_prefill_tiles(T: int, n_out: int, K: int, allow_partial: bool) -> tuple[str, int, int]:
@@ -447,10 +459,10 @@ def _pick_prefill_tiles(T: int, n_out: int, K: int, allow_partial: bool) -> tupl
     if k_tiles >= 32 and pairs >= 48:
         return "pair", 256, 1
     t128, t256 = m_tiles * (-(-n_out // 128)), m_tiles * (-(-n_out // 256))
-    if t128 <= SM_COUNT:
-        splits = max(1, min(SM_COUNT // t128, k_tiles // 16)) if allow_partial else 1
+    if t128 <= sm_count():
+        splits = max(1, min(sm_count() // t128, k_tiles // 16)) if allow_partial else 1
         return "tc", 128, splits
-    if -(-t256 // SM_COUNT) * 600 < -(-t128 // SM_COUNT) * 420:
+    if -(-t256 // sm_count()) * 600 < -(-t128 // sm_count()) * 420:
         return "tc", 256, 1
     return "tc", 128, 1
 
@@ -536,10 +548,10 @@ def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int, keys_pe
     ways, rust/engine/src/runner/model/qwen2/engine.rs:1597-1617)."""
     ctas = max(1, n_decode * n_kv * (-(-group // 16)))
     if CLUSTER_MERGE and max_kv_len <= 16 * keys_per_round:     # beyond that, more than 8 splits serve better
-        fine = min(8, -(-max_kv_len // keys_per_round), SM_COUNT // ctas)
+        fine = min(8, -(-max_kv_len // keys_per_round), sm_count() // ctas)
         if fine >= 2:
             return int(fine)
-    room = max(1, (ctas_per_sm * SM_COUNT) // ctas)      # no second round of CTAs
+    room = max(1, (ctas_per_sm * sm_count()) // ctas)      # no second round of CTAs
     return int(max(1, min(room, -(-max_kv_len // (2 * keys_per_round)), 32)))
 
 
@@ -578,7 +590,7 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
             span = min(max_kv_len, window) if window else max_kv_len
             splits = decode_splits(n_decode, n_kv, n_q // n_kv, span, *decode_shape(head_dim))
         ctas = n_decode * n_kv * (-(-(n_q // n_kv) // 16)) * splits
-        in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and ctas <= SM_COUNT
+        in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and ctas <= sm_count()
         if splits > 1 and not in_cluster:
             need = n_requests * n_q * splits * (head_dim + 2)
             if scratch is None or scratch.numel() < need:
@@ -635,7 +647,7 @@ def attention_decode_fused(qkv, bias, inv_freq, rotary_dim, slots, cache_k, cach
         span = min(max_kv_len, window) if window else max_kv_len
         splits = decode_splits(n_requests, n_kv, n_q // n_kv, span, *decode_shape(head_dim))
     scratch = counters = None
-    in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and n_requests * n_kv * splits <= SM_COUNT
+    in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and n_requests * n_kv * splits <= sm_count()
     if splits > 1 and not in_cluster:
         scratch = torch.empty((n_requests * n_q * splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
         counters = _counters(qkv.device, n_requests * n_kv)

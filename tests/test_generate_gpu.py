@@ -2,13 +2,14 @@
 implementation: greedy tokens, temperature sampling with a seed, continuous batching with
 portions of prompts, end-of-sequence, and preemption when pages run out."""
 import json
+import os
 import subprocess
 import sys
 
 import numpy as np
 import pytest
 
-from helpers import ROOT, TINY, make_model_folder, random_tokens
+from helpers import ROOT, TINY, make_model_folder, random_config, random_tokens
 from plain_qwen2 import plain_forward, plain_greedy, plain_sample, read_model_folder
 
 pytestmark = pytest.mark.gpu
@@ -192,6 +193,10 @@ def test_lookahead_decoding_gives_the_same_tokens(tmp_path_factory, dtype):
         llm = LLM(folder, short, page_size=opt["page_size"], kv_tokens=512, max_requests=4, cuda_graph=True,
                   lookahead=ahead)
         free = llm.generate(prompts, SamplingConfig(max_new_tokens=24, ignore_eos=True))
+        if dtype == "float32":
+            pcfg, w = read_model_folder(folder)
+            for prompt, res in zip(prompts, free):
+                assert res.tokens == plain_greedy(pcfg, w, prompt, 24), "graphs and lookahead against the plain model"
         # end tokens taken from the free run: every request stops somewhere in the middle
         configs = [SamplingConfig(max_new_tokens=5 + 4 * i, eos_token_id=free[i].tokens[3 + i], temperature=0.7,
                                   do_sample=(i % 2 == 1), seed=5 + i) for i in range(len(prompts))]
@@ -236,3 +241,42 @@ def test_temperatures_and_seeds_follow_a_batch_from_graph_to_graph(tmp_path_fact
         assert tokens == plain_greedy(pcfg, w, prompt, 20)
     for prompt, tokens in zip(prompts, outs[True][0]):
         check_teacher_forced(folder, prompt, tokens, 0.8, 13, 1e-4)
+
+
+@pytest.mark.parametrize("trial", range(int(os.environ.get("LAB_RANDOM_GENERATE", "12"))))
+def test_random_generation_schedules(tmp_path, trial):
+    """Random configurations, pool sizes, token budgets and options through `LLM.generate` in 32-bit:
+    with and without reservation (so some runs preempt and recompute), decode graphs, lookahead, an
+    end-of-sequence id, requests that arrive in a second call while nothing of the first is left.
+    Greedy tokens equal the plain implementation's and every page comes back.  (An earlier, longer run
+    of this generator found that the step function counted the scheduler's reserved tokens twice.)
+    LAB_RANDOM_GENERATE=200 in the environment runs that many trials instead of twelve."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    rng = np.random.default_rng(9000 + trial)
+    cfg, page = random_config(rng)
+    cfg["max_position_embeddings"] = min(cfg["max_position_embeddings"], 200)
+    vocab = cfg["vocab_size"]
+    prompts, news = [], []
+    for _ in range(int(rng.integers(1, 7))):
+        n_new = int(rng.integers(0, 20))
+        prompts.append(random_tokens(rng, int(rng.integers(1, cfg["max_position_embeddings"] - n_new)), vocab))
+        news.append(n_new)
+    eos = int(rng.integers(0, vocab)) if rng.random() < 0.5 else None
+    cfg["eos_token_id"] = eos
+    graph, ahead, reserve = bool(rng.random() < 0.6), bool(rng.random() < 0.7), bool(rng.random() < 0.5)
+    rounded = [-(-(len(p) + n) // page) * page for p, n in zip(prompts, news)]
+    kv_tokens = int(rng.integers(max(rounded), max(sum(rounded), max(rounded)) + 1))
+    folder = make_model_folder(str(tmp_path / "m"), cfg, trial, "float32")
+    pcfg, w = read_model_folder(folder)
+    llm = LLM(folder, "f32", max_batch_tokens=int(rng.choice([8, 16, 64, 512])), kv_tokens=kv_tokens, page_size=page,
+              max_requests=8, reserve_future=reserve, cuda_graph=graph, lookahead=ahead)
+    results = llm.generate(prompts, [SamplingConfig(max_new_tokens=n) for n in news])
+    late = llm.generate(prompts[:2], [SamplingConfig(max_new_tokens=n) for n in news[:2]])
+    what = f"page {page}, pool {kv_tokens}, graph {graph}, lookahead {ahead}, reservation {reserve}"
+    for prompt, n, res in zip(prompts + prompts[:2], news + news[:2], results + late):
+        assert res.tokens == plain_greedy(pcfg, w, prompt, n, eos=() if eos is None else (eos,)), what
+    llm.engine.cache.check_consistency()
+    assert llm.engine.cache.live_requests == 0 and llm.engine.free_pages() == [llm.engine.num_pages] * \
+        llm.engine.cache.num_groups, what

@@ -295,6 +295,23 @@ def test_gemm_tc_guards():
         ops().gemm_tc(x[:, :70], w[:, :70].contiguous())   # K is not a multiple of 8: refused, not wrong
 
 
+def test_a_bounded_wait_runs_out_and_the_gpu_stays_usable():
+    """Every wait inside the tensor-core kernels has a limit.  A test kernel of the product library
+    waits, with the same wait function and a limit of two milliseconds, on a barrier at which nobody
+    arrives: the wait gives up, the kernel returns, the error word says so, and a product launched
+    right after on the same stream is exact."""
+    assert ops().wait_probe(limit_ms=2.0), "the wait gave up"
+    with pytest.raises(ops().KernelError, match="bounded wait"):
+        ops().take_device_errors()
+    ops().take_device_errors()          # reading the word cleared it
+    g = torch.Generator().manual_seed(8)
+    x = (torch.randint(-4, 5, (70, 200), generator=g).float() / 4).bfloat16()
+    w = (torch.randint(-4, 5, (130, 200), generator=g).float() / 8).bfloat16()
+    out = ops().gemm_tc(x.to(DEV), w.to(DEV), out_f32=True)
+    ops().take_device_errors()
+    assert torch.equal(out.double().cpu(), x.double() @ w.double().T)
+
+
 # ----------------------------------------------------------------------------------------
 # Attention over pages
 # ----------------------------------------------------------------------------------------

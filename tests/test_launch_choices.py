@@ -15,7 +15,7 @@ def test_decode_splits_fit_the_gpu_and_the_cluster():
         assert 1 <= s <= 32
         if s > 1:
             assert (s - 1) * keys < kv, "a split without keys"
-            assert ctas * s <= per_sm * ops.SM_COUNT, "a second round of CTAs"
+            assert ctas * s <= per_sm * ops.sm_count(), "a second round of CTAs"
 
 
 def test_decode_splits_short_contexts_are_not_split():
@@ -56,4 +56,4 @@ def test_prefill_tiles_are_always_a_shape_the_kernels_take():
             assert splits == 1
         if splits > 1:
             assert -(-K // 64) // splits >= 16, "a split with too few k-tiles"
-            assert -(-T // 128) * -(-n_out // bn) * splits <= ops.SM_COUNT
+            assert -(-T // 128) * -(-n_out // bn) * splits <= ops.sm_count()

@@ -20,14 +20,18 @@ F32_ABS = 1e-4
 # bfloat16: activations are rounded at every operator boundary, and random weights make the
 # head's sums cancel, so the error is judged relative to the size of the logits: the
 # largest error against the largest logit, and the root-mean-square error against the
-# root-mean-square logit.  Measured: up to 0.072 and 0.036 (configuration B).
-BF16_MAX, BF16_RMS = 0.12, 0.06
+# root-mean-square logit.  Every layer's operators round once more, so the bounds go by depth.
+# From a recorded run (LAB_ERROR_LOG) of every comparison in this file, (max, rms): one layer up to
+# 0.018 / 0.011 (0.046 / 0.016 over 500 random configurations); two layers 0.009 / 0.008 on
+# configuration A and the 0.5B sizes, 0.076 / 0.027 on configuration F (peaky attention over 440 keys);
+# three layers 0.058 / 0.029 (B), 0.071 / 0.034 (B from graphs), 0.102 / 0.033 (G); four 0.043 / 0.024 (C).
+BF16_BY_DEPTH = {1: (0.05, 0.02), 2: (0.09, 0.035)}
+BF16_MAX, BF16_RMS = 0.12, 0.045      # three layers and more
 
 
 def bf16_bounds(layers):
-    """(max, rms) bounds of the bfloat16 error, relative to the logits' size, for a model of `layers`
-    layers: every layer's operators round once more, so the error grows with depth."""
-    return BF16_MAX, BF16_RMS
+    """(max, rms) bounds of the bfloat16 error, relative to the logits' size, for a model of `layers` layers."""
+    return BF16_BY_DEPTH.get(layers, (BF16_MAX, BF16_RMS))
 
 # bfloat16 results of two cuts of the same work go through kernels with other tile shapes
 # and differ by rounding only.
@@ -232,7 +236,7 @@ def thin_wants(steps):
 @pytest.fixture(scope="module", params=["float32", "bfloat16"])
 def case_05b(request, tmp_path_factory):
     """The benchmark's layer sizes (hidden 896, 14/2 heads of 64, intermediate 4864, vocabulary 151,936,
-    theta 1e6, tied head) with two of the 24 layers and N(0, 0.02) weights; four sequences of 200 to 260
+    theta 1e6, tied head) with two of the 24 layers and N(0, 0.02) weights; seven sequences of 200 to 260
     tokens and the plain implementation's final hidden states for them (the head is applied to the
     rows a trace asks for)."""
     from plain_qwen2 import plain_hidden, read_model_folder
@@ -241,7 +245,7 @@ def case_05b(request, tmp_path_factory):
     folder = make_model_folder(str(tmp_path_factory.mktemp(f"qwen05b_{dtype}")), QWEN25_05B, seed=0, dtype=dtype,
                                std=0.02, scales={})
     rng = np.random.default_rng(2)
-    seqs = {f"s{i}": random_tokens(rng, n, QWEN25_05B["vocab_size"]) for i, n in enumerate((230, 201, 260, 215))}
+    seqs = {f"s{i}": random_tokens(rng, n, QWEN25_05B["vocab_size"]) for i, n in enumerate((230, 201, 260, 215, 207, 240, 222))}
     pcfg, w = read_model_folder(folder)
     hidden = {name: plain_hidden(pcfg, w, ids) for name, ids in seqs.items()}
     head = w["model.embed_tokens.weight"]
@@ -257,7 +261,7 @@ def test_qwen25_05b_layer_sizes(case_05b, kind):
     from llm_inference_lab_b200.engine import Engine
 
     dtype, folder, seqs, hidden, head, runs = case_05b
-    steps = thin_wants(trace_mixed(seqs, np.random.default_rng(1), max_portion=90, decode_after=0.85)
+    steps = thin_wants(trace_mixed(seqs, np.random.default_rng(1), max_live=3, max_portion=90, decode_after=0.85)
                        if kind == "mixed" else make_trace(kind, seqs))
     need = tokens_needed(steps, page=16)
     engine = Engine(folder, dtype, max_tokens=need, page_size=16, max_requests=4, max_batch_tokens=max(need, 512))
@@ -309,7 +313,9 @@ def test_qwen25_05b_all_24_layers_in_32_bit(tmp_path):
 def test_reference_tiny_model(tmp_path_factory, dtype, kind):
     """The reference's own tiny model (its shape and closed-form weights, rebuilt bit for bit) under the
     four cuts, held to the reference's own bounds for it: 1e-4 in 32-bit; in bfloat16 0.03 against the
-    32-bit weights' logits and 0.01 between a cut and whole prompts (absolute; the logits are of size 1)."""
+    32-bit weights' logits, and 0.01 between a cut and whole prompts on the reference's own histories
+    (absolute; the logits are of size 1).  Random sequences up to the model's 64 positions run beside
+    them; between cuts they are held to this file's own band."""
     import reference_tiny as rt
     from llm_inference_lab_b200.engine import Engine
 
@@ -333,8 +339,11 @@ def test_reference_tiny_model(tmp_path_factory, dtype, kind):
     assert engine.cache.live_requests == 0
     runs[kind] = got
     if "whole" in runs and kind != "whole":
+        own = max(float(np.abs(got[k] - runs["whole"][k]).max()) for k in got if k[0].startswith("h"))
         worst = max(float(np.abs(got[k] - runs["whole"][k]).max()) for k in got)
-        assert worst <= (1e-5 if dtype == "float32" else rt.BF16_CUT_ABS), f"cut changed logits by {worst:.3e}"
+        record(dtype=dtype, cut_own=own, cut_all=worst)
+        assert own <= (1e-5 if dtype == "float32" else rt.BF16_CUT_ABS), f"cut changed logits by {own:.3e}"
+        assert worst <= (1e-5 if dtype == "float32" else BF16_CUT * scale), f"cut changed logits by {worst:.3e}"
 
 
 def big_portions(seqs):
@@ -446,4 +455,5 @@ def test_qwen25_05b_layer_sizes_long_prompt_in_bfloat16(tmp_path):
         worst = max(float(np.abs(got[k] - ref[k]).max()) for k in ref)
         rms = float(np.sqrt(np.mean([np.mean((got[k] - ref[k]) ** 2) for k in ref])))
         ref_rms = float(np.sqrt(np.mean([np.mean(ref[k] ** 2) for k in ref])))
-        assert worst <= BF16_MAX * scale and rms <= BF16_RMS * ref_rms, (cut, worst / scale, rms / ref_rms)
+        bound_max, bound_rms = bf16_bounds(2)
+        assert worst <= bound_max * scale and rms <= bound_rms * ref_rms, (cut, worst / scale, rms / ref_rms)
