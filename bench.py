@@ -136,8 +136,11 @@ def prefill_flops(cfg, layers, tokens):
     return linear + attention
 
 
-def run_decode(engine, graphs, batch, steps, warmup, rng, clocks=None):
-    """Prefill `batch` prompts of PROMPT_LEN tokens, then time `steps` decode steps (device feedback)."""
+def run_decode(engine, graphs, batch, steps, warmup, rng, clocks=None, repeats=1):
+    """Prefill `batch` prompts of PROMPT_LEN tokens, then time `steps` decode steps `repeats` times
+    (device feedback: the sampled ids stay on the device).  `graphs` None: every step is launched
+    kernel by kernel (eager) instead of replayed from a CUDA graph.  Returns a list of
+    (ms of the region, launches, mean context length) per repeat."""
     import torch
     from llm_inference_lab_b200.engine import Entry
     from llm_inference_lab_b200.kernels import ops
@@ -149,31 +152,70 @@ def run_decode(engine, graphs, batch, steps, warmup, rng, clocks=None):
         prompt = [int(t) for t in rng.integers(0, vocab, PROMPT_LEN)]
         logits = engine.step([Entry(r, prompt, [PROMPT_LEN - 1])])
         first.append(int(logits.argmax(dim=-1).item()))
-    out = graphs.step(ids, tokens=first)
+    if graphs is not None:
+        out = graphs.step(ids, tokens=first)
+        step = lambda: graphs.step(ids)  # noqa: E731
+    else:
+        eager = EagerDecode(engine, ids, first)
+        out = eager.step()
+        step = eager.step
     for _ in range(max(warmup - 1, 0)):
-        out = graphs.step(ids)
+        out = step()
     torch.cuda.synchronize()
-    ctx0 = engine.cache.length(ids[0])
-    launches0 = ops.COUNTER.launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    regions = []
     if clocks is not None:
         clocks.__enter__()
-    e0.record()
-    for _ in range(steps):
-        out = graphs.step(ids)
-    e1.record()
-    torch.cuda.synchronize()
+    for _ in range(repeats):
+        ctx0 = engine.cache.length(ids[0])
+        launches0 = ops.COUNTER.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            out = step()
+        e1.record()
+        torch.cuda.synchronize()
+        regions.append((e0.elapsed_time(e1), ops.COUNTER.launches - launches0, ctx0 + (steps + 1) / 2.0))
     if clocks is not None:
         clocks.__exit__(None, None, None)
-    ms = e0.elapsed_time(e1)
-    launches = ops.COUNTER.launches - launches0
     tokens = out.cpu().tolist()
     assert all(0 <= t < vocab for t in tokens), "decode produced an invalid token"
-    mean_ctx = ctx0 + (steps + 1) / 2.0
     ops.take_device_errors()
     for r in ids:
         engine.close(r)
-    return ms, launches, mean_ctx
+    return regions
+
+
+class EagerDecode:
+    """Decode steps launched kernel by kernel through `Engine.step`, the sampled ids fed forward on
+    the device (the host never reads them): the eager twin of the decode graphs, for the figure the
+    reference reports beside its graph mode (roadmap.md:653-656)."""
+
+    def __init__(self, engine, ids, first):
+        import torch
+        self.engine, self.ids = engine, ids
+        self.tokens = torch.tensor(first, dtype=torch.int32, device=engine.device)
+        self.rows = torch.arange(len(ids), dtype=torch.int32, device=engine.device)
+
+    def step(self):
+        from llm_inference_lab_b200.kernels import ops
+        eng = self.engine
+        pairs = [(r, 1) for r in self.ids]
+        began = eng._begin(pairs, False)
+        try:
+            ctx, _ = eng._pack_pairs(pairs, self.tokens)
+            logits = eng.model.forward(ctx, eng.views, self.rows)
+            ops.sample(logits, None, None, None, out=self.tokens)
+        except Exception:
+            eng._fail(began)
+            raise
+        eng._end(pairs, False)
+        return self.tokens
+
+
+def median_region(regions):
+    ordered = sorted(regions, key=lambda r: r[0])
+    return ordered[len(ordered) // 2]
 
 
 def run_prefill(engine, rng, repeats=5):
@@ -212,7 +254,7 @@ def run_e2e(folder, batch, steps, warmup):
     llm.step_log.clear()
     results = llm.generate(prompts, SamplingConfig(max_new_tokens=n_new, ignore_eos=True))
     assert all(len(r.tokens) == n_new for r in results)
-    decode = [(t, n) for t, n, is_decode in llm.step_log if is_decode and n == batch]
+    decode = [(t, n) for t, n, is_decode, _ in llm.step_log if is_decode and n == batch]
     timed = decode[warmup: warmup + steps + 1]
     k = len(timed) - 1
     seconds = timed[-1][0] - timed[0][0]
@@ -225,7 +267,7 @@ def run_e2e(folder, batch, steps, warmup):
             "note": "LLM.generate; each step is launched one step ahead of the host's read of the sampled ids"}
 
 
-def run_serve(folder, requests, chunk, new_tokens, max_seq, lo=128, hi=2048):
+def run_serve(folder, cfg, layers, requests, chunk, new_tokens, max_seq, lo=128, hi=2048, graph=True):
     """Continuous batching through LLM.generate: `requests` prompts of lo..hi tokens arrive at once, prompts
     are cut into portions under a budget of `chunk` tokens a step (decoding requests first), and every
     request decodes `new_tokens` tokens.  Timed on the host around the whole call, after two untimed
@@ -239,7 +281,7 @@ def run_serve(folder, requests, chunk, new_tokens, max_seq, lo=128, hi=2048):
     lengths = [int(n) for n in rng.integers(lo, hi + 1, requests)]
     need = sum(-(-(n + new_tokens) // PAGE_SIZE) * PAGE_SIZE for n in lengths)
     llm = LLM(folder, "bf16", max_batch_tokens=chunk, page_size=PAGE_SIZE, kv_tokens=need + 64 * PAGE_SIZE,
-              max_requests=requests, max_seq_len=max_seq, cuda_graph=True)
+              max_requests=requests, max_seq_len=max_seq, cuda_graph=graph)
     prompts = [[int(t) for t in rng.integers(0, llm.engine.vocab, n)] for n in lengths]
     sampling = SamplingConfig(max_new_tokens=new_tokens, ignore_eos=True)
     for _ in range(2):      # the second run captures the step shapes that came twice
@@ -247,28 +289,48 @@ def run_serve(folder, requests, chunk, new_tokens, max_seq, lo=128, hi=2048):
     torch.cuda.synchronize()
     llm.step_log.clear()
     steps0 = llm.steps
+    replays0 = (llm.graphs.replays if llm.graphs else 0, llm.engine.graph_replays)
     t0 = time.perf_counter()
     results = llm.generate(prompts, sampling)
     torch.cuda.synchronize()
     seconds = time.perf_counter() - t0
     assert all(r.finish_reason == "length" and len(r.tokens) == new_tokens for r in results)
     generated = requests * new_tokens
-    decode_steps = sum(1 for _, _, is_decode in llm.step_log if is_decode)
+    steps = llm.steps - steps0
+    log = llm.step_log
+    decode_steps = sum(1 for _, _, is_decode, _ in log if is_decode)
+    from_graphs = ((llm.graphs.replays if llm.graphs else 0) - replays0[0]) + (llm.engine.graph_replays - replays0[1])
+    # Pure decode steps against the HBM roofline: the bytes each has to read (every weight once and
+    # the cache of its requests) over the time between its tokens and the previous step's reaching
+    # the host (steps run back to back, one launched ahead).
+    nbytes = seconds_decode = 0.0
+    for prev, cur in zip(log, log[1:]):
+        if cur[2] and prev[2]:
+            nbytes += decode_bytes(cfg, layers, 0, 0) + kv_bytes_per_token(cfg, layers) * cur[3]
+            seconds_decode += cur[0] - prev[0]
     return {"workload": f"continuous batching: {requests} requests at once, prompts of {lo}..{hi} tokens, "
                         f"{chunk} tokens a step, {new_tokens} new tokens each",
             "seconds": round(seconds, 4), "prompt_tokens": sum(lengths), "generated_tokens": generated,
             "total_tokens_per_s": round((sum(lengths) + generated) / seconds, 1),
             "generated_tokens_per_s": round(generated / seconds, 1),
-            "steps": llm.steps - steps0, "pure_decode_steps": decode_steps,
+            "steps": steps, "pure_decode_steps": decode_steps,
+            "steps_from_graphs": from_graphs, "eager_share": round(1.0 - from_graphs / max(steps, 1), 4),
+            "ms_per_step": round(1e3 * seconds / max(steps, 1), 4),
+            "decode_hbm_gbs": round(nbytes / max(seconds_decode, 1e-9) / 1e9, 1),
             "ttft_ms_median": round(1e3 * statistics.median(r.ttft for r in results), 2),
             "preemptions": sum(r.preemptions for r in results)}
+
+
+def kv_bytes_per_token(cfg, layers):
+    d = cfg["hidden_size"] // cfg["num_attention_heads"]
+    return 2 * layers * 2 * cfg["num_key_value_heads"] * d
 
 
 def main() -> int:
     global PROMPT_LEN, PREFILL_TOKENS
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0,
@@ -279,6 +341,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the prefill")
     ap.add_argument("--skip-e2e", action="store_true", help="leave out the run through LLM.generate")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time decode steps launched kernel by kernel instead of replayed from CUDA graphs")
     ap.add_argument("--serve", type=int, default=0, metavar="REQUESTS",
                     help="instead of the headline run: REQUESTS prompts of 128..2,048 tokens through LLM.generate "
                          "with 512 tokens a step and 128 new tokens each (continuous batching); prints its own line")
@@ -311,9 +375,15 @@ def main() -> int:
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()
     if args.serve:
-        out = run_serve(folder, args.serve, 512, 128, max(max_seq, 2048 + 128 + PAGE_SIZE))
+        clocks = ClockSampler()
+        with clocks:
+            out = run_serve(folder, cfg, args.layers, args.serve, 512, 128, max(max_seq, 2048 + 128 + PAGE_SIZE),
+                            graph=not args.no_graph)
+        out["decode_hbm_frac"] = round(out["decode_hbm_gbs"] / pk["hbm_gbs"], 4)
         out.update({"model": f"Qwen2.5-{args.shape} shape", "layers": args.layers,
-                    "layers_of_config": cfg["num_hidden_layers"], "dtype": "bf16"})
+                    "layers_of_config": cfg["num_hidden_layers"], "dtype": "bf16",
+                    "mode": "eager launches" if args.no_graph else "cuda graphs", "peaks": pk_src,
+                    "clocks": clocks.summary()})
         print(json.dumps(out))
         return 0
     rng = np.random.default_rng(0)
@@ -329,8 +399,12 @@ def main() -> int:
                           "tokens_per_s": round(PREFILL_TOKENS / (pms / 1e3), 1)}))
         return 0
 
+    # The timed region (K steps between two events) is taken R times in a row, as far as the requests'
+    # budgets of new tokens allow; the line reports the median region, with the fastest and the slowest.
+    repeats = max(1, min(5, (NEW_TOKENS - warmup - 2) // steps))
     clocks = ClockSampler()
-    ms, launches, mean_ctx = run_decode(engine, graphs, args.batch, steps, warmup, rng, clocks)
+    regions = run_decode(engine, None if args.no_graph else graphs, args.batch, steps, warmup, rng, clocks, repeats)
+    ms, launches, mean_ctx = median_region(regions)
     value = args.batch * steps / (ms / 1e3)
     nbytes = decode_bytes(cfg, args.layers, args.batch, mean_ctx)
     achieved = nbytes / (ms / steps / 1e3) / 1e9
@@ -348,12 +422,14 @@ def main() -> int:
             "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"], "tied_embeddings": cfg["tie_word_embeddings"],
             "prompt_len": PROMPT_LEN, "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE,
-            "decode": "cuda-graph, device feedback",
+            "decode": ("eager launches" if args.no_graph else "cuda-graph") + ", device feedback",
             "l2": f"inputs larger than L2 ({nbytes / 1e9:.1f} GB of weights and cache per step)",
             "peaks": pk_src},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "gpu_launches": launches,
+        "repeats": {"n": len(regions), "ms_per_step_min": round(min(r[0] for r in regions) / steps, 4),
+                    "ms_per_step_max": round(max(r[0] for r in regions) / steps, 4)},
         "clocks": clocks.summary(),
     }
     if not args.skip_points:
@@ -364,8 +440,13 @@ def main() -> int:
         points = {}
         for b in ((1, 64) if headline else ()):
             k = min(steps, 100)
-            bms, _, _ = run_decode(engine, graphs, b, k, warmup, rng)
+            bms, _, _ = median_region(run_decode(engine, graphs, b, k, warmup, rng, repeats=min(repeats, 3)))
             points[f"decode_b{b}"] = round(b * k / (bms / 1e3), 1)
+        if not args.no_graph:
+            # the same steps launched kernel by kernel: the reference reports both modes
+            k = min(steps, 100)
+            ems, _, _ = median_region(run_decode(engine, None, args.batch, k, warmup, rng, repeats=min(repeats, 3)))
+            points[f"decode_b{args.batch}_eager"] = round(args.batch * k / (ems / 1e3), 1)
         line["points"] = points
     del graphs, engine
     torch.cuda.empty_cache()

@@ -2,11 +2,19 @@
 
 A step in which every request brings exactly one token has the same launches
 every time; only the metadata (positions, cache slots, block tables, lengths)
-and the token ids change.  Such a step is captured once per (batch size, number
-of key splits) into a CUDA graph over fixed buffers; later steps copy their
-metadata into those buffers and replay the graph.  The sampled tokens stay in a
-device buffer that is also the next step's input, so a run of decode steps
-needs no copy back to the host unless the caller wants the tokens.
+and the token ids change.  Such a step is captured once per (batch size, context
+bucket) into a CUDA graph over fixed buffers; later steps copy their metadata
+into those buffers and replay the graph.  The sampled tokens stay in a device
+buffer that is also the next step's input, so a run of decode steps needs no
+copy back to the host unless the caller wants the tokens.
+
+Batch sizes are rounded up to a few sizes (`padded_batch`): the rows beyond
+the real ones belong to requests of length zero, whose keys and values go
+nowhere and whose attention reads nothing, so a batch that shrinks request by
+request, as in continuous batching, walks through a handful of graphs instead
+of one per size.  All graphs share one memory pool: they never run side by
+side, and what a step leaves in the pool (its logits) is read before the next
+step is launched or not at all.
 
 The reference does the same for pure-decode steps: fixed metadata and source
 buffers uploaded before replay, graphs keyed by (slot table, batch, splits), a
@@ -30,19 +38,29 @@ from .engine import InvalidInput
 class _Captured:
     graph: torch.cuda.CUDAGraph
     layout: object
-    buf: torch.Tensor           # one int32 device buffer: [temps B | seeds B | metadata | tokens B]
+    rows_cap: int               # rows of the captured step (the padded batch size)
+    buf: torch.Tensor           # one int32 device buffer: [temps | seeds | metadata | tokens], each rows_cap wide
     dev: torch.Tensor           # view: the int32 metadata
-    tokens: torch.Tensor        # view [B] int32: input ids of the step, overwritten with the sampled ids
-    temps: torch.Tensor         # view [B] float32
-    seeds: torch.Tensor         # view [B] int32
-    rows: torch.Tensor          # [B] int32: 0..B-1, the rows whose logits are computed
-    host_tokens: torch.Tensor   # [B] int32 in pinned memory: the sampled ids, copied by the graph itself
-    logits: Optional[torch.Tensor] = None   # [B, vocab] float32 of the last replay (lives in the graph's pool)
+    tokens: torch.Tensor        # view [rows_cap] int32: input ids of the step, overwritten with the sampled ids
+    temps: torch.Tensor         # view [rows_cap] float32
+    seeds: torch.Tensor         # view [rows_cap] int32
+    rows: torch.Tensor          # [rows_cap] int32: 0..rows_cap-1, the rows whose logits are computed
+    host_tokens: torch.Tensor   # [rows_cap] int32 in pinned memory: the sampled ids, copied by the graph itself
+    logits: Optional[torch.Tensor] = None   # [rows_cap, vocab] float32 of the last replay (lives in the shared pool)
     launches: int = 0           # kernels the graph holds
 
 
+def padded_batch(n: int) -> int:
+    """The batch size a step of `n` requests is captured at: 1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128,
+    then multiples of 64."""
+    for size in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128):
+        if n <= size:
+            return size
+    return -(-n // 64) * 64
+
+
 class DecodeGraphs:
-    MAX_CACHED = 16
+    MAX_CACHED = 48
     MAX_KEPT_BATCH = 1024
 
     def __init__(self, engine):
@@ -56,17 +74,19 @@ class DecodeGraphs:
         self.captures = 0
         self._last, self._last_requests = None, None
         self._pairs_of = None
+        self._pool = None                     # the memory pool all graphs share
         self._ring, self._ring_at = [], 0     # pinned buffers for the ids of steps launched with `keep`
         self._done = torch.cuda.Event()     # recorded after every replay
 
     # ------------------------------------------------------------------------------------
     def _key(self, n_requests: int, max_kv_len: int):
-        return (n_requests, max(256, 1 << (int(max_kv_len) - 1).bit_length()))
+        cap = min(padded_batch(n_requests), max(self.engine.max_requests, n_requests))
+        return (cap, max(256, 1 << (int(max_kv_len) - 1).bit_length()))
 
-    def _context(self, cap: _Captured, B: int, kv_bucket: int) -> StepContext:
-        eng = self.engine
+    def _context(self, cap: _Captured, kv_bucket: int) -> StepContext:
+        eng, n = self.engine, cap.rows_cap
         widths = [eng.max_blocks] * len(eng.group_windows)
-        return eng._context(cap.dev, cap.layout, widths, B, B, [1] * B, [kv_bucket] * B, [], cap.tokens)
+        return eng._context(cap.dev, cap.layout, widths, n, n, [1] * n, [kv_bucket] * n, [], cap.tokens)
 
     def _run(self, cap: _Captured, ctx: StepContext) -> torch.Tensor:
         logits = self.engine.model.forward(ctx, self.engine.views, cap.rows)
@@ -77,29 +97,31 @@ class DecodeGraphs:
 
     def _new_capture(self, key):
         eng = self.engine
-        B, kv_bucket = key
+        n, kv_bucket = key
         n_groups = len(eng.group_windows)
-        layout = eng.cache.layout(B, B, [eng.max_blocks] * n_groups)
+        layout = eng.cache.layout(n, n, [eng.max_blocks] * n_groups)
         # Temperatures and seeds before the metadata, tokens after it: whatever a step brings from
         # the host is one contiguous piece, and one copy.
-        buf = torch.zeros((3 * B + layout.total,), dtype=torch.int32, device=eng.device)
-        at = 2 * B
-        cap = _Captured(graph=torch.cuda.CUDAGraph(), layout=layout, buf=buf, dev=buf[at: at + layout.total],
-                        tokens=buf[at + layout.total: at + layout.total + B], temps=buf[0: B].view(torch.float32),
-                        seeds=buf[B: 2 * B], rows=torch.arange(B, dtype=torch.int32, device=eng.device),
-                        host_tokens=torch.zeros((B,), dtype=torch.int32, pin_memory=True))
-        return cap, self._context(cap, B, kv_bucket)
+        buf = torch.zeros((3 * n + layout.total,), dtype=torch.int32, device=eng.device)
+        at = 2 * n
+        cap = _Captured(graph=torch.cuda.CUDAGraph(), layout=layout, rows_cap=n, buf=buf,
+                        dev=buf[at: at + layout.total], tokens=buf[at + layout.total: at + layout.total + n],
+                        temps=buf[0: n].view(torch.float32), seeds=buf[n: 2 * n],
+                        rows=torch.arange(n, dtype=torch.int32, device=eng.device),
+                        host_tokens=torch.zeros((n,), dtype=torch.int32, pin_memory=True))
+        return cap, self._context(cap, kv_bucket)
 
     # ------------------------------------------------------------------------------------
     def step(self, requests: Sequence[int], tokens: Optional[Sequence[int]] = None,
              temps: Optional[Sequence[float]] = None, seeds: Optional[Sequence[int]] = None,
              reserved: bool = False, keep: bool = False):
         """One decode step for `requests` (each brings one token).  `tokens` are the input ids
-        on the host; None means: the ids the previous step of the same batch sampled, which
-        are still on the device.  Returns the device buffer [B] of sampled ids (valid until
-        the next step of this batch size); with `keep`, a ticket for `read` instead: the ids are
-        also copied into a pinned buffer of their own, so that they can be read after later steps
-        have been launched."""
+        on the host; None means: the ids the previous step of the same requests sampled, which
+        are still on the device.  `temps` and `seeds` None means: as in the previous step of the
+        same requests (greedy if there was none).  Returns the device buffer [B] of sampled ids
+        (valid until the next step); with `keep`, a ticket for `read` instead: the ids are also copied
+        into a pinned buffer of their own, so that they can be read after later steps have been
+        launched."""
         eng = self.engine
         B = len(requests)
         if self._pairs_of is not None and self._pairs_of[0] == requests:
@@ -130,10 +152,10 @@ class DecodeGraphs:
                 raise ValueError("batch too large for the kept-token buffers")
             buf, event = self._ring[self._ring_at]
             self._ring_at = (self._ring_at + 1) % len(self._ring)
-            buf[:B].copy_(cap.tokens, non_blocking=True)
+            buf[:B].copy_(cap.tokens[:B], non_blocking=True)
             event.record(ops.current_stream())
             return (buf, event, B)
-        return cap.tokens
+        return cap.tokens[:B]
 
     def _launch(self, pairs, B, tokens, temps, seeds, same_batch) -> _Captured:
         """Uploads the step's metadata into the buffers of the graph that serves it (captured now if
@@ -150,28 +172,34 @@ class DecodeGraphs:
             cap, ctx = self._new_capture(key)
         else:
             cap = self.cached[key]
+        n = cap.rows_cap
         st = eng._next_staging()
         n_meta = cap.layout.total
         host = st["np"]
-        eng.cache.pack(pairs, cap.layout, host[2 * B:], 0, 0)
-        lo, hi = 2 * B, 2 * B + n_meta
+        # rows beyond the real ones: requests of length zero (their keys go nowhere, they read none)
+        eng.cache.pack(pairs, cap.layout, host[2 * n:], n, n)
+        lo, hi = 2 * n, 2 * n + n_meta
         moved = cap is not self._last
         if tokens is not None:
             host[hi: hi + B] = np.asarray(tokens, dtype=np.int32)
-            hi += B
+            host[hi + B: hi + n] = 0
+            hi += n
         elif moved:
             # the previous step of this batch ran from another graph (its context outgrew a bucket):
             # the ids it sampled move over on the device
-            cap.tokens.copy_(self._last.tokens, non_blocking=True)
+            cap.tokens[:B].copy_(self._last.tokens[:B], non_blocking=True)
         if temps is not None:
+            host[0: 2 * n] = 0
             host[0: B].view(np.float32)[:] = np.asarray(list(temps), dtype=np.float32)
-            host[B: 2 * B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
+            host[n: n + B] = np.asarray([s & 0x7FFFFFFF for s in seeds], dtype=np.int32)
             lo = 0
         elif same_batch and moved:
             # ... and so do the temperatures and seeds, which live in each graph's own buffer
-            cap.buf[0: 2 * B].copy_(self._last.buf[0: 2 * B], non_blocking=True)
+            last = self._last
+            cap.temps[:B].copy_(last.temps[:B], non_blocking=True)
+            cap.seeds[:B].copy_(last.seeds[:B], non_blocking=True)
         elif not same_batch:
-            host[0: 2 * B] = 0          # nobody said otherwise: greedy
+            host[0: 2 * n] = 0          # nobody said otherwise: greedy
             lo = 0
         ops.copy_to_device(cap.buf, st["host"], lo, hi)
         stream = ops.current_stream()
@@ -189,8 +217,10 @@ class DecodeGraphs:
                 self._run(cap, ctx)
             torch.cuda.current_stream().wait_stream(side)
             cap.tokens.copy_(saved)
+            if self._pool is None:
+                self._pool = torch.cuda.graph_pool_handle()
             before = ops.COUNTER.launches
-            with torch.cuda.graph(cap.graph):
+            with torch.cuda.graph(cap.graph, pool=self._pool):
                 cap.logits = self._run(cap, ctx)
             cap.launches = ops.COUNTER.launches - before
             ops.COUNTER.launches = before            # captured, not yet run
@@ -213,7 +243,8 @@ class DecodeGraphs:
         """The ids the last step sampled, on the host: waits for the step (its graph ends with the
         copy into pinned memory)."""
         self._done.synchronize()
-        return self._last.host_tokens.tolist()
+        return self._last.host_tokens[: len(self._last_requests)].tolist()
 
-    def last_logits(self, n_requests: int, max_kv_len: int) -> torch.Tensor:
-        return self.cached[self._key(n_requests, max_kv_len)].logits
+    def last_logits(self) -> torch.Tensor:
+        """The logits [requests, vocab] of the last step; valid until the next step is launched."""
+        return self._last.logits[: len(self._last_requests)]

@@ -348,9 +348,10 @@ class Engine:
         self.graph_replays += 1
         return logits
 
-    def _fill(self, entries, layout, widths, dev, tok_at, want_at) -> None:
+    def _fill(self, entries, layout, widths, dev, tok_at, want_at, pairs=None) -> None:
         """Writes a step's metadata, token ids and wanted rows into `dev` through pinned memory."""
-        pairs = [(int(e.request), len(e.tokens)) for e in entries]
+        if pairs is None:
+            pairs = [(int(e.request), len(e.tokens)) for e in entries]
         n_want = sum(len(e.want) for e in entries)
         total = want_at + ((n_want + 3) & ~3)
         st = self._next_staging()
@@ -387,7 +388,11 @@ class Engine:
             state_slots=state_slots, max_q_len=max(q_lens), max_kv_len=max(kv_lens))
 
     def _pack(self, entries: Sequence[Entry]):
-        pairs = [(int(e.request), len(e.tokens)) for e in entries]
+        return self._pack_pairs([(int(e.request), len(e.tokens)) for e in entries], None, entries)
+
+    def _pack_pairs(self, pairs, token_ids: Optional[torch.Tensor], entries: Sequence[Entry] = ()):
+        """The context of an eager step.  With `token_ids` (int32 on the device, one per row) the ids
+        stay where they are and `entries` bring none; no rows are wanted then."""
         T = sum(n for _, n in pairs)
         B = len(pairs)
         widths = []
@@ -400,9 +405,10 @@ class Engine:
         want_at = tok_at + ((T + 3) & ~3)
         total = want_at + ((n_want + 3) & ~3)
         dev = torch.empty((total,), dtype=torch.int32, device=self.device)
-        self._fill(entries, layout, widths, dev, tok_at, want_at)
+        self._fill(entries, layout, widths, dev, tok_at, want_at, pairs)
         ctx = self._context(dev, layout, widths, T, B, [n for _, n in pairs],
                             [self.cache.reserved(r) for r, _ in pairs],
-                            [self.cache.state_slot(r) for r, _ in pairs], dev[tok_at: tok_at + T])
+                            [self.cache.state_slot(r) for r, _ in pairs],
+                            dev[tok_at: tok_at + T] if token_ids is None else token_ids)
         logit_rows = dev[want_at: want_at + n_want] if n_want else None
         return ctx, logit_rows

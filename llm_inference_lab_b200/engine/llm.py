@@ -54,7 +54,8 @@ class LLM:
         self.lookahead = bool(lookahead) and self.cuda_graph
         if self.cuda_graph:
             self.engine.enable_step_graphs()      # prompt portions of a repeating shape as well
-        self.step_log: list[tuple[float, int, bool]] = []   # (time the step's tokens reached the host, tokens, decode?)
+        # (time the step's tokens reached the host, tokens, decode?, tokens its requests hold after it)
+        self.step_log: list[tuple[float, int, bool, int]] = []
         self._next_id = 0
         self.steps = 0
         self.trace = None      # optional callable taking one dict per step (the CLI's --trace-steps)
@@ -157,7 +158,7 @@ class LLM:
 
     def _step_done(self, by_id, plan, sampled, pure_decode) -> None:
         now = time.perf_counter()
-        self.step_log.append((now, sum(e.n for e in plan), pure_decode))
+        self.step_log.append((now, sum(e.n for e in plan), pure_decode, sum(e.start + e.n for e in plan)))
         for e in plan:
             if e.sample and by_id[e.id]["ttft"] is None:
                 by_id[e.id]["ttft"] = now - by_id[e.id]["t0"]

@@ -206,6 +206,8 @@ def test_lookahead_decoding_gives_the_same_tokens(tmp_path_factory, dtype):
         llm.engine.cache.check_consistency()
         if ahead:
             assert llm.graphs.replays > 20
+        # batches of three ran from the graph of four, with a request of length zero beside them
+        assert {k[0] for k in llm.graphs.cached} <= {1, 2, 4}
     assert outs[True] == outs[False]
     assert any(reason == "eos" for _, reason in outs[True][1]) and any(reason == "length" for _, reason in outs[True][1])
 
