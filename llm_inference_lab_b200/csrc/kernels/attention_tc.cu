@@ -356,25 +356,6 @@ struct DcLayout {
   static constexpr int WARP_BYTES = STAGES * 2 * DC_TILE_BYTES;
   static constexpr int RING_BYTES = DC_WARPS * WARP_BYTES > DC_MERGE_BYTES ? DC_WARPS * WARP_BYTES : DC_MERGE_BYTES;
   static constexpr int SMEM = RING_BYTES + (CLUSTER ? DC_RECV_BYTES : 0);  // rings (then the warps' states), receive area
-  static constexpr int SMEM_FUSED = SMEM + 18 * ROW_BYTES;  // + the rotated q rows, the newest key and value
-};
-
-// What the fused variant needs besides the plain one's arguments: it takes the fused projection
-// itself (rounded, or as split-K partial sums plus bias), rotates q for its heads, and the CTA
-// that owns a request's newest key rotates k and writes k and v into their cache slot before it
-// reads them back with the other keys.  The splits of a (request, kv head) count themselves in
-// `counters` (zero between launches); the one that finishes last merges them.
-struct FusedDecodeArgs {
-  const __nv_bfloat16* qkv;   // [rows, qkv_stride] or null
-  int qkv_stride;             // elements per row of qkv / of a partial plane
-  const float* partial;       // [k_splits, rows, qkv_stride] or null
-  int k_splits;
-  long long k_split_stride;
-  const __nv_bfloat16* bias;  // added to partial sums (may be null)
-  const float* inv_freq;
-  int rotary_dim;
-  const int* slots;           // [rows] page * page_size + offset of each row's new key
-  int* counters;              // [requests * n_kv] zeros
 };
 
 // CLUSTER: the splits of one (request, kv head, tile of heads) are the CTAs of one thread-block
@@ -382,13 +363,13 @@ struct FusedDecodeArgs {
 // elements: each split stores the (acc, max, sum) of those elements straight into the shared
 // memory of the CTA that merges them (remote stores do not stall, remote loads would), and after
 // one cluster barrier everyone finds all it needs at home: no scratch and no merge kernel.
-template <bool FUSED, bool CLUSTER = false>
+template <bool CLUSTER = false>
 __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, int out_stride, const __nv_bfloat16* __restrict__ q, int q_stride,
     __nv_bfloat16* __restrict__ cache_k, __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ block_table,
     int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window, float scale_log2, int splits,
-    float* __restrict__ part_acc, float* __restrict__ part_ml, FusedDecodeArgs fa) {
+    float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ __align__(16) uint8_t smem[];
   using L = DcLayout<CLUSTER>;
   pdl_trigger();
@@ -418,17 +399,11 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   const int tile_lo = split * tiles_per_split;
   const int tile_hi = min(total_tiles, tile_lo + tiles_per_split);
 
-  // In the fused variant the CTA that owns the request's newest key computes it itself: the copy
-  // from the cache leaves that row as zeros, and the row is patched in shared memory.
-  bool owns_newest = false;
-  if constexpr (FUSED)
-    owns_newest = mt == 0 && tile_lo < total_tiles && tile_lo + tiles_per_split >= total_tiles;
-  const int kvl_load = owns_newest ? kvl - 1 : kvl;
   const uint32_t ring = smem_u32(smem) + warp * L::WARP_BYTES;
   auto issue = [&](int t, int stage) {
     const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
     const int key0 = start + t * DC_BN;
-    load_kv_rows_warp<DC_BN>(kd, kd + DC_TILE_BYTES, cache_k, cache_v, bt, key0, first, kvl_load, kvh, n_kv,
+    load_kv_rows_warp<DC_BN>(kd, kd + DC_TILE_BYTES, cache_k, cache_v, bt, key0, first, kvl, kvh, n_kv,
                              page_size, num_pages, lane);
   };
   // this warp's tiles: tile_lo + warp, + DC_WARPS, ...; the first copies start before anything else
@@ -436,7 +411,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   int staged = 0;
   for (; staged < L::STAGES - 1; ++staged) {
     // a tile that reaches the newest key waits for the kernel that writes it
-    if (t_issue < tile_hi && start + (t_issue + 1) * DC_BN >= kvl_load) break;
+    if (t_issue < tile_hi && start + (t_issue + 1) * DC_BN >= kvl) break;
     if (t_issue < tile_hi) issue(t_issue, staged);
     cp_async_commit();
     t_issue += DC_WARPS;
@@ -449,60 +424,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   }
 
   uint32_t qf[KSTEPS][4];
-  if constexpr (FUSED) {
-    // ---- rotary encoding of this CTA's query heads (and of the newest key) ----
-    const uint32_t q_s = smem_u32(smem) + L::SMEM;
-    __nv_bfloat16* q_rows = reinterpret_cast<__nv_bfloat16*>(smem + L::SMEM);
-    constexpr int ROW_ELEMS = ROW_BYTES / 2;
-    auto value = [&](int col) -> float {
-      if (fa.partial) {
-        float v = 0.f;
-        const float* pp = fa.partial + (size_t)qs * fa.qkv_stride + col;
-        for (int sk = 0; sk < fa.k_splits; ++sk) v += pp[(size_t)sk * fa.k_split_stride];  // ascending order
-        if (fa.bias) v += __bfloat162float(fa.bias[col]);
-        return __bfloat162float(__float2bfloat16_rn(v));
-      }
-      return __bfloat162float(fa.qkv[(size_t)qs * fa.qkv_stride + col]);
-    };
-    const float pos = (float)(kvl - 1);
-    const int half = fa.rotary_dim / 2;
-    // rotate: out = [lo*c - hi*s, hi*c + lo*s] in 32-bit, rounded once
-    auto rotate_into = [&](__nv_bfloat16* dst, int col0, int i) {
-      if (i < half) {
-        float sn, cs;
-        sincosf(pos * fa.inv_freq[i], &sn, &cs);
-        const float vlo = value(col0 + i), vhi = value(col0 + i + half);
-        dst[i] = __float2bfloat16_rn(vlo * cs - vhi * sn);
-        dst[i + half] = __float2bfloat16_rn(vhi * cs + vlo * sn);
-      } else if (i >= 2 * half) {
-        dst[i] = __float2bfloat16_rn(value(col0 + i));
-      }
-    };
-    const int per_row = D - half;  // one item per rotated pair and per dimension that is not rotated
-    for (int e = tid; e < n_heads * per_row; e += DC_THREADS) {
-      const int r = e / per_row, w = e - r * per_row;
-      rotate_into(q_rows + r * ROW_ELEMS, (head0 + r) * D, w < half ? w : w + half);
-    }
-    for (int e = tid; e < (16 - n_heads) * D; e += DC_THREADS)  // rows beyond the group's heads
-      q_rows[(n_heads + e / D) * ROW_ELEMS + e % D] = __float2bfloat16_rn(0.f);
-    // The CTA whose keys end with the request's newest one computes that key and value: into
-    // shared memory for its own use, and into their cache slot for the steps to come.
-    __nv_bfloat16* new_k = q_rows + 16 * ROW_ELEMS;
-    __nv_bfloat16* new_v = q_rows + 17 * ROW_ELEMS;
-    if (owns_newest) {
-      for (int i = tid; i < 2 * D; i += DC_THREADS) {
-        if (i < D) rotate_into(new_k, (n_q + kvh) * D, i);
-        else new_v[i - D] = __float2bfloat16_rn(value((n_q + n_kv + kvh) * D + i - D));
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < KSTEPS; ++k) {
-      const int row = (lane & 7) + 8 * ((lane >> 3) & 1);
-      const int dcol = k * 16 + 8 * (lane >> 4);
-      ldmatrix_x4(qf[k], q_s + row * ROW_BYTES + dcol * 2);
-    }
-  } else {
+  {
     // q fragments straight from global memory: row r of the A operand is query head head0 + r
     const __nv_bfloat16* qrow = q + (size_t)qs * q_stride;
     const int ra = lane >> 2, rb = ra + 8;
@@ -524,23 +446,6 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     for (int e = 0; e < 4; ++e) o[t][e] = 0.f;
   const int lo[2] = {first, first}, hi[2] = {kvl - 1, kvl - 1};
 
-  if constexpr (FUSED) {
-    if (owns_newest && warp == DC_WARPS - 1) {  // after the barrier above: new_k / new_v are complete
-      const int slot = fa.slots[qs];
-      if (slot >= 0) {
-        const int page = slot / page_size, off = slot - page * page_size;
-        if (page >= num_pages) {
-          if (lane == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
-        } else {
-          const size_t row = (((size_t)page * n_kv + kvh) * page_size + off) * D;
-          const uint4* sk = reinterpret_cast<const uint4*>(smem + L::SMEM + 16 * ROW_BYTES);
-          const uint4* sv = reinterpret_cast<const uint4*>(smem + L::SMEM + 17 * ROW_BYTES);
-          if (lane < CPR) reinterpret_cast<uint4*>(cache_k + row)[lane] = sk[lane];
-          else if (lane < 2 * CPR) reinterpret_cast<uint4*>(cache_v + row)[lane - CPR] = sv[lane - CPR];
-        }
-      }
-    }
-  }
   int stage = 0;
   for (int t = tile_lo + warp; t < tile_hi; t += DC_WARPS) {
     // prefetch the tile L::STAGES - 1 ahead into the stage consumed last iteration
@@ -552,18 +457,6 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     __syncwarp();
     const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
     const int key0 = start + t * DC_BN;
-    if constexpr (FUSED) {
-      if (owns_newest && key0 <= kvl - 1 && kvl - 1 < key0 + DC_BN) {
-        // the newest key's row was left as zeros by the copy: put the computed key and value there
-        const int row = kvl - 1 - key0;
-        uint8_t* tile_k = smem + warp * L::WARP_BYTES + stage * 2 * DC_TILE_BYTES;
-        const uint4* sk = reinterpret_cast<const uint4*>(smem + L::SMEM + 16 * ROW_BYTES);
-        const uint4* sv = reinterpret_cast<const uint4*>(smem + L::SMEM + 17 * ROW_BYTES);
-        if (lane < CPR) reinterpret_cast<uint4*>(tile_k + row * ROW_BYTES)[lane] = sk[lane];
-        else if (lane < 2 * CPR) reinterpret_cast<uint4*>(tile_k + DC_TILE_BYTES + row * ROW_BYTES)[lane - CPR] = sv[lane - CPR];
-        __syncwarp();
-      }
-    }
     // every key of an inner tile is visible to the one query row: no mask to evaluate
     tile_step<DC_BN>(qf, kd, kd + DC_TILE_BYTES, o, m, l, key0, lo, hi, scale_log2, lane,
                      key0 >= first && key0 + DC_BN <= kvl);
@@ -653,35 +546,6 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
         out[(size_t)qs * out_stride + (size_t)(head0 + row) * D + dim] =
             __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
       }
-    }
-  }
-  if constexpr (FUSED && !CLUSTER) {
-    if (splits > 1) {
-      // The split that finishes last for this (request, kv head, tile of heads) merges them all.
-      __shared__ int is_last;
-      __threadfence();
-      __syncthreads();
-      int* counter = fa.counters + (size_t)b * gridDim.y + blockIdx.y;
-      if (tid == 0) is_last = atomicAdd(counter, 1) == splits - 1;
-      __syncthreads();
-      if (!is_last) return;
-      __threadfence();
-      for (int i = tid; i < n_heads * D; i += DC_THREADS) {
-        const int row = i / D, dim = i - row * D;
-        const size_t slot0 = ((size_t)b * n_q + head0 + row) * splits;
-        float big = -INFINITY;
-        for (int sp = 0; sp < splits; ++sp) big = fmaxf(big, part_ml[(slot0 + sp) * 2]);
-        float num = 0.f, den = 0.f;
-        for (int sp = 0; sp < splits; ++sp) {
-          const float ms = part_ml[(slot0 + sp) * 2];
-          const float wt = (ms == -INFINITY) ? 0.f : fast_exp2(ms - big);
-          num += wt * part_acc[(slot0 + sp) * D + dim];
-          den += wt * part_ml[(slot0 + sp) * 2 + 1];
-        }
-        out[(size_t)qs * out_stride + (size_t)(head0 + row) * D + dim] =
-            __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
-      }
-      if (tid == 0) *counter = 0;  // zero again for the next launch
     }
   }
 }
@@ -774,7 +638,7 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          DcLayout<false>::SMEM);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      e = cudaFuncSetAttribute(attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                DcLayout<true>::SMEM);
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
@@ -796,10 +660,10 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_lab_pdl ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel<false, true>, (__nv_bfloat16*)out, out_stride,
+    return (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel<true>, (__nv_bfloat16*)out, out_stride,
                                    (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v,
                                    q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
-                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr, FusedDecodeArgs{});
+                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr);
   }
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
@@ -807,7 +671,7 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
                              (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                              (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, q_start, kv_len, block_table,
                              max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, splits, part_acc,
-                             part_ml, FusedDecodeArgs{});
+                             part_ml);
   if (e != cudaSuccess) return (int)e;
   if (splits > 1)
     e = lab_launch(attention_merge_kernel, dim3(requests, n_q), dim3(D), 0, stream, (__nv_bfloat16*)out, out_stride,
@@ -826,74 +690,6 @@ LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, in
   return decode_launch(out, out_stride, q, q_stride, cache_k, cache_v, q_start, kv_len, block_table, max_blocks,
                        requests, n_q, n_kv, page_size, num_pages, window, scale, splits, scratch, cluster_merge != 0,
                        stream);
-}
-
-// Decode attention fused with what precedes it in a pure-decode step: the sum of the fused
-// projection's split-K partial products and its bias (or the rounded projection), the rotary
-// encoding of q and of the newest k, and the write of the newest k and v into their cache slot.
-// Requests must bring exactly one row each; groups of more than 16 query heads per kv head are
-// not served (the caller uses the separate kernels).  counters: requests * n_kv zero ints, left
-// zero.  scratch as for lab_attention_decode.
-LAB_EXPORT int lab_attention_decode_fused(void* out, int out_stride, const void* qkv, int qkv_stride,
-                                          const float* partial, int k_splits, long long k_split_stride,
-                                          const void* bias, const float* inv_freq, int rotary_dim, const int* slots,
-                                          void* cache_k, void* cache_v, const int* q_start, const int* kv_len,
-                                          const int* block_table, int max_blocks, int requests, int n_q, int n_kv,
-                                          int page_size, int num_pages, int window, float scale, int splits,
-                                          float* scratch, int* counters, int cluster_merge, cudaStream_t stream) {
-  if (requests <= 0) return 0;
-  if (n_q % n_kv || n_q / n_kv > 16 || splits < 1 || rotary_dim % 2 || rotary_dim > D) return (int)cudaErrorInvalidValue;
-  const bool cluster = cluster_merge != 0 && splits >= 2 && splits <= DC_MAX_CLUSTER;
-  if (splits > 1 && !cluster && (scratch == nullptr || counters == nullptr)) return (int)cudaErrorInvalidValue;
-  if ((qkv == nullptr) == (partial == nullptr)) return (int)cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         DcLayout<false>::SMEM_FUSED);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               DcLayout<true>::SMEM_FUSED);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  FusedDecodeArgs fa;
-  fa.qkv = (const __nv_bfloat16*)qkv;
-  fa.qkv_stride = qkv_stride;
-  fa.partial = partial;
-  fa.k_splits = k_splits;
-  fa.k_split_stride = k_split_stride;
-  fa.bias = (const __nv_bfloat16*)bias;
-  fa.inv_freq = inv_freq;
-  fa.rotary_dim = rotary_dim;
-  fa.slots = slots;
-  fa.counters = counters;
-  float* part_acc = scratch;
-  float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
-  dim3 grid(splits, n_kv, requests);
-  if (cluster) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(DC_THREADS);
-    cfg.dynamicSmemBytes = DcLayout<true>::SMEM_FUSED;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_lab_pdl ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel<true, true>, (__nv_bfloat16*)out, out_stride,
-                                   (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v,
-                                   q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
-                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr, fa);
-  }
-  return (int)lab_launch(attention_decode_kernel<true>, grid, dim3(DC_THREADS), (size_t)DcLayout<false>::SMEM_FUSED, stream,
-                         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)cache_k,
-                         (__nv_bfloat16*)cache_v, q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size,
-                         num_pages, window, scale * LOG2E, splits, part_acc, part_ml, fa);
 }
 
 // ----------------------------------------------------------------------------------------

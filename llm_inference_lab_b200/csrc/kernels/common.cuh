@@ -39,6 +39,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 // Round a float to the storage type and back: the value an operator boundary leaves.
 template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
 
+// Split-half rotary pair: (lo, hi) are elements i and i + rotary_dim / 2 of a head, (cs, sn) the cosine
+// and sine of the pair's angle (rust/engine/src/runner/model/qwen2/kernels.rs:587-631).  One spelling
+// for every kernel that rotates, so that all of them round alike.
+__device__ __forceinline__ void rope_rotate(float lo, float hi, float cs, float sn, float& out_lo, float& out_hi) {
+  out_lo = __fmaf_rn(lo, cs, -__fmul_rn(hi, sn));
+  out_hi = __fmaf_rn(hi, cs, __fmul_rn(lo, sn));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

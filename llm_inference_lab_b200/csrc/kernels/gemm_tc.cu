@@ -6,6 +6,11 @@
 //   gated:      out[t, n] = T( silu(g) * u ),  g = x . w[n], u = x . w[inter + n]   (32-bit, one rounding)
 //   split-K:    partial[z, t, n] = sum over the z-th slice of k   (32-bit, summed by the
 //               kernel that consumes it, in a fixed order)
+//   q/k/v:      the fused projection of an attention layer with its epilogue: bias, rounding,
+//               split-half rotary encoding of the q and k heads with cosines and sines from the
+//               step's table, q to the activation, k and v straight into their cache pages
+//               (rust/engine/src/runner/model/qwen2/kernels.rs:240-284 packed projection, 587-631
+//               rotation, 635-698 cache store: three launches there, one here)
 //
 // Both operands are K-major bfloat16 ([rows, K] row-major), which is how activations and
 // checkpoint weights ([out, in]) already lie, so nothing is transposed.  The operand on the
@@ -18,6 +23,9 @@
 // orientation a tile's N side is half gate rows, half up rows (two TMA loads), so a thread's
 // accumulator row holds both; in swapped orientation a tile's M side is 64 gate rows over 64 up
 // rows of the same features, and the epilogue warps exchange them through shared memory.
+// The q/k/v epilogue needs a head whole inside a tile (heads of 64 or 128): in normal orientation a
+// thread holds a token's row and rotates pairs of its own columns; in swapped orientation a thread
+// holds a feature, and the two halves of a head meet through the same exchange buffer.
 //
 // CTAs are persistent (one per SM at most) and walk the output tiles: warp 0 issues TMA loads
 // into a ring of stages that runs on across tiles, warp 1 issues the MMAs (one elected lane)
@@ -40,8 +48,20 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
+enum Mode : int { PLAIN = 0, GATED_SILU = 1, QKV_ROPE = 2 };
+
+// Where the q/k/v epilogue finds its angles and puts its results.
+struct QkvStore {
+  __nv_bfloat16* cache_k;   // [num_pages, n_kv, page_size, d]; null: this call does not write the cache
+  __nv_bfloat16* cache_v;
+  const int* row_slot;      // [tokens] page * page_size + offset of each row's key and value, -1: none
+  const float2* table;      // [tokens, d / 2] (cos, sin) of position * inv_freq
+  int n_q, n_kv, d, page_size, num_pages;
+};
+
 struct Params {
-  void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats
+  void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats;
+                        // q/k/v: the rotated q [tokens, ld_out]
   const __nv_bfloat16* bias;
   int m_rows;           // valid rows on the M side (tokens, or features when swapped)
   int n_rows;           // valid rows on the N side
@@ -51,24 +71,84 @@ struct Params {
   int k_tiles_per_split;
   int up_offset;        // gated: row offset of the "up" half inside the weight matrix
   int m_tiles, n_tiles, splits;  // tiles on the M side, on the N side, and split-K planes
+  QkvStore qkv;         // q/k/v epilogue only
 };
 
-// TM: rows of the M-side tile, 128 or (swapped orientation only) 64.  With 64 rows an output has twice
-// the tiles, so a decode step's products spread over more SMs and a CTA's share of the weights fits
-// its shared memory whole: all of it is requested before the wait on the preceding kernel.  The
-// accumulator of an M = 64 MMA lies in lanes 0..15 of each quarter of tensor memory (row r in lane
-// 32 * (r / 16) + r % 16), so each epilogue warp still reads its own quarter.
-template <int TM, int BN, bool GATED, bool SWAP>
+// Element offset of (slot, kv head) in a cache of [pages, n_kv, page_size, d], or -1 (no slot; a
+// slot outside the pool also sets the error word).
+__device__ __forceinline__ long long cache_row_offset(const QkvStore& e, int slot, int kvh) {
+  if (slot < 0) return -1;
+  const int page = slot / e.page_size, off = slot - page * e.page_size;
+  if (page >= e.num_pages) {
+    lab_set_error(LAB_ERR_PAGE_RANGE);
+    return -1;
+  }
+  return (((long long)page * e.n_kv + kvh) * e.page_size + off) * e.d;
+}
+
+// Normal orientation: this thread holds 32 consecutive "lo" columns and the 32 "hi" columns that pair
+// with them (d / 2 further on) of token row m, of head `head` (q heads, then k heads, then v heads),
+// from column `j0` of the head on.  Adds the bias, rounds (the value the projection alone would have
+// stored), rotates q and k, rounds again and stores 2 x 64 bytes.
+__device__ __forceinline__ void qkv_store_row(const Params& p, int m, int head, int j0, const uint32_t* rlo,
+                                              const uint32_t* rhi) {
+  const QkvStore& e = p.qkv;
+  const int half = e.d / 2, col_lo = head * e.d + j0, col_hi = col_lo + half;
+  __nv_bfloat16* dst;
+  if (head < e.n_q) {
+    dst = (__nv_bfloat16*)p.out + (size_t)m * p.ld_out + col_lo;
+  } else {
+    if (e.cache_k == nullptr) return;
+    const bool is_k = head < e.n_q + e.n_kv;
+    const long long at = cache_row_offset(e, e.row_slot[m], is_k ? head - e.n_q : head - e.n_q - e.n_kv);
+    if (at < 0) return;
+    dst = (is_k ? e.cache_k : e.cache_v) + at + j0;
+  }
+  const bool rotate = head < e.n_q + e.n_kv;
+  const float2* cs = e.table + (size_t)m * half + j0;
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4) {
+    uint32_t wl[4], wh[4];
+    uint4 bl = make_uint4(0, 0, 0, 0), bh = bl;
+    if (p.bias) {
+      bl = reinterpret_cast<const uint4*>(p.bias + col_lo)[q4];
+      bh = reinterpret_cast<const uint4*>(p.bias + col_hi)[q4];
+    }
+    const __nv_bfloat162* hbl = reinterpret_cast<const __nv_bfloat162*>(&bl);
+    const __nv_bfloat162* hbh = reinterpret_cast<const __nv_bfloat162*>(&bh);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 fbl = __bfloat1622float2(hbl[k]), fbh = __bfloat1622float2(hbh[k]);
+      float lo[2], hi[2];
+      lo[0] = round_to<__nv_bfloat16>(__uint_as_float(rlo[q4 * 8 + 2 * k]) + fbl.x);
+      lo[1] = round_to<__nv_bfloat16>(__uint_as_float(rlo[q4 * 8 + 2 * k + 1]) + fbl.y);
+      hi[0] = round_to<__nv_bfloat16>(__uint_as_float(rhi[q4 * 8 + 2 * k]) + fbh.x);
+      hi[1] = round_to<__nv_bfloat16>(__uint_as_float(rhi[q4 * 8 + 2 * k + 1]) + fbh.y);
+      if (rotate) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const float2 f = cs[q4 * 8 + 2 * k + u];
+          rope_rotate(lo[u], hi[u], f.x, f.y, lo[u], hi[u]);
+        }
+      }
+      wl[k] = pack_bf16(lo[0], lo[1]);
+      wh[k] = pack_bf16(hi[0], hi[1]);
+    }
+    reinterpret_cast<uint4*>(dst)[q4] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+    reinterpret_cast<uint4*>(dst + half)[q4] = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+  }
+}
+
+template <int MODE, int BN, bool SWAP>
 struct Shape {
-  static_assert(TM == 128 || (TM == 64 && SWAP), "64-row tiles exist in swapped orientation only");
+  static constexpr int TM = BM;
   static constexpr int A_BYTES = TM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  // gated + swapped: the epilogue warps exchange gate and up values through a buffer of their own
-  static constexpr int EXCHANGE_BYTES = (GATED && SWAP) ? ((TM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
+  // swapped, gated or q/k/v: the epilogue warps exchange rows of the tile through a buffer of their own
+  static constexpr int EXCHANGE_BYTES = (MODE != PLAIN && SWAP) ? ((TM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
   static constexpr int STAGES_RAW = (SMEM_BUDGET - EXCHANGE_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES_CAP = TM == 64 ? 16 : 10;
-  static constexpr int STAGES = STAGES_RAW > STAGES_CAP ? STAGES_CAP : STAGES_RAW;
+  static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
   static constexpr int ACC_COLS = BN < 32 ? 32 : BN;
   static constexpr int ACC_BUFS = 2 * ACC_COLS <= 512 ? 2 : 1;  // accumulators in tensor memory
   static constexpr int TMEM_COLS = ACC_BUFS * ACC_COLS;         // a power of two >= 32
@@ -80,10 +160,12 @@ struct Shape {
 // A persistent CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Tiles are numbered with
 // the M side fastest, so CTAs that run at the same time share the N-side operand in L2.
 // Two accumulators in tensor memory let the epilogue of one tile run beside the MMAs of the next.
-template <int TM, int BN, bool GATED, bool SWAP, typename OutT>
+template <int MODE, int BN, bool SWAP, typename OutT>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_b, Params p) {
-  using S = Shape<TM, BN, GATED, SWAP>;
+  using S = Shape<MODE, BN, SWAP>;
+  constexpr int TM = BM;
+  constexpr bool GATED = MODE == GATED_SILU;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* exchange = reinterpret_cast<float*>(tiles + S::STAGES * S::STAGE_BYTES);
@@ -231,8 +313,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   } else {
     // ---- epilogue: warps 2..5, each reads its quarter of the 128 accumulator lanes ----
     const int quarter = warp & 3;
-    constexpr int QROWS = TM / 4;            // tile rows in a quarter: its first QROWS lanes
-    const bool has_row = lane < QROWS;
+    constexpr int QROWS = TM / 4;            // tile rows in a quarter: one per lane
+    constexpr bool has_row = true;
     pdl_wait();  // the output may still be read by an earlier kernel until it has completed
     int local = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
@@ -243,9 +325,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag);
       tc_fence_after();
       const uint32_t lane_addr = tmem_base + buf * S::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      const int m = m0 + quarter * QROWS + lane;  // this thread's row on the M side (if has_row)
+      const int m = m0 + quarter * QROWS + lane;  // this thread's row on the M side
       const bool partial = p.split_stride != 0;
-      // Decided once per thread; the gated swapped epilogue meets at named barriers, which every
+      // Decided once per thread; the swapped gated and q/k/v epilogues meet at named barriers, which every
       // epilogue thread reaches whatever it decided.
       const bool go = __all_sync(0xffffffffu, ok && !*abort_flag);
       bool released = false;
@@ -256,7 +338,78 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
       };
-      if constexpr (!SWAP) {
+      if constexpr (MODE == QKV_ROPE && !SWAP) {
+        // thread = token row m; the tile's columns are whole heads (d divides BN): per head, 32 pairs
+        // of columns (i, i + d / 2) at a time
+        const int d = p.qkv.d, n_heads = p.qkv.n_q + 2 * p.qkv.n_kv;
+        const int groups = d / 64;  // groups of 32 pairs per head
+        bool more = go;
+#pragma unroll 1
+        for (int hh = 0; hh < BN / 64 && more; ++hh) {  // at most BN / 64 heads in a tile
+          if (hh * d >= BN) break;
+          const int head = n0 / d + hh;
+          if (head >= n_heads) break;  // same for the whole warp
+#pragma unroll 1
+          for (int g = 0; g < groups; ++g) {
+            uint32_t rlo[32], rhi[32];
+            tmem_ld32_issue(lane_addr + hh * d + g * 32, rlo);
+            tmem_ld32_issue(lane_addr + hh * d + d / 2 + g * 32, rhi);
+            tmem_wait();
+            if (g == groups - 1 && ((hh + 1) * d >= BN || head + 1 >= n_heads)) release();
+            if (m < p.m_rows) qkv_store_row(p, m, head, g * 32, rlo, rhi);
+          }
+        }
+        release();
+      } else if constexpr (MODE == QKV_ROPE) {
+        // thread = feature m of the fused projection; columns = tokens.  The tile's 128 rows are whole
+        // heads; the two halves of a head meet through the exchange buffer, which holds the
+        // projection's values with the bias added, rounded as the projection alone would have stored them.
+        const QkvStore& e = p.qkv;
+        const int tile_row = quarter * QROWS + lane;
+        const float b = (p.bias && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 16 && go; ++c) {
+          if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
+          float v[16];
+          tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) exchange[tile_row * (BN + 1) + c * 16 + j] = round_to<__nv_bfloat16>(v[j] + b);
+        }
+        release();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (go && m < p.m_rows) {
+          const int d = e.d, half = d / 2, head = m / d, j = m - head * d;
+          const bool rotate = head < e.n_q + e.n_kv, is_lo = j < half;
+          const float* mine = exchange + tile_row * (BN + 1);
+          const float* other = exchange + (is_lo ? tile_row + half : tile_row - half) * (BN + 1);
+          __nv_bfloat16* base = nullptr;   // q: column m of the activation; k, v: element j of the cache row
+          const bool to_cache = head >= e.n_q;
+          const bool is_k = head < e.n_q + e.n_kv;
+          if (!to_cache) base = (__nv_bfloat16*)p.out + m;
+          else if (e.cache_k != nullptr) base = (is_k ? e.cache_k : e.cache_v) + j;
+          if (base != nullptr) {
+            const int kvh = is_k ? head - e.n_q : head - e.n_q - e.n_kv;
+            for (int col = 0; col < BN; ++col) {
+              const int tok = n0 + col;
+              if (tok >= p.n_rows) break;
+              float val = mine[col];
+              if (rotate) {
+                const float2 f = e.table[(size_t)tok * half + (is_lo ? j : j - half)];
+                float lo, hi;
+                if (is_lo) rope_rotate(val, other[col], f.x, f.y, lo, hi), val = lo;
+                else rope_rotate(other[col], val, f.x, f.y, lo, hi), val = hi;
+              }
+              if (!to_cache) {
+                base[(size_t)tok * p.ld_out] = __float2bfloat16_rn(val);
+              } else {
+                const long long at = cache_row_offset(e, e.row_slot[tok], kvh);
+                if (at >= 0) base[at] = __float2bfloat16_rn(val);
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
+      } else if constexpr (!SWAP) {
         // thread = token row m; columns = output features, 32 at a time
         constexpr int OUT_COLS = GATED ? BN / 2 : BN;
         static_assert(OUT_COLS % 32 == 0, "normal orientation works on 32 output columns at a time");
@@ -352,10 +505,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
           float v[16];
           tmem_ld16(lane_addr + c * 16, v);
-          if (has_row) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) exchange[tile_row * (BN + 1) + c * 16 + j] = v[j];
-          }
+          for (int j = 0; j < 16; ++j) exchange[tile_row * (BN + 1) + c * 16 + j] = v[j];
         }
         release();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -374,7 +525,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
       } else {
         // thread = output feature m; columns = tokens
-        const float b = (p.bias && !partial && has_row && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
+        const float b = (p.bias && !partial && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
         int c = 0;
 #pragma unroll 1
         for (; c < BN / 16 && go; ++c) {
@@ -386,7 +537,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
           if (c == BN / 16 - 1 || t + 16 >= p.n_rows) release();
-          if (!has_row || m >= p.m_rows) continue;
+          if (m >= p.m_rows) continue;
           if (partial) {
             float* dst = (float*)p.out + split * p.split_stride + m;
 #pragma unroll
@@ -412,11 +563,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 }
 
 // ---- host side -------------------------------------------------------------------------
-template <int TM, int BN, bool GATED, bool SWAP, typename OutT>
+template <int MODE, int BN, bool SWAP, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
-  using S = Shape<TM, BN, GATED, SWAP>;
+  using S = Shape<MODE, BN, SWAP>;
   static bool configured = false;
-  auto kern = gemm_tc_kernel<TM, BN, GATED, SWAP, OutT>;
+  auto kern = gemm_tc_kernel<MODE, BN, SWAP, OutT>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -425,27 +576,59 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
   return (int)lab_launch(kern, grid, dim3(THREADS), (size_t)S::SMEM, stream, ma, mb, p);
 }
 
-template <bool GATED, bool SWAP, typename OutT>
-int dispatch_bn(int bm, int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid,
-                cudaStream_t s) {
-  if constexpr (SWAP) {
-    if (bm == 64) {
-      switch (bn) {
-        case 16: return launch<64, 16, GATED, SWAP, OutT>(ma, mb, p, grid, s);
-        case 32: return launch<64, 32, GATED, SWAP, OutT>(ma, mb, p, grid, s);
-        case 64: return launch<64, 64, GATED, SWAP, OutT>(ma, mb, p, grid, s);
-      }
-      return (int)cudaErrorInvalidValue;
-    }
-  }
+template <int MODE, bool SWAP, typename OutT>
+int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t s) {
+  constexpr bool WIDE = !(MODE == GATED_SILU && SWAP);  // the gated exchange buffer is sized for up to 64 tokens
   switch (bn) {
-    case 16: if constexpr (SWAP) return launch<128, 16, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 32: if constexpr (SWAP) return launch<128, 32, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 64: return launch<128, 64, GATED, SWAP, OutT>(ma, mb, p, grid, s);
-    case 128: if constexpr (!(GATED && SWAP)) return launch<128, 128, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 256: if constexpr (!(GATED && SWAP)) return launch<128, 256, GATED, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 16: if constexpr (SWAP) return launch<MODE, 16, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 32: if constexpr (SWAP) return launch<MODE, 32, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 64: if constexpr (MODE != QKV_ROPE || SWAP) return launch<MODE, 64, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 128: if constexpr (WIDE) return launch<MODE, 128, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 256: if constexpr (WIDE && !(MODE == QKV_ROPE && SWAP)) return launch<MODE, 256, SWAP, OutT>(ma, mb, p, grid, s); break;
   }
   return (int)cudaErrorInvalidValue;
+}
+
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0)
+      count = 148;
+  }
+  return count;
+}
+
+// Fills the tensor maps, the tile counts and the grid for an orientation; returns a CUDA error code.
+int set_up(Params& p, CUtensorMap& ma, CUtensorMap& mb, dim3& grid, const void* x, const void* w, int tokens,
+           int n_out, int w_rows, int K, int ldx, int gated, int swap, int bn, int splits) {
+  p.k_tiles = (K + BK - 1) / BK;
+  p.k_tiles_per_split = (p.k_tiles + splits - 1) / splits;
+  p.up_offset = n_out;
+  p.splits = splits;
+  int rc;
+  if (!swap) {
+    const int box_b = gated ? bn / 2 : bn;
+    if ((rc = lab_make_map_bf16(&ma, x, tokens, K, ldx, BM))) return rc;
+    if ((rc = lab_make_map_bf16(&mb, w, w_rows, K, K, box_b))) return rc;
+    p.m_rows = tokens;
+    p.n_rows = n_out;
+    p.m_tiles = (tokens + BM - 1) / BM;
+    p.n_tiles = (n_out + box_b - 1) / box_b;
+  } else {
+    const int m_rows_tile = gated ? BM / 2 : BM;
+    if ((rc = lab_make_map_bf16(&ma, w, w_rows, K, K, m_rows_tile))) return rc;
+    if ((rc = lab_make_map_bf16(&mb, x, tokens, K, ldx, bn))) return rc;
+    if (gated && bn > 64) return (int)cudaErrorInvalidValue;  // the exchange buffer is sized for up to 64 tokens
+    p.m_rows = n_out;
+    p.n_rows = tokens;
+    p.m_tiles = (n_out + m_rows_tile - 1) / m_rows_tile;
+    p.n_tiles = (tokens + bn - 1) / bn;
+  }
+  const long long tiles = (long long)p.m_tiles * p.n_tiles * splits;
+  grid = dim3((unsigned)(tiles < sm_count() ? tiles : sm_count()));
+  return 0;
 }
 
 // For tests of the bounded waits: one warp waits on a barrier that nobody ever arrives at, with a
@@ -469,72 +652,79 @@ __global__ void wait_probe_kernel(unsigned long long limit_ns, int* gave_up) {
 // x: [tokens, K] bf16 (row stride ldx), w: [n_out (x2 when gated), K] bf16 contiguous.
 // out: bf16 or f32 [tokens, ld_out]; with splits > 1, `out` is the partial buffer
 // [splits, tokens, ld_out] of floats (no bias, not gated).
-// swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256); bm: rows of the
-// M-side tile, 128, or 64 (swapped orientation with bn <= 64 only).
+// swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256).
 LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
-                           int ldx, int ld_out, int gated, int out_f32, int swap, int bm, int bn, int splits,
+                           int ldx, int ld_out, int gated, int out_f32, int swap, int bn, int splits,
                            cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
-  if (bm != 128 && !(bm == 64 && swap && bn <= 64)) return (int)cudaErrorInvalidValue;
   if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA
   if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return (int)cudaErrorInvalidValue;  // 16-byte bases for TMA
   if (splits < 1 || (splits > 1 && (gated || !out_f32))) return (int)cudaErrorInvalidValue;
-  const int w_rows = gated ? 2 * n_out : n_out;
   CUtensorMap ma, mb;
-  Params p;
+  Params p = {};
   p.out = out;
   p.bias = (const __nv_bfloat16*)bias;
   p.ld_out = ld_out;
-  p.k_tiles = (K + BK - 1) / BK;
-  p.k_tiles_per_split = (p.k_tiles + splits - 1) / splits;
   p.split_stride = splits > 1 ? (long long)tokens * ld_out : 0;
-  p.up_offset = n_out;
   dim3 grid;
-  int rc;
-  if (!swap) {
-    const int box_b = gated ? bn / 2 : bn;
-    if ((rc = lab_make_map_bf16(&ma, x, tokens, K, ldx, BM))) return rc;
-    if ((rc = lab_make_map_bf16(&mb, w, w_rows, K, K, box_b))) return rc;
-    p.m_rows = tokens;
-    p.n_rows = n_out;
-    p.m_tiles = (tokens + BM - 1) / BM;
-    p.n_tiles = (n_out + box_b - 1) / box_b;
-  } else {
-    const int m_rows_tile = gated ? bm / 2 : bm;
-    if ((rc = lab_make_map_bf16(&ma, w, w_rows, K, K, m_rows_tile))) return rc;
-    if ((rc = lab_make_map_bf16(&mb, x, tokens, K, ldx, bn))) return rc;
-    if (gated && bn > 64) return (int)cudaErrorInvalidValue;  // the exchange buffer is sized for up to 64 tokens
-    p.m_rows = n_out;
-    p.n_rows = tokens;
-    p.m_tiles = (n_out + m_rows_tile - 1) / m_rows_tile;
-    p.n_tiles = (tokens + bn - 1) / bn;
-  }
-  p.splits = splits;
-  {
-    static int sm_count = 0;
-    if (sm_count == 0) {
-      int dev = 0;
-      if (cudaGetDevice(&dev) != cudaSuccess ||
-          cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-        sm_count = 148;
-    }
-    const long long tiles = (long long)p.m_tiles * p.n_tiles * splits;
-    grid = dim3((unsigned)(tiles < sm_count ? tiles : sm_count));
-  }
   // A gated tile whose "gate" rows run past n_out would read "up" rows as gate: tiles are cut so
   // that valid outputs never mix the halves (rows >= n_out are masked in the epilogue), but the
   // up half must start at a row the map can address with the same box.
+  const int rc = set_up(p, ma, mb, grid, x, w, tokens, n_out, gated ? 2 * n_out : n_out, K, ldx, gated, swap, bn, splits);
+  if (rc) return rc;
   if (gated) {
     if (out_f32) return (int)cudaErrorInvalidValue;
-    if (swap) return dispatch_bn<true, true, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
-    return dispatch_bn<true, false, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
+    if (swap) return dispatch_bn<GATED_SILU, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+    return dispatch_bn<GATED_SILU, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
   }
   if (swap) {
-    if (out_f32) return dispatch_bn<false, true, float>(bm, bn, ma, mb, p, grid, stream);
-    return dispatch_bn<false, true, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
+    if (out_f32) return dispatch_bn<PLAIN, true, float>(bn, ma, mb, p, grid, stream);
+    return dispatch_bn<PLAIN, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
   }
-  if (out_f32) return dispatch_bn<false, false, float>(bm, bn, ma, mb, p, grid, stream);
-  return dispatch_bn<false, false, __nv_bfloat16>(bm, bn, ma, mb, p, grid, stream);
+  if (out_f32) return dispatch_bn<PLAIN, false, float>(bn, ma, mb, p, grid, stream);
+  return dispatch_bn<PLAIN, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+}
+
+// The fused q/k/v projection of an attention layer with its epilogue.
+//   x: [tokens, K] bf16 (row stride ldx); w: [(n_q + 2 n_kv) * d, K] bf16 contiguous (q rows, k rows, v rows);
+//   bias: the same width, or null; q_out: [tokens, ld_q] bf16 receives the rotated q;
+//   table: [tokens, d / 2] (cos, sin) pairs; row_slot: [tokens] cache slots (page * page_size + offset,
+//   -1: none); cache_k / cache_v: [num_pages, n_kv, page_size, d], or null when the call does not write.
+// Heads of 64 or 128 (a head must lie whole inside a tile), rotation over the whole head.
+LAB_EXPORT int lab_gemm_tc_qkv(void* q_out, const void* x, const void* w, const void* bias, int tokens, int n_q,
+                               int n_kv, int d, int K, int ldx, int ld_q, const void* table, const int* row_slot,
+                               void* cache_k, void* cache_v, int page_size, int num_pages, int swap, int bn,
+                               cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if ((d != 64 && d != 128) || n_q <= 0 || n_kv <= 0) return (int)cudaErrorInvalidValue;
+  if (K % 8 || ldx % 8 || K <= 0 || ld_q % 8) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)bias) | ((uintptr_t)q_out) | ((uintptr_t)cache_k) |
+       ((uintptr_t)cache_v) | ((uintptr_t)table)) & 15)
+    return (int)cudaErrorInvalidValue;
+  if (table == nullptr || ((cache_k != nullptr) && (cache_v == nullptr || row_slot == nullptr || page_size <= 0)))
+    return (int)cudaErrorInvalidValue;
+  if (!swap && bn % d) return (int)cudaErrorInvalidValue;   // whole heads in a tile
+  const int n_out = (n_q + 2 * n_kv) * d;
+  CUtensorMap ma, mb;
+  Params p = {};
+  p.out = q_out;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.ld_out = ld_q;
+  p.split_stride = 0;
+  p.qkv.cache_k = (__nv_bfloat16*)cache_k;
+  p.qkv.cache_v = (__nv_bfloat16*)cache_v;
+  p.qkv.row_slot = row_slot;
+  p.qkv.table = (const float2*)table;
+  p.qkv.n_q = n_q;
+  p.qkv.n_kv = n_kv;
+  p.qkv.d = d;
+  p.qkv.page_size = page_size;
+  p.qkv.num_pages = num_pages;
+  dim3 grid;
+  const int rc = set_up(p, ma, mb, grid, x, w, tokens, n_out, n_out, K, ldx, 0, swap, bn, 1);
+  if (rc) return rc;
+  if (swap) return dispatch_bn<QKV_ROPE, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+  return dispatch_bn<QKV_ROPE, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
 }
 
 // Launches the wait that nothing ends (see wait_probe_kernel); the limit is capped at 50 ms.

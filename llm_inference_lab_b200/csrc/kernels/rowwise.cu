@@ -244,7 +244,7 @@ LAB_EXPORT int lab_add_rmsnorm(void* y, void* x, const void* delta, const float*
 // Rotary encoding of q and k (split-half pairing over the first `rotary_dim` of each head)
 // + write of rotated k and of v into the cache pages.
 //   qkv: [tokens, (n_q + 2 n_kv) * d] rows of the fused projection (bias already added);
-//        q is rotated in place.
+//        q is rotated in place; without a cache to write, k is rotated in place as well.
 //   cache_k / cache_v: [num_pages, n_kv, page_size, d]; slot = page * page_size + offset.
 // ----------------------------------------------------------------------------------------
 // The fused projection arrives either rounded to T in `qkv` (q is then rotated in place), or
@@ -276,7 +276,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     }
     return to_f32<T>(qkv[(size_t)t * row_stride + col]);
   };
-  const float pos = (float)positions[t];
+  const float pos = rotary_dim > 0 ? (float)positions[t] : 0.f;   // no positions are read where nothing rotates
   long long cache_row = -1;  // element offset of (page, kv head 0, offset) in the cache, or -1: no write
   if (cache_k != nullptr && head_hi > n_q) {
     const int slot = slots[t];
@@ -302,6 +302,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     T* dst;
     if (head < n_q) {
       dst = partial ? q_out + (size_t)t * n_q * d + col0 : qkv + (size_t)t * row_stride + col0;
+    } else if (cache_k == nullptr) {
+      // no cache to write: k is rotated where it lies (a caller that only encodes), v stays as it is
+      if (partial || head >= n_q + n_kv) continue;
+      dst = qkv + (size_t)t * row_stride + col0;
     } else {
       if (cache_row < 0) continue;
       const bool is_k = head < n_q + n_kv;
@@ -314,8 +318,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
       if (e != (int)threadIdx.x) sincosf(pos * inv_freq[i], &sn, &cs);
       // Both halves are read before either is written: a thread owns the pair (i, i + half).
       const float lo = value(col0 + i), hi = value(col0 + i + half);
-      dst[i] = from_f32<T>(lo * cs - hi * sn);
-      dst[i + half] = from_f32<T>(hi * cs + lo * sn);
+      float rlo, rhi;
+      rope_rotate(lo, hi, cs, sn, rlo, rhi);
+      dst[i] = from_f32<T>(rlo);
+      dst[i + half] = from_f32<T>(rhi);
     } else if (i >= 2 * half) {
       dst[i] = from_f32<T>(value(col0 + i));
     }
@@ -375,8 +381,9 @@ __global__ void __launch_bounds__(256) rope_kv_write_vec_kernel(
   }
   __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)head * d;
   __nv_bfloat16* dst = src;
-  if (head >= n_q) {
-    if (cache_k == nullptr) return;
+  if (head >= n_q && cache_k == nullptr) {
+    if (is_v) return;      // no cache to write: k is rotated where it lies, v stays as it is
+  } else if (head >= n_q) {
     const int slot = slots[t];
     if (slot < 0) return;
     const int page = slot / page_size, off = slot - page * page_size;
@@ -403,9 +410,10 @@ __global__ void __launch_bounds__(256) rope_kv_write_vec_kernel(
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float2 f = cs[j];
-    const float l = __bfloat162float(lo[j]), h = __bfloat162float(hi[j]);
-    pl[j] = __float2bfloat16_rn(l * f.x - h * f.y);
-    ph[j] = __float2bfloat16_rn(h * f.x + l * f.y);
+    float rl, rh;
+    rope_rotate(__bfloat162float(lo[j]), __bfloat162float(hi[j]), f.x, f.y, rl, rh);
+    pl[j] = __float2bfloat16_rn(rl);
+    ph[j] = __float2bfloat16_rn(rh);
   }
   *reinterpret_cast<uint4*>(dst + i0) = olo;
   *reinterpret_cast<uint4*>(dst + i0 + half) = ohi;

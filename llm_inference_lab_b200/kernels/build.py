@@ -183,3 +183,20 @@ def build_many(jobs) -> list[str]:
     if errors:
         raise errors[0]
     return results
+
+
+def prune() -> list[str]:
+    """Removes libraries in the build folder that no source of this checkout produces any more (a
+    changed source or flag gives a new name and leaves the old file behind).  Keeps what this process
+    has built or found; returns the names it removed."""
+    with _lock:
+        keep = {os.path.basename(p) for p in _built.values()}
+    removed = []
+    for name in os.listdir(build_dir()):
+        if name.endswith(".so") and name not in keep:
+            try:
+                os.remove(os.path.join(build_dir(), name))
+                removed.append(name)
+            except OSError:
+                pass
+    return removed

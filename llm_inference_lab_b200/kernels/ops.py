@@ -175,7 +175,7 @@ def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, delta: torch.
     return out
 
 
-def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor | None, inv_freq: torch.Tensor, rotary_dim: int,
                   slots: torch.Tensor | None, cache_k: torch.Tensor | None, cache_v: torch.Tensor | None,
                   n_q: int, n_kv: int, head_dim: int, bias: torch.Tensor | None = None,
                   q_out: torch.Tensor | None = None) -> torch.Tensor:
@@ -188,6 +188,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Te
     _on_gpu(qkv, positions, inv_freq, slots, cache_k, cache_v, bias, q_out)
     width = (n_q + 2 * n_kv) * head_dim
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2
+    assert positions is not None or rotary_dim == 0
     page_size = num_pages = 0
     if cache_k is not None:
         num_pages, kvh, page_size, d = cache_k.shape
@@ -212,6 +213,20 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Te
         rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v), tokens, n_q, n_kv, head_dim, page_size, num_pages,
         dtype_code(qkv.dtype), _stream()), "rope_kv_write")
     return qkv[:, : n_q * head_dim]
+
+
+_no_freq: dict = {}
+
+
+def kv_store(qkv: torch.Tensor, slots, cache_k, cache_v, n_q: int, n_kv: int, head_dim: int) -> torch.Tensor:
+    """The framework's paged store: writes the k and v columns of the fused projection `qkv`
+    [tokens, (n_q + 2 n_kv) * d] to their cache slots (nothing if `cache_k` is None) and returns the q
+    columns.  What a position encoding that only encodes leaves to the framework."""
+    key = str(qkv.device)
+    none = _no_freq.get(key)
+    if none is None:
+        none = _no_freq[key] = torch.zeros((0,), dtype=torch.float32, device=qkv.device)
+    return rope_kv_write(qkv, None, none, 0, slots, cache_k, cache_v, n_q, n_kv, head_dim)
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
@@ -340,13 +355,11 @@ def force_plain(flag: bool) -> bool:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
             out_f32: bool = False, swap: bool | None = None, bn: int | None = None, splits: int = 1,
-            out: torch.Tensor | None = None, bm: int | None = None) -> torch.Tensor:
+            out: torch.Tensor | None = None) -> torch.Tensor:
     """out = x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulate).
 
     `swap` puts output features on the M side of the MMA (few tokens); `bn` is the tile on the
-    other side; `bm` the rows of the M-side tile (128, or 64 when swapped with bn <= 64: chosen
-    when 128-row tiles would leave SMs without work); `splits` > 1 returns 32-bit partial
-    products [splits, tokens, out].
+    other side; `splits` > 1 returns 32-bit partial products [splits, tokens, out].
     """
     _on_gpu(x, w, bias, out)
     T, K = x.shape
@@ -366,8 +379,6 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
                 bn *= 2
         else:
             bn = 256 if gated else 128
-    if bm is None:
-        bm = _pick_bm(T, n_out, gated, swap, bn)
     if splits > 1:
         if gated or bias is not None:
             raise KernelError("split-K takes no bias and no gate")
@@ -384,7 +395,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
         assert out.dtype == odt and out.stride(1) == 1
         ld_out, f32 = out.stride(0), out_f32
     _check(lib("gemm_tc").lab_gemm_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                      int(gated), int(f32), int(swap), bm, bn, splits, _stream()), "gemm_tc")
+                                      int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
     return out
 
 
@@ -421,12 +432,46 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     return out
 
 
-def _pick_bm(T: int, n_out: int, gated: bool, swap: bool, bn: int) -> int:
-    """Rows of the M-side tile.  Tiles of 64 rows (swapped orientation, bn <= 64) double the CTAs of
-    a decode step's products, but measured slower at the benchmark's sizes (a step of 0.85 ms
-    against 0.82 ms): a step's kernels overlap under programmatic dependent launch, and more,
-    smaller CTAs get in one another's way.  So 128 unless the caller asks."""
-    return 128
+def qkv_fusable(x, w, head_dim: int, rotary_dim: int) -> bool:
+    """Whether `qkv_rope_store` serves this projection: bfloat16 operands the tensor-core product
+    takes, heads of 64 or 128 (a head must lie whole inside a tile), rotation over the whole head."""
+    return (x.dtype == torch.bfloat16 and not _force_plain and head_dim in (64, 128) and rotary_dim == head_dim
+            and _tc_operands(x, w))
+
+
+def qkv_rope_store(x, w_qkv, bias, table, slots, cache_k, cache_v, n_q: int, n_kv: int, head_dim: int,
+                   swap: bool | None = None, bn: int | None = None) -> torch.Tensor:
+    """The fused q/k/v projection with its epilogue in one kernel: x @ w_qkv.T + bias, rounded; q and k
+    rotated with the cosines and sines of `table` ([tokens, head_dim / 2, 2] from `rope_table`); the
+    rotated q returned [tokens, n_q * head_dim]; k and v written to their cache slots (`cache_k` None:
+    the call does not write the cache)."""
+    _on_gpu(x, w_qkv, bias, table, slots, cache_k, cache_v)
+    T, K = x.shape
+    width = (n_q + 2 * n_kv) * head_dim
+    if not qkv_fusable(x, w_qkv, head_dim, head_dim):
+        raise KernelError("qkv_rope_store takes bfloat16 operands with 16-byte rows and heads of 64 or 128")
+    assert w_qkv.shape == (width, K) and (bias is None or (bias.numel() == width and bias.dtype == x.dtype))
+    assert table.dtype == torch.float32 and table.is_contiguous() and table.shape == (T, head_dim // 2, 2)
+    page_size = num_pages = 0
+    if cache_k is not None:
+        num_pages, kvh, page_size, d = cache_k.shape
+        assert kvh == n_kv and d == head_dim and cache_k.is_contiguous() and cache_v.is_contiguous()
+        assert cache_v.shape == cache_k.shape and cache_k.dtype == x.dtype and slots is not None
+        assert slots.dtype == torch.int32 and slots.numel() >= T
+    if swap is None:
+        swap = T <= 128
+    if bn is None:
+        if swap:
+            bn = 16
+            while bn < T:
+                bn *= 2
+        else:
+            bn = _pick_prefill_tiles(T, width, K, False)[1]     # 128, or 256 where its waves cost less
+    q = torch.empty((T, n_q * head_dim), dtype=x.dtype, device=x.device)
+    _check(lib("gemm_tc").lab_gemm_tc_qkv(
+        _ptr(q), _ptr(x), _ptr(w_qkv), _ptr(bias), T, n_q, n_kv, head_dim, K, x.stride(0), q.stride(0), _ptr(table),
+        _ptr(slots), _ptr(cache_k), _ptr(cache_v), page_size, num_pages, int(swap), bn, _stream()), "gemm_tc_qkv")
+    return q
 
 
 def _pick_splits(T: int, n_out: int, K: int) -> int:
@@ -602,67 +647,6 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
                                       n_requests, n_q, n_kv, page_size, num_pages, window, ctypes.c_float(scale),
                                       splits, _ptr(scratch), 1 if in_cluster else 0, _stream()), "attention_decode",
                2 if splits > 1 and not in_cluster else 1)
-    return out
-
-
-# The fused decode attention (rotation + cache write + attention + merge in one kernel) is built and
-# tested, but off by default: with programmatic dependent launch the separate rotation kernel runs
-# beside the attention kernel's reads of metadata and old keys, and fusing them puts the rotation
-# back in front of the first tile (measured with the merge inside the cluster: 0.875 ms against
-# 0.823 ms per decode step at batch 8, 1.24 against 1.17 ms at batch 64).
-FUSE_DECODE_ATTENTION = False
-_decode_counters: dict = {}
-
-
-def _counters(device, n: int) -> torch.Tensor:
-    """Zeroed counters the fused decode attention leaves zero (kept per device)."""
-    key = str(device)
-    buf = _decode_counters.get(key)
-    if buf is None or buf.numel() < n:
-        buf = torch.zeros((max(n, 4096),), dtype=torch.int32, device=device)
-        _decode_counters[key] = buf
-    return buf
-
-
-def decode_fusable(dtype, head_dim: int, n_q: int, n_kv: int) -> bool:
-    return (dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim)
-            and n_q % n_kv == 0 and n_q // n_kv <= 16)
-
-
-def attention_decode_fused(qkv, bias, inv_freq, rotary_dim, slots, cache_k, cache_v, q_start, kv_len, block_table,
-                           n_requests, max_kv_len, n_q, n_kv, head_dim, window, scale, out=None, splits=None):
-    """A pure-decode step's attention with its prologue fused in: sum of the fused projection's
-    split-K partial products and bias (or the rounded projection), rotary encoding of q and of the
-    newest k, write of the newest k and v into their cache slots, attention, merge of the splits."""
-    _on_gpu(qkv, bias, inv_freq, slots, cache_k, cache_v, q_start, kv_len, block_table)
-    width = (n_q + 2 * n_kv) * head_dim
-    num_pages, kvh, page_size, d = cache_k.shape
-    assert kvh == n_kv and d == head_dim and cache_k.dtype == torch.bfloat16 and cache_k.is_contiguous()
-    partial = qkv.dim() == 3
-    tokens = qkv.shape[1] if partial else qkv.shape[0]
-    assert tokens == n_requests and qkv.shape[-1] == width and inv_freq.numel() == rotary_dim // 2
-    if out is None:
-        out = torch.empty((tokens, n_q * head_dim), dtype=torch.bfloat16, device=qkv.device)
-    if splits is None:
-        span = min(max_kv_len, window) if window else max_kv_len
-        splits = decode_splits(n_requests, n_kv, n_q // n_kv, span, *decode_shape(head_dim))
-    scratch = counters = None
-    in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and n_requests * n_kv * splits <= sm_count()
-    if splits > 1 and not in_cluster:
-        scratch = torch.empty((n_requests * n_q * splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
-        counters = _counters(qkv.device, n_requests * n_kv)
-    L = lib("attention_tc", {"LAB_HEAD_DIM": head_dim})
-    if partial:
-        assert qkv.dtype == torch.float32 and qkv.is_contiguous()
-        args = (None, width, _ptr(qkv), qkv.shape[0], ctypes.c_longlong(tokens * width), _ptr(bias))
-    else:
-        assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and bias is None
-        args = (_ptr(qkv), qkv.stride(0), None, 0, ctypes.c_longlong(0), None)
-    _check(L.lab_attention_decode_fused(
-        _ptr(out), out.stride(0), *args, _ptr(inv_freq), rotary_dim, _ptr(slots), _ptr(cache_k), _ptr(cache_v),
-        _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1], n_requests, n_q, n_kv, page_size,
-        num_pages, window, ctypes.c_float(scale), splits, _ptr(scratch), _ptr(counters), 1 if in_cluster else 0,
-        _stream()), "attention_decode_fused")
     return out
 
 

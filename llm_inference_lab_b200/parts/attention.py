@@ -59,20 +59,23 @@ class GQAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         group = ctx.groups[cache.group]
-        # With few tokens the product may come back as split-K partial sums (bias not yet added);
-        # the position encoding then sums them, adds the bias and rounds once.
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv, allow_partial=True)
-        rotary = getattr(self.position, "rotary", None)
-        if (ops.FUSE_DECODE_ATTENTION and ctx.max_q_len == 1 and cache.write and rotary is not None
-                and ops.decode_fusable(qkv.dtype if qkv.dim() == 2 else cache.k.dtype, self.d, self.n_q, self.n_kv)):
-            # Every request brings one token: rotation, cache write and attention run as one kernel.
-            attn = ops.attention_decode_fused(
-                qkv, self.b_qkv if qkv.dim() == 3 else None, rotary[0], rotary[1], group.row_slot, cache.k, cache.v,
-                ctx.q_start, ctx.kv_len, group.block_table, ctx.n_requests, ctx.max_kv_len, self.n_q, self.n_kv,
-                self.d, self.window, self.scale)
-            return ops.linear(attn, self.w_o, self.b_o, allow_partial=self.b_o is None)
-        q = self.position.rotate_and_store(qkv, ctx.row_pos, group.row_slot, cache, self.n_q, self.n_kv, self.d,
-                                           bias=self.b_qkv if qkv.dim() == 3 else None, scratch=ctx.scratch)
+        table_of = getattr(self.position, "table", None)
+        if (table_of is not None and x.shape[0] > 128
+                and ops.qkv_fusable(x, self.w_qkv, self.d, getattr(self.position, "rotary_dim", 0))):
+            # One kernel: projection, bias, rotation of q and k from the step's table of cosines and
+            # sines, k and v straight into their cache slots.  (Steps of few tokens keep the product
+            # with K split over more CTAs and the rotation kernel that sums its parts: measured faster
+            # there than nine CTAs that each walk the whole of K.)
+            write = cache.write
+            q = ops.qkv_rope_store(x, self.w_qkv, self.b_qkv, table_of(ctx.row_pos, ctx.scratch), group.row_slot,
+                                   cache.k if write else None, cache.v if write else None, self.n_q, self.n_kv, self.d)
+        else:
+            # With few tokens the product may come back as split-K partial sums (bias not yet added), if
+            # the position encoding takes them: it then sums them, adds the bias and rounds once.
+            partial = bool(getattr(self.position, "takes_partials", False))
+            qkv = ops.linear(x, self.w_qkv, self.b_qkv, allow_partial=partial)
+            q = self.position.rotate_and_store(qkv, ctx.row_pos, group.row_slot, cache, self.n_q, self.n_kv, self.d,
+                                               bias=self.b_qkv if qkv.dim() == 3 else None, scratch=ctx.scratch)
         attn = ops.attention(q, cache.k, cache.v, ctx, group, self.n_q, self.n_kv, self.d, self.window, self.scale)
         return ops.linear(attn, self.w_o, self.b_o, allow_partial=self.b_o is None)
 

@@ -116,13 +116,28 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """Encodes positions into q and k.  A new encoding defines `encode`; the paged store of k and v is
+    the framework's (`rotate_and_store` below), so an encoding never touches the cache.  An encoding
+    that brings a fused kernel of its own may override `rotate_and_store` as a whole, take the
+    projection's 32-bit split-K partial sums (`takes_partials`), or offer per-step cosines and sines
+    to the mixer's fused projection (`table`, see `Rope`)."""
+    takes_partials = False      # rotate_and_store accepts [splits, tokens, width] partial sums plus the bias
+
+    def encode(self, qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_kv: int, head_dim: int) -> None:
+        """Encodes, in place, the q heads (columns [0, n_q * d)) and the k heads (the next n_kv * d
+        columns) of the fused projection `qkv` [tokens, (n_q + 2 n_kv) * d]; `positions` [tokens] int32."""
+        raise NotImplementedError
+
     def rotate_and_store(self, qkv, positions, slots, cache: CacheView, n_q: int, n_kv: int, head_dim: int,
                          bias=None, scratch=None) -> torch.Tensor:
-        """Encodes q and k of the fused projection `qkv` ([tokens, (n_q + 2 n_kv) * d], or its
-        32-bit split-K partial products [splits, tokens, ...] with `bias` still to add), writes
-        k and v to the cache slots when the call may write, and returns the encoded q.  `scratch` is
-        the step's dictionary for buffers that layers may share (e.g. a table of angles)."""
-        raise NotImplementedError
+        """Encodes q and k of the fused projection `qkv`, writes k and v to the cache slots when the
+        call may write, and returns the encoded q.  `scratch` is the step's dictionary for buffers that
+        layers may share (e.g. a table of angles)."""
+        from ..kernels import ops
+        self.encode(qkv, positions, n_q, n_kv, head_dim)
+        write = cache is not None and cache.write
+        return ops.kv_store(qkv, slots if write else None, cache.k if write else None, cache.v if write else None,
+                            n_q, n_kv, head_dim)
 
 
 class Block:

@@ -123,6 +123,59 @@ def test_rope_table_path_equals_scalar_path(n_q, n_kv, d, rot):
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("swap", [False, True])
+@pytest.mark.parametrize("T,n_q,n_kv,d,K,ps,bias,write", [
+    (300, 14, 2, 64, 896, 16, True, True), (70, 3, 1, 64, 200, 8, False, True), (129, 2, 2, 128, 136, 32, True, True),
+    (700, 12, 2, 128, 1536, 16, True, True), (40, 5, 5, 64, 72, 4, True, False), (8, 14, 2, 64, 896, 16, True, True),
+    (1, 28, 4, 128, 3584, 16, True, True), (64, 6, 3, 128, 104, 64, False, True),
+])
+def test_fused_qkv_projection_equals_the_separate_kernels(T, n_q, n_kv, d, K, ps, bias, write, swap):
+    """The q/k/v projection with rotation and cache write in its epilogue against the three separate
+    steps (product with bias, rounded; rotation; paged store): the same bits in q and in every cache
+    slot that is written, and nothing else touched (the caches start as NaN; rows with slot -1 write
+    nothing).  Both orientations, heads of 64 and 128, ragged sizes, a call that may not write."""
+    if swap and T > 128:
+        pytest.skip("swapped orientation serves steps of few tokens")
+    g = torch.Generator().manual_seed(31)
+    width = (n_q + 2 * n_kv) * d
+    x = (torch.randn(T, K, generator=g) * 0.5).bfloat16().to(DEV)
+    w = (torch.randn(width, K, generator=g) * 0.1).bfloat16().to(DEV)
+    b = (torch.randn(width, generator=g)).bfloat16().to(DEV) if bias else None
+    pos = torch.randint(0, 5000, (T,), generator=g).int().to(DEV)
+    n_pages = -(-T // ps) + 3
+    slots = torch.randperm(n_pages * ps, generator=g)[:T].int()
+    slots[T // 2] = -1                                     # a row without a slot
+    slots = slots.to(DEV)
+    inv = torch.from_numpy(np.power(1e6, -2.0 * np.arange(d // 2) / d).astype(np.float32)).to(DEV)
+    table = ops().rope_table(pos, inv)
+
+    def caches():
+        return [torch.full((n_pages, n_kv, ps, d), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+
+    ck, cv = caches()
+    qkv = ops().gemm_tc(x, w, b, swap=False, bn=128)
+    want_q = ops().rope_kv_write(qkv, pos, inv, d, slots if write else None, ck if write else None,
+                                 cv if write else None, n_q, n_kv, d).clone()
+    fk, fv = caches()
+    got_q = ops().qkv_rope_store(x, w, b, table, slots, fk if write else None, fv if write else None, n_q, n_kv, d,
+                                 swap=swap)
+    ops().take_device_errors()
+    assert torch.equal(got_q, want_q)
+    for got, want in ((fk, ck), (fv, cv)):
+        assert torch.equal(torch.isnan(got.float()), torch.isnan(want.float())), "the same slots were written"
+        assert torch.equal(torch.nan_to_num(got.float()), torch.nan_to_num(want.float()))
+    if write:
+        assert int((~torch.isnan(fk.float())).sum()) == (T - 1) * n_kv * d
+    # and once against the 64-bit formulas
+    ref = x.double().cpu() @ w.double().cpu().T + (b.double().cpu() if bias else 0)
+    ref = ref.bfloat16().double()[:, : n_q * d].reshape(T, n_q, d)
+    ang = (pos.cpu().float()[:, None] * inv.cpu()[None, :]).double()
+    lo, hi = ref[..., : d // 2], ref[..., d // 2:]
+    rot = torch.cat([lo * ang.cos()[:, None] - hi * ang.sin()[:, None], hi * ang.cos()[:, None] + lo * ang.sin()[:, None]],
+                    dim=-1).reshape(T, n_q * d)
+    assert rel_err(got_q, rot) < 1e-2
+
+
 def test_rope_kv_write_from_split_k_partials():
     """The fused projection may arrive as 32-bit split-K partial sums with the bias still to add:
     the result equals summing, adding the bias, rounding once, and then the ordinary call."""
@@ -223,21 +276,21 @@ def test_gemm_tc_exact(T, N, K, gated, bias, swap, bn, splits):
     assert torch.equal(out.double().cpu(), ref)
 
 
-@pytest.mark.parametrize("bm", [64, 128])
 @pytest.mark.parametrize("T,N,K,gated,bias,bn,splits", [
     (8, 1152, 896, False, True, 16, 1), (8, 896, 4864, False, False, 16, 10), (5, 200, 104, True, False, 16, 1),
     (1, 4864, 896, True, False, 16, 1), (33, 1000, 200, False, True, 64, 1), (20, 20000, 64, False, False, 32, 1),
     (64, 4864, 896, True, False, 64, 1), (40, 136, 1000, True, False, 64, 1), (17, 72, 2000, False, False, 32, 7),
 ])
-def test_gemm_tc_swapped_tile_rows(bm, T, N, K, gated, bias, bn, splits):
-    """Swapped orientation with M-side tiles of 64 and of 128 rows: both exact, outputs with several
-    tiles per CTA, features that fill no whole tile, split K, the gated epilogue."""
+def test_gemm_tc_swapped_orientation(T, N, K, gated, bias, bn, splits):
+    """Swapped orientation (features on the 128-row side, a decode step's few tokens on the other):
+    exact, outputs with several tiles per CTA, features that fill no whole tile, split K, the gated
+    epilogue."""
     g = torch.Generator().manual_seed(16)
     x = (torch.randint(-4, 5, (T, K), generator=g).float() / 4).bfloat16()
     w = (torch.randint(-4, 5, (N * (2 if gated else 1), K), generator=g).float() / 8).bfloat16()
     b = (torch.randint(-8, 9, (N,), generator=g).float() / 2).bfloat16() if bias else None
     out = ops().gemm_tc(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), gated=gated,
-                        out_f32=not gated, swap=True, bn=bn, splits=splits, bm=bm)
+                        out_f32=not gated, swap=True, bn=bn, splits=splits)
     ops().take_device_errors()
     ref = x.double() @ w.double().T
     if splits > 1:
@@ -512,55 +565,6 @@ def test_attention_decode_cluster_merge(n_q, n_kv, d, window, splits):
     for a, b, w in zip(outs[True], outs[False], want):
         assert torch.equal(a, b)
         assert rel_err(a, w) < 2e-2
-
-
-@pytest.mark.parametrize("cluster", [True, False])
-@pytest.mark.parametrize("partial", [False, True])
-@pytest.mark.parametrize("n_q,n_kv,d,ps,window,rot,kvs,splits", [
-    (14, 2, 64, 16, 0, 64, [640, 33, 1, 257], None), (6, 1, 32, 8, 0, 32, [100, 7], 3),
-    (3, 3, 48, 8, 20, 48, [100, 19, 20, 21], None), (8, 2, 128, 32, 0, 64, [1000, 96], 4),
-    (4, 2, 16, 4, 0, 0, [9, 30], 2)])
-def test_attention_decode_fused(cluster, partial, n_q, n_kv, d, ps, window, rot, kvs, splits, monkeypatch):
-    """The fused decode kernel (partial sums + bias + rotation + cache write + attention + merge, through
-    the cluster's shared memory or by the last CTA) gives what the separate kernels give, and leaves
-    the same cache behind."""
-    monkeypatch.setattr(ops(), "CLUSTER_MERGE", cluster)
-    rng = np.random.default_rng(5)
-    B = len(kvs)
-    requests = [(kv, 1) for kv in kvs]
-    ck, cv, bt, ks, vs = build_paged(rng, requests, n_kv, d, ps, torch.bfloat16)
-    width = (n_q + 2 * n_kv) * d
-    part = torch.from_numpy(rng.standard_normal((4, B, width)).astype(np.float32))
-    bias = torch.from_numpy(rng.standard_normal(width).astype(np.float32)).bfloat16()
-    qkv_sum = part[0]
-    for s in range(1, 4):
-        qkv_sum = qkv_sum + part[s]
-    qkv = (qkv_sum + bias.float()).bfloat16()
-    inv = torch.from_numpy(np.power(1e4, -2.0 * np.arange(rot // 2) / max(rot, 1)).astype(np.float32))
-    kv_len = torch.tensor(kvs, dtype=torch.int32)
-    pos = kv_len - 1
-    blocks = torch.from_numpy(bt)
-    slots = torch.tensor([int(bt[b, (kv - 1) // ps]) * ps + (kv - 1) % ps for b, kv in enumerate(kvs)],
-                         dtype=torch.int32)
-    q_start = torch.arange(B + 1, dtype=torch.int32)
-    scale = 1.0 / math.sqrt(d)
-    dev = lambda a: a.to(DEV)  # noqa: E731
-    # separate kernels
-    ck1, cv1 = ck.clone().to(DEV), cv.clone().to(DEV)
-    q1 = ops().rope_kv_write(dev(qkv.clone()), dev(pos), dev(inv), rot, dev(slots), ck1, cv1, n_q, n_kv, d)
-    want = ops().attention_tc(q1, ck1, cv1, dev(q_start), dev(kv_len), dev(pos), dev(blocks), B, [1] * B, max(kvs),
-                              n_q, n_kv, d, window, scale, splits=splits)
-    # fused, twice in a row (the counters must come back to zero)
-    for _ in range(2):
-        ck2, cv2 = ck.clone().to(DEV), cv.clone().to(DEV)
-        src = dev(part) if partial else dev(qkv)
-        got = ops().attention_decode_fused(src, dev(bias) if partial else None, dev(inv), rot, dev(slots), ck2, cv2,
-                                           dev(q_start), dev(kv_len), dev(blocks), B, max(kvs), n_q, n_kv, d, window,
-                                           scale, splits=splits)
-        ops().take_device_errors()
-        held = torch.isfinite(ck1.float()) | torch.isfinite(ck2.float())
-        assert torch.equal(ck1[held], ck2[held]) and torch.equal(cv1[held], cv2[held]), "same cache contents"
-        assert rel_err(got, want.double()) < 2e-2
 
 
 @pytest.mark.parametrize("kind,dtype", [("plain", torch.float32), ("plain", torch.bfloat16), ("tc", torch.bfloat16)])

@@ -372,20 +372,18 @@ def define_toy_routed():
 
     class StridedRope(PositionEncoding):
         """Rotary encoding whose angle grows `stride` times as fast: position p is encoded as
-        p * stride.  Built on the framework's rotation kernel, with positions of its own."""
+        p * stride.  It only encodes (here with the framework's rotation kernel and positions of its
+        own); the paged store of k and v is the framework's."""
 
         def __init__(self, spec, weights, dtype, device):
             super().__init__(spec, weights, dtype, device)
             d = int(spec["rotary_dim"])
             inv = np.power(float(spec["theta"]), -2.0 * np.arange(d // 2, dtype=np.float64) / d).astype(np.float32)
             self.inv_freq, self.rotary_dim, self.stride = torch.from_numpy(inv).to(device), d, int(spec["stride"])
-            self.rotary = None      # no fused kernel may take this rotation over
 
-        def rotate_and_store(self, qkv, positions, slots, cache, n_q, n_kv, head_dim, bias=None, scratch=None):
-            write = cache is not None and cache.write
-            return ops.rope_kv_write(qkv, positions * self.stride, self.inv_freq, self.rotary_dim,
-                                     slots if write else None, cache.k if write else None,
-                                     cache.v if write else None, n_q, n_kv, head_dim, bias=bias)
+        def encode(self, qkv, positions, n_q, n_kv, head_dim):
+            ops.rope_kv_write(qkv, positions * self.stride, self.inv_freq, self.rotary_dim, None, None, None, n_q,
+                              n_kv, head_dim)
 
     register_part("feed_forward", "top1_experts", Top1Experts)
     register_part("position", "strided_rope", StridedRope)
