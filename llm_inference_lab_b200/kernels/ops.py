@@ -119,12 +119,27 @@ def _on_gpu(*tensors) -> None:
             raise KernelError("kernel arguments must be CUDA tensors")
 
 
+_error_hooks: list = []
+
+
+def on_device_error(method) -> None:
+    """The bound method `method` is called when `take_device_errors` finds an error (to put scratch
+    state right again); held weakly, so that it does not keep its object alive."""
+    import weakref
+    _error_hooks[:] = [h for h in _error_hooks if h() is not None]
+    _error_hooks.append(weakref.WeakMethod(method))
+
+
 def take_device_errors() -> None:
     """Synchronise and raise if any kernel left an error code."""
     for key, handle in list(_libs.items()):
         out = ctypes.c_int(0)
-        _check(handle.lab_take_error_word(ctypes.byref(out)), "reading the error word")
+        _check(handle.lab_take_error_word(ctypes.byref(out)), "reading the error word", 0)
         if out.value:
+            for hook in _error_hooks:
+                method = hook()
+                if method is not None:
+                    method()
             raise KernelError(f"kernel library {key.split('[')[0]} reported: "
                               f"{DEVICE_ERRORS.get(out.value, out.value)}")
 
@@ -345,6 +360,10 @@ def sm_count() -> int:
         else:
             _sm_count = 148
     return _sm_count
+
+
+def forced_plain() -> bool:
+    return _force_plain
 
 
 def force_plain(flag: bool) -> bool:

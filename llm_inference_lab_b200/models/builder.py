@@ -19,6 +19,10 @@ from ..profiling import scoped_range
 from ..parts.spec import CacheNeed, ModelBlueprint, PagedKV, TensorSpec
 
 
+# False: pure decode steps run part by part as every other step does (tests compare the two).
+USE_DECODE_STACK = True
+
+
 def _part_classes(bp: ModelBlueprint):
     yield lookup("embedding", bp.embedding.kind), bp.embedding
     for layer in bp.layers:
@@ -93,6 +97,9 @@ class CausalLM:
         self.final_norm = lookup("norm", bp.final_norm.kind)(bp.final_norm, weights, dtype, device)
         self.head = lookup("head", bp.head.kind)(bp.head, weights, dtype, device)
         self.order = bp.order
+        # pure decode steps of few tokens run all layer calls as one kernel where the layers fit it
+        from .decode_stack import DecodeStack
+        self.decode_stack = DecodeStack.build(self.blocks, bp.order, dtype, device) if str(device) != "cpu" else None
         self.range_names = [f"layer.{call.layer}" for call in bp.order]     # profiling ranges
         self.cache_plan = cache_plan(bp)
 
@@ -101,7 +108,14 @@ class CausalLM:
         with scoped_range("embedding"):
             x = self.embedding.forward(ctx.token_ids)
         pending = None
-        for call, name in zip(self.order, self.range_names):
+        stack = self.decode_stack
+        if stack is not None and USE_DECODE_STACK and stack.serves(ctx, caches):
+            with scoped_range("decode_stack"):
+                stack.run(x, ctx, caches)
+            calls = ()
+        else:
+            calls = zip(self.order, self.range_names)
+        for call, name in calls:
             view = caches[call.cache]
             if not call.write:
                 view = dataclasses.replace(view, write=False)

@@ -628,3 +628,54 @@ def test_a_layer_reads_the_cache_another_layer_fills(tmp_path, dtype):
     ok(whole, want[2], "whole prompt on pages used again")
     engine.close(2)
     assert engine.free_pages() == [engine.num_pages]
+
+
+@pytest.mark.parametrize("name,lengths", [("F", [5, 40, 130, 64, 65, 1, 300, 17, 33, 128, 2, 90, 70, 200, 9, 250]),
+                                          ("G", [150, 3, 64])])
+def test_decode_stack_equals_the_parts_it_replaces(tmp_path, name, lengths):
+    """A decode step of few tokens that is launched kernel by kernel runs its layers as one persistent
+    kernel (phases between grid-wide barriers) where the model's layers fit it.  The same steps run part
+    by part give the same logits up to bfloat16 rounding, both are the plain implementation's, and the
+    fused step is a handful of launches.  Heads of 64 and of 128, a window, batches of 16 and of 3,
+    histories that end on page edges, a width that is no multiple of the k-tile."""
+    from llm_inference_lab_b200.engine import Engine, Entry
+    from llm_inference_lab_b200.kernels import ops
+    from llm_inference_lab_b200.models import builder
+    from plain_qwen2 import plain_forward
+
+    cfg, opt = TINY[name]
+    folder = make_model_folder(str(tmp_path / name), cfg, opt["seed"], "bfloat16")
+    rng = np.random.default_rng(3)
+    steps = 4
+    seqs = [random_tokens(rng, n + steps, cfg["vocab_size"]) for n in lengths]
+    outs, launches = {}, {}
+    for fused in (False, True):
+        builder.USE_DECODE_STACK = fused
+        try:
+            engine = Engine(folder, "bfloat16", max_tokens=4096, page_size=opt["page_size"], max_requests=len(lengths))
+            assert engine.model.decode_stack is not None
+            for i, ids in enumerate(seqs):
+                engine.step([Entry(i, ids[: lengths[i]], [])])
+            got = []
+            for s in range(steps):
+                before = ops.COUNTER.launches
+                logits = engine.step([Entry(i, [ids[lengths[i] + s]], [0]) for i, ids in enumerate(seqs)])
+                launches[fused] = ops.COUNTER.launches - before
+                got.append(logits.float().cpu().numpy())
+            ops.take_device_errors()
+            outs[fused] = np.stack(got)           # [steps, requests, vocab]
+            for i in range(len(seqs)):
+                engine.close(i)
+            assert engine.cache.live_requests == 0
+        finally:
+            builder.USE_DECODE_STACK = True
+    assert launches[True] <= 6 < launches[False], launches
+    pcfg, w = read_model_folder(folder)
+    want = np.stack([np.stack([plain_forward(pcfg, w, ids)[lengths[i] + s] for i, ids in enumerate(seqs)])
+                     for s in range(steps)])
+    scale = np.abs(want).max()
+    for fused in (False, True):
+        err = np.abs(outs[fused] - want).max() / scale
+        rms = np.sqrt(((outs[fused] - want) ** 2).mean() / (want ** 2).mean())
+        assert err < 0.12 and rms < 0.045, (fused, err, rms)
+    assert np.abs(outs[True] - outs[False]).max() / scale < 0.08
