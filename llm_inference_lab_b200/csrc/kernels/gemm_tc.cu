@@ -6,6 +6,11 @@
 //   gated:      out[t, n] = T( silu(g) * u ),  g = x . w[n], u = x . w[inter + n]   (32-bit, one rounding)
 //   split-K:    partial[z, t, n] = sum over the z-th slice of k   (32-bit, summed by the
 //               kernel that consumes it, in a fixed order)
+//   pick:       the output head of a step that wants tokens, not logits: every tile keeps, per
+//               token, its best candidate (the logit, or logit / temperature + Gumbel noise) and
+//               a second, tiny kernel picks each token's best over all tiles; the logits are
+//               never written (kernels.rs:1489-1552 is the reference's two-stage arg-max over
+//               logits it has stored)
 //   q/k/v:      the fused projection of an attention layer with its epilogue: bias, rounding,
 //               split-half rotary encoding of the q and k heads with cosines and sines from the
 //               step's table, q to the activation, k and v straight into their cache pages
@@ -38,6 +43,8 @@
 // Formulas and rounding order: rust/engine/src/runner/model/qwen2/kernels.rs:156-178,
 // 393-418 (32-bit accumulation, bias added in 32-bit, one rounding), 422-448 and 1469-1486
 // (gate/up with the SiLU product), 300-387 (split-K partials merged in 32-bit).
+#include <limits.h>
+
 #include "tcgen05.cuh"
 
 namespace {
@@ -48,7 +55,7 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
-enum Mode : int { PLAIN = 0, GATED_SILU = 1, QKV_ROPE = 2 };
+enum Mode : int { PLAIN = 0, GATED_SILU = 1, QKV_ROPE = 2, PICK = 3 };
 
 // Where the q/k/v epilogue finds its angles and puts its results.
 struct QkvStore {
@@ -58,6 +65,28 @@ struct QkvStore {
   const float2* table;      // [tokens, d / 2] (cos, sin) of position * inv_freq
   int n_q, n_kv, d, page_size, num_pages;
 };
+
+// What the picking head needs: one token per row, greedy where the temperature is 0 (ties to the
+// smallest index, a NaN never wins, a row of NaNs gives INT32_MAX), else Gumbel-max with the hash of
+// (seed, position, index) the sampling kernel uses.
+struct PickArgs {
+  int* tokens;                 // [rows] out
+  const float* temperature;    // [rows] or null (greedy)
+  const uint32_t* seeds;       // [rows]
+  const int* positions;        // [rows]
+  float* part_val;             // [rows, m_tiles] best candidate of each tile
+  int* part_idx;
+};
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7FEB352Du;
+  x ^= x >> 15;
+  x *= 0x846CA68Bu;
+  x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
 struct Params {
   void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats;
@@ -72,6 +101,7 @@ struct Params {
   int up_offset;        // gated: row offset of the "up" half inside the weight matrix
   int m_tiles, n_tiles, splits;  // tiles on the M side, on the N side, and split-K planes
   QkvStore qkv;         // q/k/v epilogue only
+  PickArgs pick;        // picking head only
 };
 
 // Element offset of (slot, kv head) in a cache of [pages, n_kv, page_size, d], or -1 (no slot; a
@@ -147,6 +177,7 @@ struct Shape {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // swapped, gated or q/k/v: the epilogue warps exchange rows of the tile through a buffer of their own
   static constexpr int EXCHANGE_BYTES = (MODE != PLAIN && SWAP) ? ((TM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
+  static_assert(MODE != PICK || SWAP, "the picking head runs with the vocabulary on the 128-row side");
   static constexpr int STAGES_RAW = (SMEM_BUDGET - EXCHANGE_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
   static constexpr int ACC_COLS = BN < 32 ? 32 : BN;
@@ -314,7 +345,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     // ---- epilogue: warps 2..5, each reads its quarter of the 128 accumulator lanes ----
     const int quarter = warp & 3;
     constexpr int QROWS = TM / 4;            // tile rows in a quarter: one per lane
-    constexpr bool has_row = true;
     pdl_wait();  // the output may still be read by an earlier kernel until it has completed
     int local = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
@@ -360,6 +390,70 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           }
         }
         release();
+      } else if constexpr (MODE == PICK) {
+        // thread = vocabulary entry m; columns = tokens.  Every candidate of the tile goes through the
+        // exchange buffer (an entry that may not win, beyond the vocabulary or the step's rows, as NaN:
+        // a NaN never wins); then each token's best over the tile's 128 entries is found by a few
+        // threads that scan a share of the rows in ascending order, so that ties go to the smaller index.
+        const PickArgs& a = p.pick;
+        const int tile_row = quarter * QROWS + lane;
+#pragma unroll 1
+        for (int c = 0; c < BN / 16 && go; ++c) {
+          if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
+          float v[16];
+          tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int tok = n0 + c * 16 + j;
+            float val = __int_as_float(0x7fc00000);
+            if (m < p.m_rows && tok < p.n_rows) {
+              val = v[j];
+              const float temp = a.temperature ? a.temperature[tok] : 0.f;
+              if (temp > 0.f) {
+                const uint32_t key = mix32(mix32(a.seeds[tok] ^ 0x9E3779B9u) ^ (uint32_t)a.positions[tok]);
+                const uint32_t h = mix32(key + (uint32_t)m * 0x85EBCA6Bu);
+                const float u = ((float)(h >> 9) + 0.5f) * (1.f / 8388608.f);
+                val = val * (1.f / temp) - logf(-logf(u));
+              }
+            }
+            exchange[tile_row * (BN + 1) + c * 16 + j] = val;
+          }
+        }
+        release();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // PARTS threads per token, each a share of the rows; then the shares of a token are combined
+        constexpr int PARTS = 128 / BN > 0 ? 128 / BN : 1, SHARE = TM / PARTS;
+        const int t = threadIdx.x - 64, col = t % BN, part = t / BN;
+        float bv = -INFINITY;
+        int bi = INT_MAX;
+        if (go && part < PARTS && n0 + col < p.n_rows) {
+#pragma unroll 8
+          for (int r = part * SHARE; r < (part + 1) * SHARE; ++r) {
+            const float val = exchange[r * (BN + 1) + col];
+            if (better(val, m0 + r, bv, bi)) {
+              bv = val;
+              bi = m0 + r;
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // every share is read: the buffer's first rows take the results
+        int* exch_idx = reinterpret_cast<int*>(exchange) + 128;
+        exchange[t] = bv;
+        exch_idx[t] = bi;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (go && t < BN && n0 + t < p.n_rows) {
+          bv = -INFINITY;
+          bi = INT_MAX;
+#pragma unroll
+          for (int q = 0; q < PARTS; ++q)
+            if (better(exchange[q * BN + t], exch_idx[q * BN + t], bv, bi)) {
+              bv = exchange[q * BN + t];
+              bi = exch_idx[q * BN + t];
+            }
+          a.part_val[(size_t)(n0 + t) * p.m_tiles + m0 / TM] = bv;
+          a.part_idx[(size_t)(n0 + t) * p.m_tiles + m0 / TM] = bi;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
       } else if constexpr (MODE == QKV_ROPE) {
         // thread = feature m of the fused projection; columns = tokens.  The tile's 128 rows are whole
         // heads; the two halves of a head meet through the exchange buffer, which holds the
@@ -584,7 +678,7 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Para
     case 32: if constexpr (SWAP) return launch<MODE, 32, SWAP, OutT>(ma, mb, p, grid, s); break;
     case 64: if constexpr (MODE != QKV_ROPE || SWAP) return launch<MODE, 64, SWAP, OutT>(ma, mb, p, grid, s); break;
     case 128: if constexpr (WIDE) return launch<MODE, 128, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 256: if constexpr (WIDE && !(MODE == QKV_ROPE && SWAP)) return launch<MODE, 256, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 256: if constexpr (WIDE && !(MODE == QKV_ROPE && SWAP) && MODE != PICK) return launch<MODE, 256, SWAP, OutT>(ma, mb, p, grid, s); break;
   }
   return (int)cudaErrorInvalidValue;
 }
@@ -629,6 +723,56 @@ int set_up(Params& p, CUtensorMap& ma, CUtensorMap& mb, dim3& grid, const void* 
   const long long tiles = (long long)p.m_tiles * p.n_tiles * splits;
   grid = dim3((unsigned)(tiles < sm_count() ? tiles : sm_count()));
   return 0;
+}
+
+// The second stage of the picking head: one block per token reduces the tiles' candidates.
+__global__ void __launch_bounds__(128) pick_finish_kernel(int* __restrict__ tokens, const float* __restrict__ part_val,
+                                                          const int* __restrict__ part_idx, int tiles) {
+  __shared__ float sv[4];
+  __shared__ int si[4];
+  pdl_trigger();
+  pdl_wait();
+  const int tok = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = INT_MAX;
+  for (int c0 = threadIdx.x; c0 < tiles; c0 += 128 * 4) {   // four loads in flight
+    float v[4];
+    int i[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + 128 * u;
+      v[u] = c < tiles ? part_val[(size_t)tok * tiles + c] : -INFINITY;
+      i[u] = c < tiles ? part_idx[(size_t)tok * tiles + c] : INT_MAX;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (better(v[u], i[u], bv, bi)) {
+        bv = v[u];
+        bi = i[u];
+      }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = bv;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int q = 1; q < 4; ++q)
+      if (better(sv[q], si[q], bv, bi)) {
+        bv = sv[q];
+        bi = si[q];
+      }
+    tokens[tok] = bi;
+  }
 }
 
 // For tests of the bounded waits: one warp waits on a barrier that nobody ever arrives at, with a
@@ -683,6 +827,32 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
   }
   if (out_f32) return dispatch_bn<PLAIN, false, float>(bn, ma, mb, p, grid, stream);
   return dispatch_bn<PLAIN, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+}
+
+// The output head of a step that wants tokens: tokens[t] = the pick over n_out logits x[t] . w[n] (greedy where
+// temperature is null or 0, else Gumbel-max with seeds and positions).  tokens <= bn <= 128.
+// part_val / part_idx: [tokens * ceil(n_out / 128)] scratch.  Two launches: the product, and the pick over its tiles.
+LAB_EXPORT int lab_gemm_tc_pick(int* out_tokens, const void* x, const void* w, int tokens, int n_out, int K, int ldx,
+                                const float* temperature, const void* seeds, const int* positions, float* part_val,
+                                int* part_idx, int bn, cudaStream_t stream) {
+  if (tokens <= 0 || n_out <= 0) return 0;
+  if (K % 8 || ldx % 8 || K <= 0 || tokens > bn || bn > 128) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return (int)cudaErrorInvalidValue;
+  if (!part_val || !part_idx || (temperature && (!seeds || !positions))) return (int)cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  Params p = {};
+  p.pick.tokens = out_tokens;
+  p.pick.temperature = temperature;
+  p.pick.seeds = (const uint32_t*)seeds;
+  p.pick.positions = positions;
+  p.pick.part_val = part_val;
+  p.pick.part_idx = part_idx;
+  dim3 grid;
+  int rc = set_up(p, ma, mb, grid, x, w, tokens, n_out, n_out, K, ldx, 0, 1, bn, 1);
+  if (rc) return rc;
+  if ((rc = dispatch_bn<PICK, true, float>(bn, ma, mb, p, grid, stream))) return rc;
+  return (int)lab_launch(pick_finish_kernel, dim3(tokens), dim3(128), 0, stream, out_tokens, (const float*)part_val,
+                         (const int*)part_idx, p.m_tiles);
 }
 
 // The fused q/k/v projection of an attention layer with its epilogue.

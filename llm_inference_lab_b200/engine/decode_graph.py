@@ -13,8 +13,8 @@ the real ones belong to requests of length zero, whose keys and values go
 nowhere and whose attention reads nothing, so a batch that shrinks request by
 request, as in continuous batching, walks through a handful of graphs instead
 of one per size.  All graphs share one memory pool: they never run side by
-side, and what a step leaves in the pool (its logits) is read before the next
-step is launched or not at all.
+side, and nothing a step leaves in the pool is read later (the sampled ids live
+in buffers of their own).
 
 The reference does the same for pure-decode steps: fixed metadata and source
 buffers uploaded before replay, graphs keyed by (slot table, batch, splits), a
@@ -46,7 +46,6 @@ class _Captured:
     seeds: torch.Tensor         # view [rows_cap] int32
     rows: torch.Tensor          # [rows_cap] int32: 0..rows_cap-1, the rows whose logits are computed
     host_tokens: torch.Tensor   # [rows_cap] int32 in pinned memory: the sampled ids, copied by the graph itself
-    logits: Optional[torch.Tensor] = None   # [rows_cap, vocab] float32 of the last replay (lives in the shared pool)
     launches: int = 0           # kernels the graph holds
 
 
@@ -88,12 +87,11 @@ class DecodeGraphs:
         widths = [eng.max_blocks] * len(eng.group_windows)
         return eng._context(cap.dev, cap.layout, widths, n, n, [1] * n, [kv_bucket] * n, [], cap.tokens)
 
-    def _run(self, cap: _Captured, ctx: StepContext) -> torch.Tensor:
-        logits = self.engine.model.forward(ctx, self.engine.views, cap.rows)
-        # position of the token being drawn = tokens held after this step
-        ops.sample(logits, cap.temps, cap.seeds, ctx.kv_len, out=cap.tokens)
+    def _run(self, cap: _Captured, ctx: StepContext) -> None:
+        # position of the token being drawn = tokens held after this step; the head picks the tokens
+        # itself, so a decode step writes no logits
+        self.engine.model.forward(ctx, self.engine.views, cap.rows, pick=(cap.temps, cap.seeds, ctx.kv_len, cap.tokens))
         cap.host_tokens.copy_(cap.tokens, non_blocking=True)   # part of the graph: no launch of its own later
-        return logits
 
     def _new_capture(self, key):
         eng = self.engine
@@ -221,7 +219,7 @@ class DecodeGraphs:
                 self._pool = torch.cuda.graph_pool_handle()
             before = ops.COUNTER.launches
             with torch.cuda.graph(cap.graph, pool=self._pool):
-                cap.logits = self._run(cap, ctx)
+                self._run(cap, ctx)
             cap.launches = ops.COUNTER.launches - before
             ops.COUNTER.launches = before            # captured, not yet run
             self.cached[key] = cap
@@ -244,7 +242,3 @@ class DecodeGraphs:
         copy into pinned memory)."""
         self._done.synchronize()
         return self._last.host_tokens[: len(self._last_requests)].tolist()
-
-    def last_logits(self) -> torch.Tensor:
-        """The logits [requests, vocab] of the last step; valid until the next step is launched."""
-        return self._last.logits[: len(self._last_requests)]

@@ -200,28 +200,31 @@ class Engine:
         if len(entries) > self.max_requests:
             raise InvalidInput(f"{len(entries)} requests in one step exceed max_requests {self.max_requests}")
 
-    def step(self, entries: Sequence[Entry], reserved: bool = False) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[Entry], reserved: bool = False, pick=None) -> Optional[torch.Tensor]:
         """Runs one packed batch.  Returns 32-bit logits [wanted, vocab] on the device, in
         the order of the entries and of their `want`, or None if nothing was wanted.
 
-        With ``reserved`` the caller (the scheduler) has reserved the pages already.
+        With ``reserved`` the caller (the scheduler) has reserved the pages already.  With ``pick`` =
+        (temperatures, seeds, positions), device tensors with one element per wanted place (or three
+        Nones for greedy), the step returns one token id per wanted place (int32 on the device)
+        instead of logits: the head picks them itself and no logits are written.
         """
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
         self.validate(entries, reserved)
         if not profiling.ON:
-            return self._step(entries, reserved)
+            return self._step(entries, reserved, pick)
         # The reference's label: a prefill step if any request brings more than one token or holds
         # nothing yet (rust/engine/src/runner/model/qwen2/engine.rs:862-864).
         prefill = any(len(e.tokens) > 1 or not self.cache.has(e.request) or self.cache.length(e.request) == 0
                       for e in entries)
         with profiling.scoped_range("step.prefill" if prefill else "step.decode"):
-            return self._step(entries, reserved)
+            return self._step(entries, reserved, pick)
 
-    def _step(self, entries: Sequence[Entry], reserved: bool) -> Optional[torch.Tensor]:
+    def _step(self, entries: Sequence[Entry], reserved: bool, pick=None) -> Optional[torch.Tensor]:
         pairs = [(int(e.request), len(e.tokens)) for e in entries]
         began = self._begin(pairs, reserved)
         try:
-            logits = self._run(entries)
+            logits = self._run(entries, pick)
         except Exception:
             self._fail(began)
             raise
@@ -284,9 +287,10 @@ class Engine:
                 self.stats.prefill_tokens += n
 
     # ------------------------------------------------------------------------------------
-    def _run(self, entries: Sequence[Entry]):
-        """Packs the step and runs the model, eagerly or from a CUDA graph of the same shape."""
-        if self._graphs_on:
+    def _run(self, entries: Sequence[Entry], pick=None):
+        """Packs the step and runs the model, eagerly or from a CUDA graph of the same shape (a step
+        that picks its tokens itself runs eagerly)."""
+        if self._graphs_on and pick is None:
             max_kv = max(self.cache.reserved(e.request) for e in entries)
             bucket = 256
             while bucket < max_kv:
@@ -308,6 +312,8 @@ class Engine:
             if seen >= 2 and seen & (seen - 1) == 0:
                 return self._capture(sig, entries, bucket)
         ctx, logit_rows = self._pack(entries)
+        if pick is not None and logit_rows is not None:
+            return self.model.forward(ctx, self.views, logit_rows, pick=(*pick, None))
         return self.model.forward(ctx, self.views, logit_rows)
 
     def _capture(self, sig, entries, bucket):

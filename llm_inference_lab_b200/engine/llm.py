@@ -115,9 +115,15 @@ class LLM:
                 seeds = [c.seed for c in cfgs]
                 entries = [Entry(e.id, sched.portion(e.id, e.start, e.n), [e.n - 1] if e.sample else [])
                            for e in plan]
-                logits = self.engine.step(entries, reserved=True)
-                if logits is not None:
-                    sampled = self.sampler.pick(logits, temps, seeds, [e.start + e.n for e in rows])
+                positions = [e.start + e.n for e in rows]
+                if rows and not self.cuda_graph:
+                    # the head picks the tokens itself: no logits are written
+                    tokens = self.engine.step(entries, reserved=True, pick=self.sampler.device_args(temps, seeds, positions))
+                    sampled = self.sampler.check(tokens.cpu().tolist(), self.engine.vocab)
+                else:
+                    logits = self.engine.step(entries, reserved=True)
+                    if logits is not None:
+                        sampled = self.sampler.pick(logits, temps, seeds, positions)
             except Exception:
                 sched.abandon(plan)
                 raise

@@ -493,6 +493,53 @@ def qkv_rope_store(x, w_qkv, bias, table, slots, cache_k, cache_v, n_q: int, n_k
     return q
 
 
+_pick_scratch: dict = {}
+# Rows up to which a step's head picks its tokens itself (the kernel takes up to 128).  Measured at the
+# Qwen2.5-0.5B sizes against the head that writes 32-bit logits for the sampling kernel: a decode step of
+# 8 or 16 rows takes the same time (0.792 ms both ways; 0.812 against 0.814 ms) without the 5 to 10 MB of
+# logits written and read back; at 32 rows the pick in the epilogue costs more than the logits' traffic
+# (0.980 against 0.950 ms), at 64 rows 1.16 against 1.14 ms.
+PICK_MAX_ROWS = 16
+
+
+def head_pick_fusable(x, w) -> bool:
+    """Whether `head_pick` serves this head: bfloat16 operands the tensor-core product takes, few rows."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and not _force_plain
+            and x.shape[0] <= min(PICK_MAX_ROWS, 128) and _tc_operands(x, w))
+
+
+def head_pick(x, w, temperature=None, seeds=None, positions=None, out=None) -> torch.Tensor:
+    """One token per row of x from the head's logits x @ w.T without writing them: every tile of the
+    product keeps its best candidate per row (greedy, or Gumbel-max where `temperature` > 0, by the
+    sampling kernel's rule) and a second, tiny kernel picks each row's best."""
+    _on_gpu(x, w, temperature, seeds, positions, out)
+    T, K = x.shape
+    vocab = w.shape[0]
+    if not (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and T <= 128 and _tc_operands(x, w)):
+        raise KernelError("head_pick takes bfloat16 operands with 16-byte rows and up to 128 rows")
+    if temperature is not None:
+        assert temperature.dtype == torch.float32 and seeds.dtype == torch.int32 and positions.dtype == torch.int32
+        assert temperature.numel() >= T and seeds.numel() >= T and positions.numel() >= T
+    if out is None:
+        out = torch.empty((T,), dtype=torch.int32, device=x.device)
+    assert out.dtype == torch.int32 and out.numel() >= T
+    tiles = -(-vocab // 128)
+    key = str(x.device)
+    buf = _pick_scratch.get(key)
+    if buf is None or buf[0].numel() < T * tiles:
+        cap = max(T, 128) * tiles
+        buf = (torch.empty((cap,), dtype=torch.float32, device=x.device),
+               torch.empty((cap,), dtype=torch.int32, device=x.device))
+        _pick_scratch[key] = buf
+    bn = 16
+    while bn < T:
+        bn *= 2
+    _check(lib("gemm_tc").lab_gemm_tc_pick(_ptr(out), _ptr(x), _ptr(w), T, vocab, K, x.stride(0), _ptr(temperature),
+                                           _ptr(seeds), _ptr(positions), _ptr(buf[0]), _ptr(buf[1]), bn, _stream()),
+           "gemm_tc_pick", 2)
+    return out
+
+
 def _pick_splits(T: int, n_out: int, K: int) -> int:
     """Split K when an output has too few tiles to keep the memory system busy (decode)."""
     if T > 128:

@@ -103,8 +103,10 @@ class CausalLM:
         self.range_names = [f"layer.{call.layer}" for call in bp.order]     # profiling ranges
         self.cache_plan = cache_plan(bp)
 
-    def forward(self, ctx: StepContext, caches: list[CacheView], logit_rows: torch.Tensor | None):
-        """Runs the rows of `ctx`; returns 32-bit logits [len(logit_rows), vocab] or None."""
+    def forward(self, ctx: StepContext, caches: list[CacheView], logit_rows: torch.Tensor | None, pick=None):
+        """Runs the rows of `ctx`; returns 32-bit logits [len(logit_rows), vocab] or None.  With
+        `pick` = (temperatures, seeds, positions, out), each [len(logit_rows)] on the device, it returns one
+        token per wanted row instead (`Head.pick`)."""
         with scoped_range("embedding"):
             x = self.embedding.forward(ctx.token_ids)
         pending = None
@@ -125,6 +127,8 @@ class CausalLM:
             return None
         with scoped_range("final_norm+head"):
             h = self.final_norm.forward_add(x, pending, rows=logit_rows)
+            if pick is not None:
+                return self.head.pick(h, *pick)
             return self.head.forward(h)
 
 

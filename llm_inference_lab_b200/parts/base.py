@@ -163,6 +163,13 @@ class Head(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def pick(self, x: torch.Tensor, temperature, seeds, positions, out=None) -> torch.Tensor:
+        """One token per row (int32): greedy where `temperature` is None or 0, else sampled with the
+        row's seed at its position.  The default forms the logits and lets the sampling kernel pick; a
+        head may do both in one pass."""
+        from ..kernels import ops
+        return ops.sample(self.forward(x), temperature, seeds, positions, out=out)
+
 
 MIXERS: dict[str, type] = {}
 FEED_FORWARDS: dict[str, type] = {}

@@ -41,6 +41,12 @@ class LinearHead(Head):
     def forward(self, x):
         return ops.linear(x, self.weight, None, out_f32=True)
 
+    def pick(self, x, temperature, seeds, positions, out=None):
+        # In one pass where the tensor-core product serves: the [rows, vocab] logits are never written.
+        if ops.head_pick_fusable(x, self.weight):
+            return ops.head_pick(x, self.weight, temperature, seeds, positions, out=out)
+        return super().pick(x, temperature, seeds, positions, out=out)
+
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("head", "linear_head", LinearHead)

@@ -72,6 +72,16 @@ class Sampler:
         assert len(tokens) == rows
         return tokens
 
+    def device_args(self, temperatures: Sequence[float], seeds: Sequence[int], positions: Sequence[int]):
+        """(temperatures, seeds, positions) on the device for a step that picks its own tokens
+        (`Engine.step(..., pick=...)`); three Nones when every row is greedy."""
+        if not any(t > 0 for t in temperatures):
+            return (None, None, None)
+        meta = torch.tensor([list(temperatures)], dtype=torch.float32).to(self.device, non_blocking=True)
+        ints = torch.tensor([[s & 0x7FFFFFFF for s in seeds], list(positions)], dtype=torch.int32).to(
+            self.device, non_blocking=True)
+        return (meta[0], ints[0], ints[1])
+
     @staticmethod
     def check(tokens: list[int], vocab: int) -> list[int]:
         """A row without any finite candidate comes back as INT32_MAX (sampling.cu)."""

@@ -639,3 +639,36 @@ def test_sample_temperature_matches_plain(vocab):
                          torch.tensor(seeds[3:4], dtype=torch.int32).to(DEV),
                          torch.tensor(positions[3:4], dtype=torch.int32).to(DEV)).cpu().tolist()
     assert again[0] == out[3]
+
+
+@pytest.mark.parametrize("rows,vocab,K", [(1, 503, 64), (6, 151936, 896), (40, 5003, 200), (128, 3000, 104)])
+def test_head_that_picks_equals_head_then_sampling(rows, vocab, K):
+    """The output head that keeps each tile's best candidate and lets the last CTA pick, against the
+    head that writes 32-bit logits followed by the sampling kernel: the same tokens, greedy rows and
+    rows with a temperature side by side; a row of NaN reports INT32_MAX; ties go to the smaller index."""
+    g = torch.Generator().manual_seed(40 + rows)
+    x = (torch.randn(rows, K, generator=g)).bfloat16()
+    w = (torch.randn(vocab, K, generator=g) * 0.2).bfloat16()
+    if vocab > 300:
+        w[vocab - 7] = w[11]                       # two entries with the same logits in every row: a tie
+    if rows > 2:
+        x[2] = float("nan")
+    temps = torch.tensor([0.0 if r % 3 == 0 else 0.5 + 0.1 * r for r in range(rows)])
+    seeds = torch.arange(rows, dtype=torch.int32) * 977 + 5
+    positions = torch.arange(rows, dtype=torch.int32) * 3 + 1
+    xd, wd = x.to(DEV), w.to(DEV)
+    for args in ((None, None, None), (temps.to(DEV), seeds.to(DEV), positions.to(DEV))):
+        got = ops().head_pick(xd, wd, *args).cpu().tolist()
+        want = ops().sample(ops().gemm_tc(xd, wd, out_f32=True), *args).cpu().tolist()
+        ops().take_device_errors()
+        assert got == want
+        if rows > 2:
+            assert got[2] == 2**31 - 1
+    greedy = ops().head_pick(xd, wd).cpu().tolist()
+    ref = (x.double() @ w.double().T)
+    for r in range(rows):
+        if r != 2 or rows <= 2:
+            best = float(ref[r].max())
+            assert float(ref[r, greedy[r]]) >= best - 1e-3 * max(1.0, abs(best))
+            if vocab > 300 and greedy[r] in (11, vocab - 7):
+                assert greedy[r] == 11
