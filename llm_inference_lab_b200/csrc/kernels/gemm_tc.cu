@@ -28,9 +28,12 @@
 // orientation a tile's N side is half gate rows, half up rows (two TMA loads), so a thread's
 // accumulator row holds both; in swapped orientation a tile's M side is 64 gate rows over 64 up
 // rows of the same features, and the epilogue warps exchange them through shared memory.
-// The q/k/v epilogue needs a head whole inside a tile (heads of 64 or 128): in normal orientation a
-// thread holds a token's row and rotates pairs of its own columns; in swapped orientation a thread
-// holds a feature, and the two halves of a head meet through the same exchange buffer.
+// The q/k/v epilogue needs a head whole inside a tile (heads of 64 or 128) and runs in normal
+// orientation: a thread holds a token's row and rotates pairs of its own columns.  (Steps of few
+// tokens keep the plain product with K in slices and the rotation kernel that sums them: in swapped
+// orientation the epilogue measured slower both with nine CTAs that walk the whole of K, 0.875
+// against 0.80 ms a decode step at batch 8, and with K in slices and the last CTA of a tile rotating
+// and storing for all its tokens, 0.90 ms.)
 //
 // CTAs are persistent (one per SM at most) and walk the output tiles: warp 0 issues TMA loads
 // into a ring of stages that runs on across tiles, warp 1 issues the MMAs (one elected lane)
@@ -175,9 +178,10 @@ struct Shape {
   static constexpr int A_BYTES = TM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  // swapped, gated or q/k/v: the epilogue warps exchange rows of the tile through a buffer of their own
-  static constexpr int EXCHANGE_BYTES = (MODE != PLAIN && SWAP) ? ((TM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
+  // swapped, gated or picking: the epilogue warps exchange rows of the tile through a buffer of their own
+  static constexpr int EXCHANGE_BYTES = ((MODE == GATED_SILU || MODE == PICK) && SWAP) ? ((TM * (BN + 1) * 4 + 1023) / 1024) * 1024 : 0;
   static_assert(MODE != PICK || SWAP, "the picking head runs with the vocabulary on the 128-row side");
+  static_assert(MODE != QKV_ROPE || !SWAP, "the q/k/v epilogue runs with tokens on the 128-row side");
   static constexpr int STAGES_RAW = (SMEM_BUDGET - EXCHANGE_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
   static constexpr int ACC_COLS = BN < 32 ? 32 : BN;
@@ -357,7 +361,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       const uint32_t lane_addr = tmem_base + buf * S::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       const int m = m0 + quarter * QROWS + lane;  // this thread's row on the M side
       const bool partial = p.split_stride != 0;
-      // Decided once per thread; the swapped gated and q/k/v epilogues meet at named barriers, which every
+      // Decided once per thread; the swapped gated and picking epilogues meet at named barriers, which every
       // epilogue thread reaches whatever it decided.
       const bool go = __all_sync(0xffffffffu, ok && !*abort_flag);
       bool released = false;
@@ -452,55 +456,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             }
           a.part_val[(size_t)(n0 + t) * p.m_tiles + m0 / TM] = bv;
           a.part_idx[(size_t)(n0 + t) * p.m_tiles + m0 / TM] = bi;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
-      } else if constexpr (MODE == QKV_ROPE) {
-        // thread = feature m of the fused projection; columns = tokens.  The tile's 128 rows are whole
-        // heads; the two halves of a head meet through the exchange buffer, which holds the
-        // projection's values with the bias added, rounded as the projection alone would have stored them.
-        const QkvStore& e = p.qkv;
-        const int tile_row = quarter * QROWS + lane;
-        const float b = (p.bias && m < p.m_rows) ? __bfloat162float(p.bias[m]) : 0.f;
-#pragma unroll 1
-        for (int c = 0; c < BN / 16 && go; ++c) {
-          if (n0 + c * 16 >= p.n_rows) break;  // same for the whole warp
-          float v[16];
-          tmem_ld16(lane_addr + c * 16, v);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) exchange[tile_row * (BN + 1) + c * 16 + j] = round_to<__nv_bfloat16>(v[j] + b);
-        }
-        release();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (go && m < p.m_rows) {
-          const int d = e.d, half = d / 2, head = m / d, j = m - head * d;
-          const bool rotate = head < e.n_q + e.n_kv, is_lo = j < half;
-          const float* mine = exchange + tile_row * (BN + 1);
-          const float* other = exchange + (is_lo ? tile_row + half : tile_row - half) * (BN + 1);
-          __nv_bfloat16* base = nullptr;   // q: column m of the activation; k, v: element j of the cache row
-          const bool to_cache = head >= e.n_q;
-          const bool is_k = head < e.n_q + e.n_kv;
-          if (!to_cache) base = (__nv_bfloat16*)p.out + m;
-          else if (e.cache_k != nullptr) base = (is_k ? e.cache_k : e.cache_v) + j;
-          if (base != nullptr) {
-            const int kvh = is_k ? head - e.n_q : head - e.n_q - e.n_kv;
-            for (int col = 0; col < BN; ++col) {
-              const int tok = n0 + col;
-              if (tok >= p.n_rows) break;
-              float val = mine[col];
-              if (rotate) {
-                const float2 f = e.table[(size_t)tok * half + (is_lo ? j : j - half)];
-                float lo, hi;
-                if (is_lo) rope_rotate(val, other[col], f.x, f.y, lo, hi), val = lo;
-                else rope_rotate(other[col], val, f.x, f.y, lo, hi), val = hi;
-              }
-              if (!to_cache) {
-                base[(size_t)tok * p.ld_out] = __float2bfloat16_rn(val);
-              } else {
-                const long long at = cache_row_offset(e, e.row_slot[tok], kvh);
-                if (at >= 0) base[at] = __float2bfloat16_rn(val);
-              }
-            }
-          }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
       } else if constexpr (!SWAP) {
@@ -674,11 +629,11 @@ template <int MODE, bool SWAP, typename OutT>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t s) {
   constexpr bool WIDE = !(MODE == GATED_SILU && SWAP);  // the gated exchange buffer is sized for up to 64 tokens
   switch (bn) {
-    case 16: if constexpr (SWAP) return launch<MODE, 16, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 32: if constexpr (SWAP) return launch<MODE, 32, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 64: if constexpr (MODE != QKV_ROPE || SWAP) return launch<MODE, 64, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 16: if constexpr (SWAP && MODE != QKV_ROPE) return launch<MODE, 16, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 32: if constexpr (SWAP && MODE != QKV_ROPE) return launch<MODE, 32, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 64: if constexpr (MODE != QKV_ROPE) return launch<MODE, 64, SWAP, OutT>(ma, mb, p, grid, s); break;
     case 128: if constexpr (WIDE) return launch<MODE, 128, SWAP, OutT>(ma, mb, p, grid, s); break;
-    case 256: if constexpr (WIDE && !(MODE == QKV_ROPE && SWAP) && MODE != PICK) return launch<MODE, 256, SWAP, OutT>(ma, mb, p, grid, s); break;
+    case 256: if constexpr (WIDE && MODE != PICK) return launch<MODE, 256, SWAP, OutT>(ma, mb, p, grid, s); break;
   }
   return (int)cudaErrorInvalidValue;
 }
@@ -863,7 +818,7 @@ LAB_EXPORT int lab_gemm_tc_pick(int* out_tokens, const void* x, const void* w, i
 // Heads of 64 or 128 (a head must lie whole inside a tile), rotation over the whole head.
 LAB_EXPORT int lab_gemm_tc_qkv(void* q_out, const void* x, const void* w, const void* bias, int tokens, int n_q,
                                int n_kv, int d, int K, int ldx, int ld_q, const void* table, const int* row_slot,
-                               void* cache_k, void* cache_v, int page_size, int num_pages, int swap, int bn,
+                               void* cache_k, void* cache_v, int page_size, int num_pages, int bn,
                                cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if ((d != 64 && d != 128) || n_q <= 0 || n_kv <= 0) return (int)cudaErrorInvalidValue;
@@ -873,7 +828,7 @@ LAB_EXPORT int lab_gemm_tc_qkv(void* q_out, const void* x, const void* w, const 
     return (int)cudaErrorInvalidValue;
   if (table == nullptr || ((cache_k != nullptr) && (cache_v == nullptr || row_slot == nullptr || page_size <= 0)))
     return (int)cudaErrorInvalidValue;
-  if (!swap && bn % d) return (int)cudaErrorInvalidValue;   // whole heads in a tile
+  if (bn % d) return (int)cudaErrorInvalidValue;   // whole heads in a tile
   const int n_out = (n_q + 2 * n_kv) * d;
   CUtensorMap ma, mb;
   Params p = {};
@@ -891,9 +846,8 @@ LAB_EXPORT int lab_gemm_tc_qkv(void* q_out, const void* x, const void* w, const 
   p.qkv.page_size = page_size;
   p.qkv.num_pages = num_pages;
   dim3 grid;
-  const int rc = set_up(p, ma, mb, grid, x, w, tokens, n_out, n_out, K, ldx, 0, swap, bn, 1);
+  const int rc = set_up(p, ma, mb, grid, x, w, tokens, n_out, n_out, K, ldx, 0, 0, bn, 1);
   if (rc) return rc;
-  if (swap) return dispatch_bn<QKV_ROPE, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
   return dispatch_bn<QKV_ROPE, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
 }
 

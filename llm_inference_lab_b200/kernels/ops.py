@@ -459,11 +459,12 @@ def qkv_fusable(x, w, head_dim: int, rotary_dim: int) -> bool:
 
 
 def qkv_rope_store(x, w_qkv, bias, table, slots, cache_k, cache_v, n_q: int, n_kv: int, head_dim: int,
-                   swap: bool | None = None, bn: int | None = None) -> torch.Tensor:
+                   bn: int | None = None) -> torch.Tensor:
     """The fused q/k/v projection with its epilogue in one kernel: x @ w_qkv.T + bias, rounded; q and k
     rotated with the cosines and sines of `table` ([tokens, head_dim / 2, 2] from `rope_table`); the
     rotated q returned [tokens, n_q * head_dim]; k and v written to their cache slots (`cache_k` None:
-    the call does not write the cache)."""
+    the call does not write the cache).  Tokens lie on the 128-row side of the product: for steps of
+    many tokens."""
     _on_gpu(x, w_qkv, bias, table, slots, cache_k, cache_v)
     T, K = x.shape
     width = (n_q + 2 * n_kv) * head_dim
@@ -477,19 +478,12 @@ def qkv_rope_store(x, w_qkv, bias, table, slots, cache_k, cache_v, n_q: int, n_k
         assert kvh == n_kv and d == head_dim and cache_k.is_contiguous() and cache_v.is_contiguous()
         assert cache_v.shape == cache_k.shape and cache_k.dtype == x.dtype and slots is not None
         assert slots.dtype == torch.int32 and slots.numel() >= T
-    if swap is None:
-        swap = T <= 128
     if bn is None:
-        if swap:
-            bn = 16
-            while bn < T:
-                bn *= 2
-        else:
-            bn = _pick_prefill_tiles(T, width, K, False)[1]     # 128, or 256 where its waves cost less
+        bn = _pick_prefill_tiles(T, width, K, False)[1]     # 128, or 256 where its waves cost less
     q = torch.empty((T, n_q * head_dim), dtype=x.dtype, device=x.device)
     _check(lib("gemm_tc").lab_gemm_tc_qkv(
         _ptr(q), _ptr(x), _ptr(w_qkv), _ptr(bias), T, n_q, n_kv, head_dim, K, x.stride(0), q.stride(0), _ptr(table),
-        _ptr(slots), _ptr(cache_k), _ptr(cache_v), page_size, num_pages, int(swap), bn, _stream()), "gemm_tc_qkv")
+        _ptr(slots), _ptr(cache_k), _ptr(cache_v), page_size, num_pages, bn, _stream()), "gemm_tc_qkv")
     return q
 
 

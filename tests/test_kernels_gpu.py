@@ -123,19 +123,16 @@ def test_rope_table_path_equals_scalar_path(n_q, n_kv, d, rot):
     assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("swap", [False, True])
 @pytest.mark.parametrize("T,n_q,n_kv,d,K,ps,bias,write", [
     (300, 14, 2, 64, 896, 16, True, True), (70, 3, 1, 64, 200, 8, False, True), (129, 2, 2, 128, 136, 32, True, True),
     (700, 12, 2, 128, 1536, 16, True, True), (40, 5, 5, 64, 72, 4, True, False), (8, 14, 2, 64, 896, 16, True, True),
     (1, 28, 4, 128, 3584, 16, True, True), (64, 6, 3, 128, 104, 64, False, True),
 ])
-def test_fused_qkv_projection_equals_the_separate_kernels(T, n_q, n_kv, d, K, ps, bias, write, swap):
+def test_fused_qkv_projection_equals_the_separate_kernels(T, n_q, n_kv, d, K, ps, bias, write):
     """The q/k/v projection with rotation and cache write in its epilogue against the three separate
     steps (product with bias, rounded; rotation; paged store): the same bits in q and in every cache
     slot that is written, and nothing else touched (the caches start as NaN; rows with slot -1 write
-    nothing).  Both orientations, heads of 64 and 128, ragged sizes, a call that may not write."""
-    if swap and T > 128:
-        pytest.skip("swapped orientation serves steps of few tokens")
+    nothing).  Heads of 64 and 128, ragged sizes down to one token, a call that may not write."""
     g = torch.Generator().manual_seed(31)
     width = (n_q + 2 * n_kv) * d
     x = (torch.randn(T, K, generator=g) * 0.5).bfloat16().to(DEV)
@@ -157,8 +154,7 @@ def test_fused_qkv_projection_equals_the_separate_kernels(T, n_q, n_kv, d, K, ps
     want_q = ops().rope_kv_write(qkv, pos, inv, d, slots if write else None, ck if write else None,
                                  cv if write else None, n_q, n_kv, d).clone()
     fk, fv = caches()
-    got_q = ops().qkv_rope_store(x, w, b, table, slots, fk if write else None, fv if write else None, n_q, n_kv, d,
-                                 swap=swap)
+    got_q = ops().qkv_rope_store(x, w, b, table, slots, fk if write else None, fv if write else None, n_q, n_kv, d)
     ops().take_device_errors()
     assert torch.equal(got_q, want_q)
     for got, want in ((fk, ck), (fv, cv)):
