@@ -213,6 +213,45 @@ class EagerDecode:
         return self.tokens
 
 
+def run_stack_stamps(engine, batch, rng):
+    """The decode stack's own clock: CTA 0 stamps every phase (start, first operand built, first item
+    done, all items done) and every CTA stamps the end of its share; printed per kind of phase."""
+    import numpy as np
+    import torch
+    from llm_inference_lab_b200.engine import Entry
+
+    stack = engine.model.decode_stack
+    if stack is None:
+        return {"error": "the model's layers do not fit the decode stack"}
+    calls = len(stack.order)
+    for r in range(batch):
+        engine.step([Entry(r, [int(t) for t in rng.integers(0, engine.vocab, PROMPT_LEN)], [])])
+    stack.stamps = torch.zeros((4 * 5 * calls + 1 + 5 * calls * stack.grid,), dtype=torch.int64, device="cuda")
+    for _ in range(4):
+        engine.step([Entry(r, [5], [0]) for r in range(batch)])
+        torch.cuda.synchronize()
+    full = stack.stamps.cpu().numpy().astype(np.int64)
+    stack.stamps = None
+    for r in range(batch):
+        engine.close(r)
+    t, per = full[: 4 * 5 * calls + 1], full[4 * 5 * calls + 1:].reshape(5 * calls, stack.grid)
+    ph = t[:-1].reshape(calls, 5, 4)
+    starts = np.concatenate([t[:-1].reshape(-1, 4)[:, 0], t[-1:]])
+    out = {"kernel_us": round(float(t[-1] - t[0]) / 1e3, 1), "layer_calls": calls, "batch": batch, "phases": {}}
+    skip = min(2, calls - 1)
+    for k, name in enumerate(["qkv", "attention", "o_proj", "gate_up", "down"]):
+        length = (starts[1:] - starts[:-1]).reshape(calls, 5)[skip:, k]
+        entry = {"phase_us": round(float(length.mean()) / 1e3, 2)}
+        if k != 1:      # (the warp that stamps takes no part in the attention phase)
+            done = (per.reshape(calls, 5, -1)[skip:, k] - ph[skip:, k, 0][:, None]) / 1e3
+            entry["cta_done_us_median"] = round(float(np.median(done)), 2)
+            entry["cta_done_us_max"] = round(float(done.max(1).mean()), 2)
+            entry["cta0_operand_us"] = round(float((ph[skip:, k, 1] - ph[skip:, k, 0]).mean()) / 1e3, 2)
+            entry["cta0_item_us"] = round(float((ph[skip:, k, 2] - ph[skip:, k, 1]).mean()) / 1e3, 2)
+        out["phases"][name] = entry
+    return out
+
+
 def median_region(regions):
     ordered = sorted(regions, key=lambda r: r[0])
     return ordered[len(ordered) // 2]
@@ -346,6 +385,9 @@ def main() -> int:
     ap.add_argument("--serve", type=int, default=0, metavar="REQUESTS",
                     help="instead of the headline run: REQUESTS prompts of 128..2,048 tokens through LLM.generate "
                          "with 512 tokens a step and 128 new tokens each (continuous batching); prints its own line")
+    ap.add_argument("--stack-stamps", action="store_true",
+                    help="run a few eager decode steps with the decode stack's in-kernel clock on and print what "
+                         "each kind of phase took")
     ap.add_argument("--only-prefill", type=int, default=0, metavar="TOKENS",
                     help="run only a prefill of TOKENS tokens a few times and print its time (for profiling)")
     args = ap.parse_args()
@@ -392,6 +434,9 @@ def main() -> int:
     graphs = DecodeGraphs(engine)
     engine.enable_step_graphs()   # a prefill of a repeating shape is replayed from a CUDA graph
 
+    if args.stack_stamps:
+        print(json.dumps(run_stack_stamps(engine, args.batch, rng)))
+        return 0
     if args.only_prefill:
         PREFILL_TOKENS = args.only_prefill
         pms = run_prefill(engine, rng, repeats=2)
