@@ -406,7 +406,7 @@ def main() -> int:
     cfg = SHAPES[args.shape]
     args.layers = args.layers or cfg["num_hidden_layers"]
     headline = args.shape == "0.5B" and PROMPT_LEN == 512
-    max_seq = max(4096, PROMPT_LEN + NEW_TOKENS + PAGE_SIZE)
+    max_seq = max(4096, PROMPT_LEN + NEW_TOKENS + PAGE_SIZE, args.only_prefill + PAGE_SIZE)
     live = max(64 if headline else 0, args.batch)      # requests that hold pages at the same time
 
     import numpy as np
@@ -429,8 +429,9 @@ def main() -> int:
         print(json.dumps(out))
         return 0
     rng = np.random.default_rng(0)
-    engine = Engine(folder, "bf16", max_tokens=live * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + 4096, page_size=PAGE_SIZE,
-                    max_requests=live, max_batch_tokens=max(8192, PROMPT_LEN), max_seq_len=max_seq)
+    engine = Engine(folder, "bf16", max_tokens=live * (PROMPT_LEN + NEW_TOKENS + PAGE_SIZE) + max(4096, args.only_prefill),
+                    page_size=PAGE_SIZE,
+                    max_requests=live, max_batch_tokens=max(8192, PROMPT_LEN, args.only_prefill), max_seq_len=max_seq)
     graphs = DecodeGraphs(engine)
     engine.enable_step_graphs()   # a prefill of a repeating shape is replayed from a CUDA graph
 
