@@ -139,19 +139,6 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
 // through a private ring of shared-memory stages; the warps' softmax states are merged at
 // the end.  With several splits the CTA leaves (acc, max, sum) in scratch for the merge kernel.
 // ----------------------------------------------------------------------------------------
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// The address, in the cluster's shared window, of `addr` (shared, this CTA) in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, int rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-
 // A warp's instructions depend on one another (ldmatrix, mma, shuffles, exp2, mma), so a tile takes
 // a warp microseconds, and what keeps the memory system busy is the number of warps per SM.  Heads
 // of up to 64: 4 warps with tiles of 32 keys, two CTAs per SM.  Larger heads: 12 warps with tiles of

@@ -17,7 +17,15 @@
 // rescaled in place only when its maximum has grown by more than a factor of 256 since the reference
 // it is held against, and divided by the sum at the end.  (Measured slower: for heads of 64 an
 // accumulator in registers, rescaled every tile from two O buffers, by 10 %; two CTAs per SM with one
-// S buffer each, by 70 % at 2,048 tokens and 6 % at 8,192.)
+// S buffer each, by 70 % at 2,048 tokens and 6 % at 8,192.  No faster: two groups of four softmax warps
+// that share the key tiles, even and odd, each with an S buffer, an O and running maxima of its own,
+// merged at the end; 2.96 ms a 2,048-token prefill of 24 layers either way.  In-kernel clocks of the
+// CTA with the most keys showed why: a warp's 128 ex2 of a tile take about 1,000 cycles of the one
+// special-function unit of its SM sub-partition, which two groups can only share; a group that has
+// handed over P waits about 1,500 cycles for its next scores (wake the MMA warp, issue P V, issue S,
+// the MMAs, wake the group), which the other group's exponentials fill but do not shorten; the first
+// scores of a CTA arrive 5,000 cycles after its start and the masked tile on the diagonal takes twice
+// the time of a full one.)
 // Formulas as the reference's tensor-core prefill attention
 // (rust/engine/src/runner/model/qwen2/kernels.rs:946-1124, 1295-1452): scores scaled by 1/sqrt(d)
 // (folded into the exp2 argument), key <= query, p rounded to T before PV, o = acc / sum.

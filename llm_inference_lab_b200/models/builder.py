@@ -84,6 +84,8 @@ def cache_plan(bp: ModelBlueprint) -> CachePlan:
 class CausalLM:
     """Embedding, blocks in the blueprint's order, final norm, head."""
 
+    decode_stack = None     # the one kernel that runs all layer calls of a small decode step, where the layers fit it
+
     def __init__(self, bp: ModelBlueprint, weights: dict[str, torch.Tensor], dtype: torch.dtype, device):
         self.blueprint, self.dtype, self.device = bp, dtype, device
         weights = dict(weights)
