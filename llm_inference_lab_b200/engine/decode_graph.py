@@ -88,6 +88,10 @@ class DecodeGraphs:
         return eng._context(cap.dev, cap.layout, widths, n, n, [1] * n, [kv_bucket] * n, [], cap.tokens)
 
     def _run(self, cap: _Captured, ctx: StepContext) -> None:
+        # What the parts share within a step (the table of rotation angles, for one) is formed anew in
+        # every run: the run that is captured must hold the kernels that fill it, not find what the
+        # warm-up run before it left.
+        ctx.scratch.clear()
         # position of the token being drawn = tokens held after this step; the head picks the tokens
         # itself, so a decode step writes no logits
         self.engine.model.forward(ctx, self.engine.views, cap.rows, pick=(cap.temps, cap.seeds, ctx.kv_len, cap.tokens))

@@ -302,6 +302,8 @@ def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tenso
 
 
 _sample_scratch: dict = {}
+# Scratch that was outgrown stays alive: a CUDA graph captured earlier still launches kernels with its address.
+_retired_scratch: list = []
 
 
 def _sample_buffers(device, rows: int, chunks: int):
@@ -314,6 +316,7 @@ def _sample_buffers(device, rows: int, chunks: int):
         buf = (torch.empty((cap,), dtype=torch.float32, device=device),
                torch.empty((cap,), dtype=torch.int32, device=device),
                torch.zeros((cap_rows,), dtype=torch.int32, device=device))
+        _retired_scratch.append(_sample_scratch.get(key))
         _sample_scratch[key] = buf
     return buf
 
@@ -524,6 +527,7 @@ def head_pick(x, w, temperature=None, seeds=None, positions=None, out=None) -> t
         cap = max(T, 128) * tiles
         buf = (torch.empty((cap,), dtype=torch.float32, device=x.device),
                torch.empty((cap,), dtype=torch.int32, device=x.device))
+        _retired_scratch.append(_pick_scratch.get(key))
         _pick_scratch[key] = buf
     bn = 16
     while bn < T:

@@ -116,6 +116,32 @@ def test_bfloat16_greedy_is_near_plain(tmp_path_factory):
         check_teacher_forced(folder, prompt, res.tokens, 0.0, 0, 0.2)
 
 
+@pytest.mark.parametrize("name,requests", [("F", 130), ("G", 200)])
+@pytest.mark.parametrize("graph", [False, True])
+def test_bfloat16_decoding_of_many_requests_at_once(tmp_path_factory, name, requests, graph):
+    """Decode steps of 128 rows and more take other routes than small ones (the rotation reads its
+    angles from a table that the step's layers share, the products run with tokens on the 128-row
+    side): eagerly and from CUDA graphs, whose captured kernels must fill that table themselves in every
+    replay.  Every token is near the plain implementation's best at its position."""
+    from llm_inference_lab_b200.engine.llm import LLM
+    from llm_inference_lab_b200.kernels import ops
+    from llm_inference_lab_b200.sampling import SamplingConfig
+
+    cfg, opt = TINY[name]
+    folder = folder_of(tmp_path_factory, name, "bfloat16")
+    rng = np.random.default_rng(31)
+    prompts = [random_tokens(rng, int(rng.integers(1, 12)), cfg["vocab_size"]) for _ in range(requests)]
+    llm = LLM(folder, "bf16", page_size=opt["page_size"], kv_tokens=requests * 32, max_requests=requests,
+              cuda_graph=graph)
+    results = llm.generate(prompts, SamplingConfig(max_new_tokens=6, ignore_eos=True))
+    ops.take_device_errors()
+    if graph:
+        assert any(rows >= 128 for rows, _ in llm.graphs.cached), "no decode step of 128 rows or more"
+    for i in range(0, requests, 7):
+        check_teacher_forced(folder, prompts[i], results[i].tokens, 0.0, 0, 0.2)
+    assert llm.engine.cache.live_requests == 0
+
+
 def test_eos_and_options(tmp_path_factory):
     from llm_inference_lab_b200.engine.llm import LLM
     from llm_inference_lab_b200.sampling import SamplingConfig
