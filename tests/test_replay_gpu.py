@@ -308,6 +308,53 @@ def test_qwen25_05b_all_24_layers_in_32_bit(tmp_path):
     assert err <= F32_ABS, f"max abs error {err:.3e} (largest logit {np.abs(want).max():.2f})"
 
 
+def test_qwen25_15b_layer_sizes_bfloat16_against_the_32_bit_engine(tmp_path):
+    """The next larger benchmark shape (hidden 1,536, 12/2 heads of 128, intermediate 8,960; two of its 28
+    layers, N(0, 0.02) weights): heads of 128 and wider products take other tiles, kernels and splits than
+    the 0.5B sizes.  The bfloat16 engine is held against the 32-bit engine on the same weights (which the
+    other tests hold against the plain implementation): prompts that run on every prefill route, decode
+    steps of 1 to 200 rows, eagerly and from CUDA graphs."""
+    import torch
+    from llm_inference_lab_b200.engine import Engine, Entry
+    from llm_inference_lab_b200.engine.decode_graph import DecodeGraphs
+    from llm_inference_lab_b200.kernels import ops
+
+    cfg = dict(QWEN25_05B, hidden_size=1536, intermediate_size=8960, num_hidden_layers=2, num_attention_heads=12,
+               num_key_value_heads=2, max_position_embeddings=8192)
+    folder = make_model_folder(str(tmp_path / "m"), cfg, seed=3, dtype="bfloat16", std=0.02, scales={})
+    engines = {dt: Engine(folder, dt, max_tokens=40000, page_size=16, max_requests=256, max_batch_tokens=2048,
+                          max_seq_len=2048) for dt in ("float32", "bfloat16")}
+    vocab = cfg["vocab_size"]
+    rng = np.random.default_rng(0)
+    bound = 0.03     # of the largest logit of the step; two layers of this size measure 0.007 to 0.011
+
+    def both(entries):
+        out = {dt: e.step(entries).float() for dt, e in engines.items()}
+        return float((out["bfloat16"] - out["float32"]).abs().max() / out["float32"].abs().max())
+
+    for r, n in enumerate((5, 70, 130, 300, 1000)):
+        err = both([Entry(r, random_tokens(rng, n, vocab), sorted({0, n // 2, n - 1}))])
+        record(dtype="bfloat16", shape="1.5B", prefill=n, rel=err)
+        assert err <= bound, f"prefill of {n} tokens: {err:.4f}"
+    for r in range(5, 200):
+        toks = random_tokens(rng, int(rng.integers(1, 80)), vocab)
+        for e in engines.values():
+            e.step([Entry(r, toks, [])])
+    for B in (1, 8, 17, 64, 128, 200):
+        err = both([Entry(r, random_tokens(rng, 1, vocab), [0]) for r in range(B)])
+        record(dtype="bfloat16", shape="1.5B", decode=B, rel=err)
+        assert err <= bound, f"decode step of {B} rows: {err:.4f}"
+    graphs = DecodeGraphs(engines["bfloat16"])
+    for B in (3, 64, 130):
+        toks = random_tokens(rng, B, vocab)
+        ref = engines["float32"].step([Entry(r, [t], [0]) for r, t in enumerate(toks)]).float()
+        got = graphs.step(list(range(B)), tokens=toks).long()
+        gap = (ref.max(dim=1).values - ref.gather(1, got[:, None])[:, 0]) / ref.abs().max(dim=1).values
+        assert float(gap.max()) <= bound, f"graph decode of {B} rows picked a token {float(gap.max()):.4f} below the best"
+    ops.take_device_errors()
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("kind", ["whole", "tail", "portions", "mixed"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_reference_tiny_model(tmp_path_factory, dtype, kind):
