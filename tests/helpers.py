@@ -85,12 +85,19 @@ def random_tokens(rng, n, vocab):
     return [int(t) for t in rng.integers(0, vocab, size=n)]
 
 
-def plain_logits(folder, sequences):
-    """{name: [len, vocab] float64} of whole sequences by the plain implementation."""
-    from plain_qwen2 import plain_forward, read_model_folder
+def plain_logits(folder, sequences, twin=None):
+    """{name: [len, vocab] float64} of whole sequences by the plain implementation.  `twin`: "float32"
+    computes in 32-bit, "bfloat16" rounds every operator's result to bfloat16: what the arithmetic of an
+    engine of that type alone does to these logits."""
+    import contextlib
+
+    from plain_qwen2 import plain_forward, plain_precision, read_model_folder, round_bfloat16
 
     cfg, w = read_model_folder(folder)
-    return {name: plain_forward(cfg, w, ids) for name, ids in sequences.items()}
+    how = {None: contextlib.nullcontext(), "float32": plain_precision(np.float32),
+           "bfloat16": plain_precision(edge=round_bfloat16)}[twin]
+    with how:
+        return {name: np.asarray(plain_forward(cfg, w, ids), dtype=np.float64) for name, ids in sequences.items()}
 
 
 # ----------------------------------------------------------------------------------------

@@ -14,13 +14,49 @@ the lines of the reference whose formula it restates.  Where the reference
 rounds to its storage type T between operators, this file does not (T is
 float64 here); the 32-bit engine is compared with a tight tolerance and the
 bfloat16 engine with the band the reference itself uses for T = bf16.
+
+How far rounding alone moves the logits of a given model is measured with the same
+functions: inside `plain_precision(np.float32)` they compute in 32-bit, and inside
+`plain_precision(edge=round_bfloat16)` every operator's result is rounded to
+bfloat16 where the reference's T = bf16 kernels round (kernels.rs:393-418 one
+rounding per product, 546-582 norm, 587-631 rotation, 802-828 p rounded before
+P V, 1469-1486 the gated product, the residual sum).  A test may hold an engine's
+error against such a twin where it exceeds its fixed bound.
 """
 from __future__ import annotations
 
+import contextlib
 import json
 import os
 
 import numpy as np
+
+_COMPUTE = np.float64   # the type the parts compute in
+_EDGE = None            # what every operator's result goes through (None: nothing)
+
+
+@contextlib.contextmanager
+def plain_precision(compute=np.float64, edge=None):
+    """Within the block the parts compute in `compute` and pass each operator's result through `edge`."""
+    global _COMPUTE, _EDGE
+    saved = (_COMPUTE, _EDGE)
+    _COMPUTE, _EDGE = compute, edge
+    try:
+        yield
+    finally:
+        _COMPUTE, _EDGE = saved
+
+
+def round_bfloat16(x):
+    """x rounded to the nearest bfloat16 (ties to even), as float32."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    finite = (bits & np.uint32(0x7F800000)) != np.uint32(0x7F800000)
+    rounded = (bits + np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    return np.where(finite, rounded, bits).astype(np.uint32).view(np.float32)
+
+
+def _edge(y):
+    return y if _EDGE is None else np.asarray(_EDGE(y), dtype=_COMPUTE)
 
 
 # ----------------------------------------------------------------------------------------
@@ -29,22 +65,26 @@ import numpy as np
 
 def plain_embedding(ids, table):
     """x[t, :] = table[ids[t], :], no scaling.  rust/engine/src/runner/model/qwen2/kernels.rs:46-57"""
-    return np.asarray(table, dtype=np.float64)[np.asarray(ids, dtype=np.int64)]
+    return _edge(np.asarray(table, dtype=_COMPUTE)[np.asarray(ids, dtype=np.int64)])
 
 
 def plain_rms_norm(x, weight, eps):
     """y = x * rsqrt(mean(x^2) + eps) * w, mean over the true width.  kernels.rs:546-582"""
-    x = np.asarray(x, dtype=np.float64)
-    inv = 1.0 / np.sqrt((x * x).mean(axis=-1, keepdims=True) + float(eps))
-    return x * inv * np.asarray(weight, dtype=np.float64)
+    x = np.asarray(x, dtype=_COMPUTE)
+    inv = 1.0 / np.sqrt((x * x).mean(axis=-1, keepdims=True) + _COMPUTE(eps))
+    return _edge(x * inv * np.asarray(weight, dtype=_COMPUTE))
+
+
+def _product(x, weight, bias=None):
+    y = np.asarray(x, dtype=_COMPUTE) @ np.asarray(weight, dtype=_COMPUTE).T
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=_COMPUTE)
+    return y
 
 
 def plain_linear(x, weight, bias=None):
     """y = x W^T (+ b); W is stored [out, in].  kernels.rs:156-178, 393-418"""
-    y = np.asarray(x, dtype=np.float64) @ np.asarray(weight, dtype=np.float64).T
-    if bias is not None:
-        y = y + np.asarray(bias, dtype=np.float64)
-    return y
+    return _edge(_product(x, weight, bias))
 
 
 def plain_inv_freq(head_dim, theta):
@@ -59,14 +99,14 @@ def plain_rope(x, positions, theta):
 
     x: [T, heads, d]; positions: [T].
     """
-    x = np.asarray(x, dtype=np.float64)
+    x = np.asarray(x, dtype=_COMPUTE)
     d = x.shape[-1]
     inv = plain_inv_freq(d, theta)
     ang = (np.asarray(positions, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
-    c = np.cos(ang.astype(np.float64))[:, None, :]
-    s = np.sin(ang.astype(np.float64))[:, None, :]
+    c = np.cos(ang.astype(np.float64))[:, None, :].astype(_COMPUTE)
+    s = np.sin(ang.astype(np.float64))[:, None, :].astype(_COMPUTE)
     lo, hi = x[..., : d // 2], x[..., d // 2:]
-    return np.concatenate([lo * c - hi * s, hi * c + lo * s], axis=-1)
+    return _edge(np.concatenate([lo * c - hi * s, hi * c + lo * s], axis=-1))
 
 
 def plain_attention(q, k, v, positions, window=0):
@@ -79,9 +119,9 @@ def plain_attention(q, k, v, positions, window=0):
 
     q: [T, n_h, d]; k, v: [T, n_kv, d]; positions: [T] absolute, increasing.
     """
-    q = np.asarray(q, dtype=np.float64)
-    k = np.asarray(k, dtype=np.float64)
-    v = np.asarray(v, dtype=np.float64)
+    q = np.asarray(q, dtype=_COMPUTE)
+    k = np.asarray(k, dtype=_COMPUTE)
+    v = np.asarray(v, dtype=_COMPUTE)
     T, n_h, d = q.shape
     n_kv = k.shape[1]
     group = n_h // n_kv
@@ -91,27 +131,31 @@ def plain_attention(q, k, v, positions, window=0):
     if window:
         visible &= diff < window
     out = np.empty_like(q)
-    scale = 1.0 / np.sqrt(d)
+    scale = _COMPUTE(1.0 / np.sqrt(d))
     for h in range(n_h):
         g = h // group
         s = (q[:, h, :] @ k[:, g, :].T) * scale
         s = np.where(visible, s, -np.inf)
         s = s - s.max(axis=-1, keepdims=True)
         p = np.exp(s)
-        p = p / p.sum(axis=-1, keepdims=True)
-        out[:, h, :] = p @ v[:, g, :]
-    return out
+        if _EDGE is None:
+            p = p / p.sum(axis=-1, keepdims=True)
+            out[:, h, :] = p @ v[:, g, :]
+        else:
+            # p is rounded before P V, the sum runs over the unrounded p (kernels.rs:802-828, 946-1124)
+            out[:, h, :] = (_edge(p) @ v[:, g, :]) / p.sum(axis=-1, keepdims=True)
+    return _edge(out)
 
 
 def plain_silu(x):
     """silu(g) = g / (1 + exp(-g)).  kernels.rs:1469-1486"""
-    x = np.asarray(x, dtype=np.float64)
+    x = np.asarray(x, dtype=_COMPUTE)
     return x / (1.0 + np.exp(-x))
 
 
 def plain_gated_mlp(x, w_gate, w_up, w_down):
     """down( silu(x Wg^T) * (x Wu^T) ), no biases.  kernels.rs:1469-1486; engine.rs:1242-1293"""
-    return plain_linear(plain_silu(plain_linear(x, w_gate)) * plain_linear(x, w_up), w_down)
+    return plain_linear(_edge(plain_silu(_product(x, w_gate)) * _product(x, w_up)), w_down)
 
 
 def plain_attention_part(x, w, prefix, cfg, positions, window):
@@ -134,10 +178,10 @@ def plain_block(x, w, layer, cfg, positions):
     eps = cfg["rms_norm_eps"]
     a = plain_attention_part(plain_rms_norm(x, w[p + "input_layernorm.weight"], eps), w, p + "self_attn.",
                              cfg, positions, layer_window(cfg, layer))
-    r = x + a
+    r = _edge(x + a)
     f = plain_gated_mlp(plain_rms_norm(r, w[p + "post_attention_layernorm.weight"], eps),
                         w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
-    return r + f
+    return _edge(r + f)
 
 
 # ----------------------------------------------------------------------------------------
@@ -168,7 +212,7 @@ def plain_head(cfg, w, hidden):
     """Logits of rows of the final norm's output; the head is the embedding table when tied.
     engine.rs:299-303, 1312-1341"""
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
-    return plain_linear(hidden, head)
+    return _product(hidden, head)     # the logits stay 32-bit: no rounding at this edge
 
 
 def plain_forward(cfg, w, ids):

@@ -54,6 +54,17 @@ def model_case(tmp_path_factory, name, dtype):
     return _cache[key]
 
 
+_twins = {}
+
+
+def twin_of(tmp_path_factory, name, dtype):
+    """The twin's logits for the sequences of `model_case(name, dtype)` (formed once)."""
+    if (name, dtype) not in _twins:
+        folder, _, _, seqs, _, _ = model_case(tmp_path_factory, name, dtype)
+        _twins[(name, dtype)] = plain_logits(folder, seqs, twin=dtype)
+    return _twins[(name, dtype)]
+
+
 def make_trace(kind, seqs):
     if kind == "whole":
         return trace_whole(seqs)
@@ -73,21 +84,61 @@ def record(**what):
             fh.write(json.dumps(dict(test=os.environ.get("PYTEST_CURRENT_TEST", ""), **what)) + "\n")
 
 
-def check(got, ref, dtype, seqs, layers=3):
+# Where an engine's error exceeds its fixed bound, the model itself may be that sensitive to rounding (a
+# wide, deep, peaky random model in 32-bit; a narrow one in bfloat16).  That is decided by the plain
+# implementation run with the engine's own precision (`plain_logits(..., twin=dtype)`): the engine may then
+# be at most this much farther from the 64-bit logits than that twin is (both are the largest of a million
+# rounding errors summed in different orders: over 800 random configurations ten went beyond their fixed
+# bound, with 0.76 to 1.54 times their twin's error).  A misplaced key or page moves logits by their own
+# size, a hundred times beyond any of this.
+TWIN_FACTOR = 2.0
+# The fixed configurations in bfloat16 are held against their twin in every test, bound or no bound
+# (`always`): over configurations A to G and the four cuts the engine's largest error was 0.93 to 1.26 times
+# its twin's and its root-mean-square error 0.94 to 1.01 times: the kernels round where the twin rounds and
+# nowhere else.
+TWIN_ALWAYS_MAX, TWIN_ALWAYS_RMS = 1.6, 1.15
+
+
+def check(got, ref, dtype, seqs, layers=3, twin=None, always=False):
     assert set(got) == {(n, p) for n, ids in seqs.items() for p in range(len(ids))}, "every position was asked for"
-    check_rows(got, ref, dtype, layers)
+    check_rows(got, ref, dtype, layers, twin, always)
 
 
-def check_rows(got, ref, dtype, layers=3):
+def check_rows(got, ref, dtype, layers=3, twin=None, always=False):
+    """`twin`: None, or a function that returns the twin's logits {name: [T, vocab]} for the rows of `got`.
+    With `always`, a bfloat16 engine is held against its twin whether or not it keeps the fixed bound:
+    rounding decides how far it may be, not the widest model the bound has to admit."""
+    if always and dtype == "bfloat16":
+        mx, rms, where = error_stats(got, ref)
+        tmx, trms, _ = error_stats(as_rows(twin(), got), ref)
+        record(dtype=dtype, max=mx, rms=rms, twin_max=tmx, twin_rms=trms, layers=layers, always=True)
+        assert mx <= TWIN_ALWAYS_MAX * tmx and rms <= TWIN_ALWAYS_RMS * trms, \
+            f"relative max {mx:.3e}, rms {rms:.3e}, worst at {where}; rounding at the operators' edges alone gives {tmx:.3e}, {trms:.3e}"
     if dtype == "float32":
         err, scale, where = worst_error(got, ref)
         record(dtype=dtype, abs=err, scale=scale)
+        if err > F32_ABS and twin is not None:
+            noise = worst_error(as_rows(twin(), got), ref)[0]
+            record(dtype=dtype, abs=err, twin_abs=noise)
+            assert err <= TWIN_FACTOR * noise, f"max abs error {err:.3e} at {where}; 32-bit arithmetic alone gives {noise:.3e}"
+            return
         assert err <= F32_ABS, f"max abs error {err:.3e} at {where} (largest logit {scale:.2f})"
     else:
         mx, rms, where = error_stats(got, ref)
         record(dtype=dtype, max=mx, rms=rms, layers=layers)
         bound_max, bound_rms = bf16_bounds(layers)
+        if (mx > bound_max or rms > bound_rms) and twin is not None:
+            tmx, trms, _ = error_stats(as_rows(twin(), got), ref)
+            record(dtype=dtype, max=mx, rms=rms, twin_max=tmx, twin_rms=trms, layers=layers)
+            assert mx <= max(bound_max, TWIN_FACTOR * tmx) and rms <= max(bound_rms, TWIN_FACTOR * trms), \
+                f"relative max {mx:.3e}, rms {rms:.3e}, worst at {where}; rounding at the operators' edges alone gives {tmx:.3e}, {trms:.3e}"
+            return
         assert mx <= bound_max and rms <= bound_rms, f"relative max {mx:.3e}, rms {rms:.3e}, worst at {where}"
+
+
+def as_rows(by_name, like):
+    """{(name, position): row} of whole-sequence logits, for the keys of `like`."""
+    return {(name, pos): by_name[name][pos] for (name, pos) in like}
 
 
 @pytest.mark.parametrize("kind", ["whole", "tail", "portions", "mixed"])
@@ -104,7 +155,7 @@ def test_replay(tmp_path_factory, name, dtype, kind):
                     max_batch_tokens=max(need, 64))
     total_pages = engine.free_pages()
     got = run_trace_inprocess(engine, steps)
-    check(got, ref, dtype, seqs, cfg["num_hidden_layers"])
+    check(got, ref, dtype, seqs, cfg["num_hidden_layers"], twin=lambda: twin_of(tmp_path_factory, name, dtype), always=True)
     assert engine.free_pages() == total_pages and engine.cache.live_requests == 0, "everything was given back"
     engine.cache.check_consistency()
     if kind == "mixed":
@@ -137,8 +188,10 @@ def test_random_configurations_and_traces(tmp_path, seed, dtype):
     vocabulary and page size, windows) under random interleavings with portions of 1 to 300 tokens.
     In 32-bit every configuration is held to the absolute bound.  In bfloat16 the error of a deep
     peaky model compounds from layer to layer, so the same sizes run with one layer, where the bound
-    measured on the fixed configurations holds.  LAB_RANDOM_CONFIGURATIONS=500 in the environment
-    runs that many instead of twelve."""
+    measured on the fixed configurations holds.  A configuration beyond its bound is held against the
+    plain implementation's twin of the same precision (a few in a hundred are that sensitive to rounding:
+    three layers of width 300 in 32-bit, a width of 42 in bfloat16).  LAB_RANDOM_CONFIGURATIONS=500 in
+    the environment runs that many instead of twelve."""
     from llm_inference_lab_b200.engine import Engine
 
     rng = np.random.default_rng(7000 + seed)
@@ -152,7 +205,8 @@ def test_random_configurations_and_traces(tmp_path, seed, dtype):
     if seed % 3 == 1:
         engine.enable_step_graphs()
     got = run_trace_inprocess(engine, steps)
-    check(got, plain_logits(folder, seqs), dtype, seqs, cfg["num_hidden_layers"])
+    check(got, plain_logits(folder, seqs), dtype, seqs, cfg["num_hidden_layers"],
+          twin=lambda: plain_logits(folder, seqs, twin=dtype))
     engine.cache.check_consistency()
     assert engine.cache.live_requests == 0 and engine.free_pages() == [engine.num_pages] * engine.cache.num_groups
 
@@ -463,7 +517,9 @@ def test_replay_heads_of_64_and_128(tmp_path_factory, name, dtype, kind):
     before = ops.COUNTER.launches
     got = run_trace_inprocess(engine, steps)
     assert ops.COUNTER.launches > before
-    check(got, ref, dtype, seqs, cfg["num_hidden_layers"])
+    if ("twin", name, dtype) not in _twins and dtype == "bfloat16":
+        _twins[("twin", name, dtype)] = plain_logits(folder, seqs, twin=dtype)
+    check(got, ref, dtype, seqs, cfg["num_hidden_layers"], twin=lambda: _twins[("twin", name, dtype)], always=True)
     assert engine.cache.live_requests == 0 and engine.free_pages() == [engine.num_pages] * engine.cache.num_groups
     runs[kind] = got
     if "whole" in runs and kind != "whole":
