@@ -82,3 +82,33 @@ def test_forward_is_causal_and_reads_the_folder(tmp_path, raw):
         assert not np.allclose(far[25:], full[25:], atol=1e-6), "beyond it the windowed layers see less"
     out = plain_greedy(cfg, w, ids[:5], 3)
     assert len(out) == 3 and out[0] == int(np.argmax(plain_forward(cfg, w, ids[:5])[-1]))
+
+
+def test_twins_of_an_engines_precision(tmp_path):
+    """The plain functions as twins: bfloat16 rounding is round-to-nearest-even (checked against the
+    tensor library's cast, specials included); inside `plain_precision` the parts compute in 32-bit or
+    round every operator's result, outside they are the 64-bit yardstick again; the twins lie near the
+    yardstick by their precision's size, the bfloat16 one farther than the 32-bit one."""
+    import torch
+
+    import plain_qwen2 as pq
+    from plain_qwen2 import plain_precision, read_model_folder, round_bfloat16
+
+    x = (np.random.default_rng(0).standard_normal(50000) * 3.7).astype(np.float32)
+    x[:6] = [0.0, np.inf, -np.inf, 1e-40, 3.3895314e38, -1.0000001]
+    assert np.array_equal(round_bfloat16(x), torch.from_numpy(x).to(torch.bfloat16).float().numpy())
+
+    folder = make_model_folder(str(tmp_path / "m"), TINY_A, 0, "float32")
+    cfg, w = read_model_folder(folder)
+    ids = [int(t) for t in np.random.default_rng(1).integers(0, TINY_A["vocab_size"], 40)]
+    ref = plain_forward(cfg, w, ids)
+    with plain_precision(np.float32):
+        f32 = plain_forward(cfg, w, ids)
+        assert f32.dtype == np.float32
+    with plain_precision(edge=round_bfloat16):
+        b16 = plain_forward(cfg, w, ids)
+    assert pq._COMPUTE is np.float64 and pq._EDGE is None, "the yardstick is back"
+    assert np.array_equal(plain_forward(cfg, w, ids), ref)
+    scale = np.abs(ref).max()
+    e32, e16 = np.abs(f32 - ref).max() / scale, np.abs(b16 - ref).max() / scale
+    assert 0 < e32 < 1e-5 and 1e-4 < e16 < 0.05
