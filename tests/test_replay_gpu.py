@@ -399,7 +399,7 @@ def test_qwen25_15b_layer_sizes_bfloat16_against_the_32_bit_engine(tmp_path):
         record(dtype="bfloat16", shape="1.5B", decode=B, rel=err)
         assert err <= bound, f"decode step of {B} rows: {err:.4f}"
     graphs = DecodeGraphs(engines["bfloat16"])
-    for B in (3, 64, 130):
+    for B in (1, 3, 8, 16, 17, 24, 33, 64, 65, 96, 130, 200):     # every route by rows, padded and not
         toks = random_tokens(rng, B, vocab)
         ref = engines["float32"].step([Entry(r, [t], [0]) for r, t in enumerate(toks)]).float()
         got = graphs.step(list(range(B)), tokens=toks).long()
