@@ -94,8 +94,8 @@ def record(**what):
 TWIN_FACTOR = 2.0
 # The fixed configurations in bfloat16 are held against their twin in every test, bound or no bound
 # (`always`): over configurations A to G and the four cuts the engine's largest error was 0.93 to 1.26 times
-# its twin's and its root-mean-square error 0.94 to 1.01 times: the kernels round where the twin rounds and
-# nowhere else.
+# its twin's and its root-mean-square error 0.94 to 1.01 times; over 300 random one-layer configurations 0.72
+# to 1.15 and 0.92 to 1.01 times: the kernels round where the twin rounds and nowhere else.
 TWIN_ALWAYS_MAX, TWIN_ALWAYS_RMS = 1.6, 1.15
 
 
@@ -188,9 +188,10 @@ def test_random_configurations_and_traces(tmp_path, seed, dtype):
     vocabulary and page size, windows) under random interleavings with portions of 1 to 300 tokens.
     In 32-bit every configuration is held to the absolute bound.  In bfloat16 the error of a deep
     peaky model compounds from layer to layer, so the same sizes run with one layer, where the bound
-    measured on the fixed configurations holds.  A configuration beyond its bound is held against the
-    plain implementation's twin of the same precision (a few in a hundred are that sensitive to rounding:
-    three layers of width 300 in 32-bit, a width of 42 in bfloat16).  LAB_RANDOM_CONFIGURATIONS=500 in
+    measured on the fixed configurations holds.  In bfloat16 every configuration is held against the plain
+    implementation's twin (the same model with every operator's result rounded to bfloat16); in 32-bit a
+    configuration beyond the absolute bound is (a few in a hundred are that sensitive to rounding: three
+    layers of width 300 with peaky attention).  LAB_RANDOM_CONFIGURATIONS=500 in
     the environment runs that many instead of twelve."""
     from llm_inference_lab_b200.engine import Engine
 
@@ -206,7 +207,7 @@ def test_random_configurations_and_traces(tmp_path, seed, dtype):
         engine.enable_step_graphs()
     got = run_trace_inprocess(engine, steps)
     check(got, plain_logits(folder, seqs), dtype, seqs, cfg["num_hidden_layers"],
-          twin=lambda: plain_logits(folder, seqs, twin=dtype))
+          twin=lambda: plain_logits(folder, seqs, twin=dtype), always=True)
     engine.cache.check_consistency()
     assert engine.cache.live_requests == 0 and engine.free_pages() == [engine.num_pages] * engine.cache.num_groups
 
