@@ -304,8 +304,13 @@ def case_05b(request, tmp_path_factory):
     pcfg, w = read_model_folder(folder)
     hidden = {name: plain_hidden(pcfg, w, ids) for name, ids in seqs.items()}
     head = w["model.embed_tokens.weight"]
+    twin = None
+    if dtype == "bfloat16":     # the same hidden states with every operator's result rounded to bfloat16
+        from plain_qwen2 import plain_precision, round_bfloat16
+        with plain_precision(edge=round_bfloat16):
+            twin = {name: np.asarray(plain_hidden(pcfg, w, ids), dtype=np.float64) for name, ids in seqs.items()}
     del w
-    yield dtype, folder, seqs, hidden, head, {}
+    yield dtype, folder, seqs, hidden, head, {"twin": twin}
 
 
 @pytest.mark.parametrize("kind", ["whole", "tail", "portions", "mixed"])
@@ -322,11 +327,13 @@ def test_qwen25_05b_layer_sizes(case_05b, kind):
     engine = Engine(folder, dtype, max_tokens=need, page_size=16, max_requests=4, max_batch_tokens=max(need, 512))
     total_pages = engine.free_pages()
     got = run_trace_inprocess(engine, steps)
-    ref = {}
+    ref, twin = {}, {}
     for name in seqs:
         rows = sorted(p for n, p in got if n == name)
         ref[name] = dict(zip(rows, hidden[name][rows] @ head.T))
-    check_rows(got, ref, dtype, layers=2)
+        if runs["twin"] is not None:
+            twin[name] = dict(zip(rows, runs["twin"][name][rows] @ head.T))
+    check_rows(got, ref, dtype, layers=2, twin=(lambda: twin) if twin else None, always=True)
     assert engine.free_pages() == total_pages and engine.cache.live_requests == 0
     engine.cache.check_consistency()
     if kind == "mixed":
