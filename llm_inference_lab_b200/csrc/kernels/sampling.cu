@@ -25,6 +25,7 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { retur
 
 constexpr int CHUNK = 4096;   // vocabulary entries per block (the reference's argmax tile, kernels.rs:1489-1518)
 constexpr int THREADS = 256;
+static_assert(CHUNK % (THREADS * 4) == 0, "a thread takes whole groups of four entries");
 
 // One block per (chunk of the vocabulary, row).  Each block leaves the best candidate of its
 // chunk in `part_val/part_idx`; the block that finishes last for a row (counted in
@@ -51,14 +52,37 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ token
   float bv = -INFINITY;
   int bi = INT_MAX;
   const int end = min(vocab, (chunk + 1) * CHUNK);
-  for (int i = chunk * CHUNK + threadIdx.x; i < end; i += THREADS) {
-    float v = lr[i];
+  auto consider = [&](float v, int i) {
     if (temp > 0.f) {
       const uint32_t h = mix32(key + (uint32_t)i * 0x85EBCA6Bu);
       const float u = ((float)(h >> 9) + 0.5f) * (1.f / 8388608.f);
       v = v * inv_temp - logf(-logf(u));
     }
     if (better(v, i, bv, bi)) { bv = v; bi = i; }  // a NaN compares false and never wins
+  };
+  if ((ld & 3) == 0 && (((uintptr_t)logits) & 15) == 0) {
+    // rows of 16-byte multiples: four entries a load, the chunk's four loads of a thread in flight together
+    constexpr int ROUNDS = CHUNK / (THREADS * 4);
+    float4 q[ROUNDS];
+#pragma unroll
+    for (int it = 0; it < ROUNDS; ++it) {
+      const int i = chunk * CHUNK + (it * THREADS + (int)threadIdx.x) * 4;
+      q[it] = i + 3 < end ? *reinterpret_cast<const float4*>(lr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int it = 0; it < ROUNDS; ++it) {
+      const int i = chunk * CHUNK + (it * THREADS + (int)threadIdx.x) * 4;
+      if (i + 3 < end) {
+        consider(q[it].x, i);
+        consider(q[it].y, i + 1);
+        consider(q[it].z, i + 2);
+        consider(q[it].w, i + 3);
+      } else {
+        for (int j = i; j < end; ++j) consider(lr[j], j);
+      }
+    }
+  } else {
+    for (int i = chunk * CHUNK + threadIdx.x; i < end; i += THREADS) consider(lr[i], i);
   }
   auto block_best = [&]() {
 #pragma unroll

@@ -602,17 +602,21 @@ def test_attention_needle(kind, dtype, needle):
 # Sampling
 # ----------------------------------------------------------------------------------------
 
-def test_sample_greedy_ties_and_nan():
-    V = 5003
-    logits = torch.full((4, V), -1.0)
+@pytest.mark.parametrize("V,pad", [(5003, 0), (5004, 0), (5003, 1), (4099, 1)])
+def test_sample_greedy_ties_and_nan(V, pad):
+    """Rows of odd width are read entry by entry, rows whose stride is a multiple of four entries four at a
+    load (with a vocabulary that ends inside a group of four when `pad` widens the stride only)."""
+    logits = torch.full((4, V + pad), -1.0)[:, :V]
     logits[0, 700] = 3.0
     logits[0, 4000] = 3.0                      # tie: the smaller index wins
-    logits[1, 5002] = 9.0
+    logits[1, V - 1] = 9.0
     logits[1, 17] = float("nan")               # a NaN never wins
     logits[2, :] = float("nan")                # nothing finite: reported as invalid
     logits[3, 0] = 0.5
-    out = ops().sample(logits.to(DEV)).cpu().tolist()
-    assert out[0] == 700 and out[1] == 5002 and out[3] == 0
+    dev = torch.full((4, V + pad), 7.0, device=DEV)[:, :V]      # what lies beyond the vocabulary must not win
+    dev.copy_(logits)
+    out = ops().sample(dev).cpu().tolist()
+    assert out[0] == 700 and out[1] == V - 1 and out[3] == 0
     assert out[2] == 2**31 - 1
 
 
