@@ -147,11 +147,12 @@ class DecodeGraphs:
         eng._end(pairs, reserved)
         self._last, self._last_requests = cap, list(requests)
         if keep:
-            if not self._ring:
-                self._ring = [(torch.zeros((self.MAX_KEPT_BATCH,), dtype=torch.int32, pin_memory=True),
-                               torch.cuda.Event()) for _ in range(4)]
-            if B > self.MAX_KEPT_BATCH:
-                raise ValueError("batch too large for the kept-token buffers")
+            if not self._ring or B > self._ring[0][0].numel():
+                # (buffers that were outgrown are dropped once their tickets are: a ticket holds its buffer)
+                size = max(self.MAX_KEPT_BATCH, eng.max_requests, B)
+                self._ring = [(torch.zeros((size,), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                              for _ in range(4)]
+                self._ring_at = 0
             buf, event = self._ring[self._ring_at]
             self._ring_at = (self._ring_at + 1) % len(self._ring)
             buf[:B].copy_(cap.tokens[:B], non_blocking=True)
